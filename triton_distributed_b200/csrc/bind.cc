@@ -1,0 +1,257 @@
+// Python bindings (pybind11 through torch/extension.h).  The only translation
+// unit that sees torch headers; kernels are reached through tdb/api.h.
+//
+// Plays the part of the reference's pybind op registry
+// (csrc/lib/registry.h, registry.cc, op_pybind.cc:29-33).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "tdb/api.h"
+#include "tdb/symm_heap.h"
+
+namespace py = pybind11;
+using tdb::SymmHeap;
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_cuda(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
+}
+
+tdb::DType to_dtype(at::ScalarType t) {
+  switch (t) {
+    case at::kBFloat16: return tdb::kBF16;
+    case at::kHalf: return tdb::kF16;
+    case at::kFloat: return tdb::kF32;
+    case at::kInt: return tdb::kI32;
+    case at::kByte: return tdb::kU8;
+    case at::kFloat8_e4m3fn: return tdb::kE4M3;
+    default: TORCH_CHECK(false, "unsupported dtype");
+  }
+}
+
+// A torch tensor viewing `bytes` of a heap (local, peer or multicast window).
+at::Tensor heap_tensor(SymmHeap& h, uint64_t offset, std::vector<int64_t> sizes, at::ScalarType dtype, int peer,
+                       bool multicast) {
+  int64_t numel = 1;
+  for (auto s : sizes) numel *= s;
+  const uint64_t bytes = static_cast<uint64_t>(numel) * c10::elementSize(dtype);
+  TORCH_CHECK(offset + bytes <= h.heap_bytes(), "heap_tensor: out of range");
+  uint64_t base;
+  if (multicast) {
+    TORCH_CHECK(h.has_multicast(), "heap has no multicast mapping");
+    base = h.mc_base();
+  } else {
+    base = h.peer_base(peer < 0 ? h.rank() : peer);
+  }
+  int dev = 0;
+  check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, dev);
+  return at::from_blob(reinterpret_cast<void*>(base + offset), sizes, [](void*) {}, opts);
+}
+
+uint64_t heap_offset_of(SymmHeap& h, const at::Tensor& t) {
+  const uint64_t p = reinterpret_cast<uint64_t>(t.data_ptr());
+  TORCH_CHECK(p >= h.local_base() && p < h.local_base() + h.heap_bytes(), "tensor is not in the local symmetric heap");
+  return p - h.local_base();
+}
+
+py::dict read_status(SymmHeap& h) {
+  py::dict d;
+  tdb::StatusPage* pg = h.status_host();
+  if (pg == nullptr) return d;
+  volatile tdb::StatusRecord* r = &pg->rec;
+  d["code"] = r->code;
+  d["kernel"] = r->kernel;
+  d["where"] = r->where;
+  d["block"] = r->block;
+  d["peer"] = r->peer;
+  d["index"] = r->index;
+  d["expected"] = r->expected;
+  d["observed"] = r->observed;
+  d["abort"] = *reinterpret_cast<volatile int32_t*>(&pg->abort_word);
+  d["heartbeat"] = *reinterpret_cast<volatile int32_t*>(&pg->heartbeat);
+  return d;
+}
+void clear_status(SymmHeap& h) {
+  if (h.status_host() != nullptr) std::memset(h.status_host(), 0, sizeof(tdb::StatusPage));
+}
+void set_abort(SymmHeap& h, int v) {
+  if (h.status_host() != nullptr) *reinterpret_cast<volatile int32_t*>(&h.status_host()->abort_word) = v;
+}
+
+tdb::TensorMap make_tmap3(const void* base, tdb::DType dt, uint64_t d2, uint64_t rows, uint64_t cols,
+                          uint64_t row_stride, uint64_t d2_stride, uint32_t box_rows, uint32_t box_cols) {
+  tdb::TensorMap m;
+  const int r = tdb::encode_tensor_map_3d(&m, base, dt, d2, rows, cols, row_stride, d2_stride, box_rows, box_cols, 128);
+  TORCH_CHECK(r == 0, "cuTensorMapEncodeTiled failed with code ", r);
+  return m;
+}
+
+int pick_block_n(int64_t N, int block_n) {
+  if (block_n == 128 || block_n == 256) return block_n;
+  return N <= 128 ? 128 : 256;
+}
+
+int sm_count() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
+
+// C[M,N] = A[M,K] @ B[N,K]^T   (bf16)
+void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int block_n, int num_ctas) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && c.is_cuda(), "gemm: CUDA tensors expected");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && c.scalar_type() == at::kBFloat16,
+              "gemm: bf16 expected");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2, "gemm: 2-D tensors expected");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && c.stride(1) == 1, "gemm: innermost dimension must be contiguous");
+  const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
+  TORCH_CHECK(b.size(1) == K && c.size(0) == M && c.size(1) == N, "gemm: shape mismatch");
+  TORCH_CHECK(K % 8 == 0 && a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "gemm: K and row strides must be multiples of 8");
+  if (M == 0 || N == 0) return;
+  c10::cuda::CUDAGuard guard(a.device());
+  tdb::GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.mode = tdb::kGemmPlain;
+  g.M = M; g.N = N; g.K = K;
+  g.c = c.data_ptr();
+  g.ldc = c.stride(0);
+  g.block_n = pick_block_n(N, block_n);
+  g.tmap_a = make_tmap3(a.data_ptr(), tdb::kBF16, 1, M, K, a.stride(0) * 2, a.stride(0) * 2 * M, 128, 64);
+  g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, g.block_n, 64);
+  const int tiles = ((M + 127) / 128) * ((N + g.block_n - 1) / g.block_n);
+  g.num_ctas = std::min<int>(num_ctas > 0 ? num_ctas : sm_count(), tiles);
+  g.symm.world = 1;
+  g.symm.timeout_ns = 2000000000ull;
+  check_cuda(tdb::launch_gemm(g, cur_stream()), "launch_gemm");
+}
+
+// Fused all-gather + GEMM.  a_local [m, K]; b [N_local, K]; out [W*m, N_local];
+// ws / flags / ctx live in the symmetric heap (ws, flags) and in device memory (ctx).
+void ag_gemm_bf16(SymmHeap& h, const at::Tensor& a_local, const at::Tensor& b, at::Tensor& c, at::Tensor& ws,
+                  at::Tensor& flags, at::Tensor& ctx, int64_t max_seg_rows, int64_t max_chunks, int n_comm,
+                  int block_n, int num_ctas, bool use_multimem, double timeout_s) {
+  TORCH_CHECK(a_local.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "ag_gemm: bf16 expected");
+  TORCH_CHECK(a_local.is_contiguous() && b.stride(1) == 1 && c.stride(1) == 1, "ag_gemm: contiguous inputs expected");
+  const int W = h.world();
+  const int64_t m = a_local.size(0), K = a_local.size(1), N = b.size(0), M = m * W;
+  TORCH_CHECK(b.size(1) == K && c.size(0) == M && c.size(1) == N, "ag_gemm: shape mismatch");
+  TORCH_CHECK(m <= max_seg_rows, "ag_gemm: more rows than the context was created for");
+  TORCH_CHECK(K % 8 == 0, "ag_gemm: K must be a multiple of 8");
+  const uint64_t buf_elems = static_cast<uint64_t>(W) * max_seg_rows * K;
+  TORCH_CHECK(static_cast<uint64_t>(ws.numel()) >= 2 * buf_elems, "ag_gemm: workspace too small");
+  c10::cuda::CUDAGuard guard(a_local.device());
+  tdb::GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.mode = tdb::kGemmAllGather;
+  g.M = M; g.N = N; g.K = K;
+  g.c = c.data_ptr();
+  g.ldc = c.stride(0);
+  g.block_n = pick_block_n(N, block_n);
+  g.tmap_a = make_tmap3(ws.data_ptr(), tdb::kBF16, 2, M, K, K * 2, buf_elems * 2, 128, 64);
+  g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, g.block_n, 64);
+  g.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
+  g.seg_rows = m;
+  g.max_seg_rows = max_seg_rows;
+  g.n_comm_ctas = n_comm;
+  g.a_local = a_local.data_ptr();
+  g.ag_ws = ws.data_ptr();
+  g.ag_flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
+  g.max_chunks = max_chunks;
+  g.ctx = reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr());
+  g.symm = h.info(static_cast<uint64_t>(timeout_s * 1e9));
+  g.use_multimem = use_multimem ? 1 : 0;
+  check_cuda(tdb::launch_gemm(g, cur_stream()), "launch_gemm(all-gather)");
+}
+
+// Fused GEMM + reduce-scatter.  a [M, K_local]; b [N, K_local]; out [M/W, N].
+void gemm_rs_bf16(SymmHeap& h, const at::Tensor& a, const at::Tensor& b, at::Tensor& out, at::Tensor& slots,
+                  at::Tensor& flags, at::Tensor& ctx, int64_t max_seg_rows, int64_t max_tiles, int block_n,
+                  int num_ctas, double timeout_s) {
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_rs: bf16 expected");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1, "gemm_rs: contiguous inputs expected");
+  const int W = h.world();
+  const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
+  TORCH_CHECK(M % W == 0, "gemm_rs: M must be divisible by the world size");
+  const int64_t m = M / W;
+  TORCH_CHECK(b.size(1) == K && out.size(0) == m && out.size(1) == N, "gemm_rs: shape mismatch");
+  TORCH_CHECK(m <= max_seg_rows, "gemm_rs: more rows than the context was created for");
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0, "gemm_rs: K and N must be multiples of 8");
+  TORCH_CHECK(static_cast<uint64_t>(slots.numel()) >= 2ull * W * max_seg_rows * N, "gemm_rs: slot buffer too small");
+  c10::cuda::CUDAGuard guard(a.device());
+  tdb::GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.mode = tdb::kGemmReduceScatter;
+  g.M = M; g.N = N; g.K = K;
+  g.block_n = pick_block_n(N, block_n);
+  g.tmap_a = make_tmap3(a.data_ptr(), tdb::kBF16, 1, M, K, a.stride(0) * 2, a.stride(0) * 2 * M, 128, 64);
+  g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, g.block_n, 64);
+  g.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
+  g.seg_rows = m;
+  g.max_seg_rows = max_seg_rows;
+  g.rs_slots = slots.data_ptr();
+  g.rs_flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
+  g.max_tiles = max_tiles;
+  g.rs_out = out.data_ptr();
+  g.ld_out = out.stride(0);
+  g.ctx = reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr());
+  g.symm = h.info(static_cast<uint64_t>(timeout_s * 1e9));
+  check_cuda(tdb::launch_gemm(g, cur_stream()), "launch_gemm(reduce-scatter)");
+}
+
+}  // namespace
+
+void bind_more(py::module_& m);  // bind_ops.inc-style split kept in this file for build simplicity
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "triton_distributed_b200 native library (sm_100a)";
+
+  py::class_<SymmHeap>(m, "SymmHeap")
+      .def(py::init<int, int, int, uint64_t, const std::string&, bool>(), py::arg("rank"), py::arg("world"),
+           py::arg("device"), py::arg("heap_bytes"), py::arg("session"), py::arg("want_multicast"))
+      .def("create", &SymmHeap::create)
+      .def("exchange_and_map", &SymmHeap::exchange_and_map, py::call_guard<py::gil_scoped_release>())
+      .def("multicast_setup", &SymmHeap::multicast_setup, py::call_guard<py::gil_scoped_release>())
+      .def("multicast_bind", &SymmHeap::multicast_bind)
+      .def("create_ipc", &SymmHeap::create_ipc)
+      .def("ipc_handle", [](SymmHeap& h) { return py::bytes(h.ipc_handle()); })
+      .def("map_ipc",
+           [](SymmHeap& h, const std::vector<py::bytes>& hs) {
+             std::vector<std::string> v;
+             for (auto& b : hs) v.push_back(std::string(b));
+             h.map_ipc(v);
+           })
+      .def("destroy", &SymmHeap::destroy)
+      .def("alloc", &SymmHeap::alloc, py::arg("bytes"), py::arg("align") = 256)
+      .def("free", &SymmHeap::free)
+      .def("tensor", &heap_tensor, py::arg("offset"), py::arg("sizes"), py::arg("dtype"), py::arg("peer") = -1,
+           py::arg("multicast") = false)
+      .def("offset_of", &heap_offset_of)
+      .def("read_status", &read_status)
+      .def("clear_status", &clear_status)
+      .def("set_abort", &set_abort)
+      .def_property_readonly("local_base", &SymmHeap::local_base)
+      .def("peer_base", &SymmHeap::peer_base)
+      .def_property_readonly("mc_base", &SymmHeap::mc_base)
+      .def_property_readonly("heap_bytes", &SymmHeap::heap_bytes)
+      .def_property_readonly("has_multicast", &SymmHeap::has_multicast)
+      .def_property_readonly("rank", &SymmHeap::rank)
+      .def_property_readonly("world", &SymmHeap::world)
+      .def_property_readonly("bytes_in_use", &SymmHeap::bytes_in_use)
+      .def_property_readonly("mode", &SymmHeap::mode);
+
+  m.def("stream_write_value32", [](uint64_t addr, uint32_t v) {
+    TORCH_CHECK(tdb::stream_write_value32(addr, v, cur_stream()) == 0, "cuStreamWriteValue32 failed");
+  });
+  m.def("stream_wait_value32", [](uint64_t addr, uint32_t v, bool geq) {
+    const int r = geq ? tdb::stream_wait_value32_geq(addr, v, cur_stream()) : tdb::stream_wait_value32_eq(addr, v, cur_stream());
+    TORCH_CHECK(r == 0, "cuStreamWaitValue32 failed");
+  });
+
+  m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("block_n") = 0,
+        py::arg("num_ctas") = 0);
+  m.def("ag_gemm_bf16", &ag_gemm_bf16);
+  m.def("gemm_rs_bf16", &gemm_rs_bf16);
+  m.def("gemm_smem_bytes", &tdb::gemm_smem_bytes);
+  bind_more(m);
+}

@@ -1,0 +1,502 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a and its two fused
+// tensor-parallel forms:
+//
+//   plain           C[M,N] = A[M,K] * B[N,K]^T
+//   all-gather      A is sharded by rows over the ranks; "comm" CTAs of the same
+//                   launch push the local shard into every rank's workspace
+//                   (NVLS multimem.st, or plain peer stores) chunk by chunk and
+//                   set a per-chunk epoch flag; GEMM CTAs wait for exactly the
+//                   chunk a tile needs, then TMA-load it from LOCAL memory.
+//   reduce-scatter  every rank computes a partial C; the epilogue stores each
+//                   tile straight into the owner rank's slot over NVLink and
+//                   sets a per-tile epoch flag there; after its last tile every
+//                   CTA joins the owner-side reduction of the arrived slots.
+//
+// Roles inside a CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer
+// (one elected lane) and TMEM owner, warps 2-5 = epilogue (TMEM -> registers ->
+// bf16 -> global / peer memory).  Accumulators are double-buffered in TMEM
+// (2 x BLOCK_N fp32 columns) so the epilogue of tile i overlaps the main loop of
+// tile i+1.
+//
+// Reference behaviour being matched (not its code):
+//   AG+GEMM   python/triton_dist/kernels/nvidia/allgather_gemm.py:159-264 (consumer GEMM waits per rank
+//             segment, local segment first) and allgather.py:106-137 (producer + ready flags)
+//   GEMM+RS   python/triton_dist/kernels/nvidia/gemm_reduce_scatter.py:122-250 (tile order starts at the
+//             next rank's segment, `fuse_scatter` epilogue writes into the owner's buffer :235-248)
+//             and reduce_scatter.py:674-815 (local reduction over the W slots)
+// Flags hold the call epoch (kept in device memory and bumped by the last CTA),
+// buffers alternate by epoch parity, so nothing is reset and no barrier is needed
+// between calls; every wait is bounded and reports through the status page.
+#include <cuda.h>
+
+#include "tdb/api.h"
+#include "tdb/symm_device.cuh"
+
+namespace tdb {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;           // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr int kGroupM = 8;
+constexpr uint64_t kMbarTimeoutNs = 4000000000ull;  // 4 s
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  // full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], tmem_base, abort
+  static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 16;
+};
+
+struct KParams {
+  int mode;
+  int M, N, K;
+  __nv_bfloat16* c;
+  int64_t ldc;
+  int tiles_m_seg;   // M tiles per segment
+  int tiles_n;
+  int num_seg;
+  int seg_first;     // first segment in this rank's tile order
+  int seg_rows;
+  int n_comm;
+  // all-gather
+  const __nv_bfloat16* a_local;
+  __nv_bfloat16* ag_ws;
+  uint64_t ag_buf_elems;   // elements between the two workspace buffers
+  uint32_t* ag_flags;
+  int max_chunks;
+  int use_mc;
+  // reduce-scatter
+  __nv_bfloat16* rs_slots;
+  uint64_t rs_slot_elems;  // elements per (buffer, source) slot
+  uint32_t* rs_flags;
+  int max_tiles;
+  __nv_bfloat16* rs_out;
+  int64_t ld_out;
+  CtxDev* ctx;
+  SymmInfo symm;
+};
+
+struct Tile {
+  int seg, mt, nt, m0, n0, m_end;
+};
+
+__device__ __forceinline__ Tile decode_tile(const KParams& p, int t, int BN) {
+  Tile r;
+  const int per_seg = p.tiles_m_seg * p.tiles_n;
+  const int si = t / per_seg;
+  const int rem = t - si * per_seg;
+  r.seg = (p.seg_first + si) % p.num_seg;
+  const int group_sz = kGroupM * p.tiles_n;
+  const int g = rem / group_sz;
+  const int first_m = g * kGroupM;
+  const int gm = min(p.tiles_m_seg - first_m, kGroupM);
+  const int in_g = rem - g * group_sz;
+  r.mt = first_m + in_g % gm;
+  r.nt = in_g / gm;
+  r.m0 = r.seg * p.seg_rows + r.mt * kBM;
+  r.n0 = r.nt * BN;
+  r.m_end = min(p.M, (r.seg + 1) * p.seg_rows);
+  return r;
+}
+
+// Push this rank's shard into every rank's workspace (comm CTAs of the all-gather mode).
+__device__ void ag_push(const KParams& p, uint32_t epoch) {
+  const int buf = epoch & 1;
+  const int W = p.symm.world, rank = p.symm.rank;
+  const int chunks = (p.seg_rows + kBM - 1) / kBM;
+  const uint64_t row_bytes = static_cast<uint64_t>(p.K) * 2;
+  char* ws_local = reinterpret_cast<char*>(p.ag_ws + buf * p.ag_buf_elems);
+  for (int c = blockIdx.x; c < chunks; c += p.n_comm) {
+    const int r0 = c * kBM;
+    const int rows = min(kBM, p.seg_rows - r0);
+    const uint64_t bytes = rows * row_bytes;
+    const char* src = reinterpret_cast<const char*>(p.a_local) + r0 * row_bytes;
+    char* dst_local = ws_local + (static_cast<uint64_t>(rank) * p.seg_rows + r0) * row_bytes;
+    const uint64_t nvec = bytes >> 4;
+    if (p.use_mc) {
+      char* dst = mc_ptr(p.symm, dst_local);
+      uint64_t i = threadIdx.x;
+      for (; i + 3ull * kThreads < nvec; i += 4ull * kThreads) {
+        uint4 v0 = ld_nc_v4(src + (i << 4));
+        uint4 v1 = ld_nc_v4(src + ((i + kThreads) << 4));
+        uint4 v2 = ld_nc_v4(src + ((i + 2 * kThreads) << 4));
+        uint4 v3 = ld_nc_v4(src + ((i + 3 * kThreads) << 4));
+        multimem_st_v4(dst + (i << 4), v0);
+        multimem_st_v4(dst + ((i + kThreads) << 4), v1);
+        multimem_st_v4(dst + ((i + 2 * kThreads) << 4), v2);
+        multimem_st_v4(dst + ((i + 3 * kThreads) << 4), v3);
+      }
+      for (; i < nvec; i += kThreads) multimem_st_v4(dst + (i << 4), ld_nc_v4(src + (i << 4)));
+    } else {
+      char* dsts[kMaxRanks];
+#pragma unroll
+      for (int j = 0; j < kMaxRanks; ++j) dsts[j] = symm_at(p.symm, dst_local, j < W ? (rank + j) % W : rank);
+      uint64_t i = threadIdx.x;
+      for (; i + kThreads < nvec; i += 2ull * kThreads) {
+        uint4 v0 = ld_nc_v4(src + (i << 4));
+        uint4 v1 = ld_nc_v4(src + ((i + kThreads) << 4));
+#pragma unroll
+        for (int j = 0; j < kMaxRanks; ++j) {
+          if (j < W) {
+            st_v4(dsts[j] + (i << 4), v0);
+            st_v4(dsts[j] + ((i + kThreads) << 4), v1);
+          }
+        }
+      }
+      for (; i < nvec; i += kThreads) {
+        uint4 v0 = ld_nc_v4(src + (i << 4));
+#pragma unroll
+        for (int j = 0; j < kMaxRanks; ++j)
+          if (j < W) st_v4(dsts[j] + (i << 4), v0);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < W) {
+      // every lane orders the CTA's stores (made visible to it by the barrier)
+      // before its own flag store
+      fence_acq_rel_sys();
+      uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * W + rank) * p.max_chunks + c;
+      st_release_sys(symm_at(p.symm, flag, (rank + threadIdx.x) % W), epoch);
+    }
+  }
+}
+
+// Owner-side reduction of the reduce-scatter mode: out[rows of my segment] = sum over sources.
+__device__ void rs_reduce(const KParams& p, uint32_t epoch, int BN) {
+  const int buf = epoch & 1;
+  const int W = p.symm.world;
+  const int items = p.tiles_m_seg * p.tiles_n;
+  const int vec_per_row = BN / 8;
+  for (int it = blockIdx.x; it < items; it += gridDim.x) {
+    const int mt = it / p.tiles_n, nt = it - mt * p.tiles_n;
+    bool ok = true;
+    if (threadIdx.x < W) {
+      const uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * W + threadIdx.x) * p.max_tiles + it;
+      ok = wait_until(p.symm, flag, epoch, kCmpGe, kKernelGemmRs, 2, threadIdx.x, it);
+    }
+    ok = __syncthreads_and(ok);
+    if (!ok) return;
+    const int r0 = mt * kBM;
+    const int rows = min(kBM, p.seg_rows - r0);
+    const int n0 = nt * BN;
+    const int total = rows * vec_per_row;
+    for (int v = threadIdx.x; v < total; v += kThreads) {
+      const int r = v / vec_per_row, cv = v - r * vec_per_row;
+      const int col = n0 + cv * 8;
+      if (col >= p.N) continue;
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int s = 0; s < W; ++s) {
+        const __nv_bfloat16* src = p.rs_slots + (static_cast<uint64_t>(buf) * W + s) * p.rs_slot_elems +
+                                   static_cast<uint64_t>(r0 + r) * p.N + col;
+        const uint4 u = ld_relaxed_sys_v4(src);
+        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
+                     f3 = unpack_bf16x2(u.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      st_v4(p.rs_out + static_cast<uint64_t>(r0 + r) * p.ld_out + col, o);
+    }
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const KParams p) {
+  using L = SmemLayout<BN>;
+  constexpr int kStages = L::kStages;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // dynamic shared memory is only guaranteed 16-byte aligned: round up to 1024
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t epoch = (p.ctx != nullptr) ? ld_volatile(&p.ctx->epoch) : 1u;
+  const int buf = epoch & 1;
+
+  const bool is_comm = (p.mode == kGemmAllGather) && (static_cast<int>(blockIdx.x) < p.n_comm);
+  if (is_comm) {
+    ag_push(p, epoch);
+  } else {
+    // ------------------------------------------------------------------ setup
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < kStages; ++i) {
+        mbar_init(&full_bar[i], 1);
+        mbar_init(&empty_bar[i], 1);
+      }
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&tmem_full[i], 1);
+        mbar_init(&tmem_empty[i], 128);
+      }
+      *abort_flag = 0;
+      fence_mbar_init();
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+      tmem_alloc(tmem_base_smem, 2 * BN);
+      tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    const int n_gemm = gridDim.x - ((p.mode == kGemmAllGather) ? p.n_comm : 0);
+    const int g_idx = blockIdx.x - ((p.mode == kGemmAllGather) ? p.n_comm : 0);
+    const int num_tiles = p.num_seg * p.tiles_m_seg * p.tiles_n;
+    const int num_kb = (p.K + kBK - 1) / kBK;
+
+    if (warp == 0) {
+      // ------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        uint32_t it = 0;
+        uint32_t issued = 0;
+        bool ok = true;
+        for (int t = g_idx; t < num_tiles && ok; t += n_gemm) {
+          const Tile tl = decode_tile(p, t, BN);
+          if (p.mode == kGemmAllGather) {
+            const uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * p.symm.world + tl.seg) * p.max_chunks + tl.mt;
+            ok = wait_until(p.symm, flag, epoch, kCmpGe, kKernelAgGemm, 1, tl.seg, tl.mt);
+            if (!ok) break;
+            fence_proxy_async();
+          }
+          for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1;
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kMbarTimeoutNs)) {
+              ok = false;
+              report(p.symm, kTimeoutMbarrier, kKernelGemm, 10, -1, s, (int)ph, t);
+              break;
+            }
+            uint8_t* sa = smem + s * L::kStageBytes;
+            uint8_t* sb = sa + L::kABytes;
+            mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
+            tma_load_3d(sa, &tmap_a, &full_bar[s], kb * kBK, tl.m0, (p.mode == kGemmAllGather) ? buf : 0);
+            tma_load_3d(sb, &tmap_b, &full_bar[s], kb * kBK, tl.n0, 0);
+            ++issued;
+          }
+        }
+        if (!ok) {
+          *abort_flag = 1;
+          // drain: every load already issued completes its full barrier on its own
+          const uint32_t first = issued > (uint32_t)kStages ? issued - kStages : 0;
+          for (uint32_t j = first; j < issued; ++j)
+            mbar_wait(&full_bar[j % kStages], (j / kStages) & 1, nullptr, 200000000ull);
+        }
+      }
+    } else if (warp == 1) {
+      // ------------------------------------------------------------ MMA issuer
+      if (lane == 0) {
+        constexpr uint32_t idesc = make_idesc(1u, kBM, BN);
+        uint32_t it = 0;
+        int local = 0;
+        bool ok = true;
+        for (int t = g_idx; t < num_tiles && ok; t += n_gemm, ++local) {
+          const int b = local & 1;
+          const uint32_t aph = (local >> 1) & 1;
+          if (!mbar_wait(&tmem_empty[b], aph ^ 1, abort_flag, kMbarTimeoutNs)) {
+            ok = false;
+            report(p.symm, kTimeoutMbarrier, kKernelGemm, 20, -1, b, (int)aph, t);
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + b * BN;
+          for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1;
+            if (!mbar_wait(&full_bar[s], ph, abort_flag, kMbarTimeoutNs)) {
+              ok = false;
+              report(p.symm, kTimeoutMbarrier, kKernelGemm, 21, -1, s, (int)ph, t);
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
+            const uint64_t adesc = make_smem_desc_sw128(sa);
+            const uint64_t bdesc = make_smem_desc_sw128(sa + L::kABytes);
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              // advance 16 elements (32 bytes) along K inside the swizzle row: +2 in the >>4 address field
+              umma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(&empty_bar[s]);
+          }
+          if (ok) umma_commit(&tmem_full[b]);
+        }
+        if (!ok) *abort_flag = 1;
+      }
+    } else {
+      // ------------------------------------------------------------ epilogue (warps 2..5)
+      const int q = warp & 3;  // TMEM lane quarter this warp may access
+      int local = 0;
+      bool ok = true;
+      for (int t = g_idx; t < num_tiles && ok; t += n_gemm, ++local) {
+        const Tile tl = decode_tile(p, t, BN);
+        const int b = local & 1;
+        const uint32_t aph = (local >> 1) & 1;
+        if (!mbar_wait(&tmem_full[b], aph, abort_flag, kMbarTimeoutNs)) {
+          ok = false;
+          if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemm, 30, -1, b, (int)aph, t);
+          break;
+        }
+        tc_fence_after_sync();
+        const int row = tl.m0 + q * 32 + lane;
+        const bool row_ok = row < tl.m_end;
+        __nv_bfloat16* dst_row;
+        if (p.mode == kGemmReduceScatter) {
+          __nv_bfloat16* slot = p.rs_slots + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.rs_slot_elems +
+                                static_cast<uint64_t>(row - tl.seg * p.seg_rows) * p.N;
+          dst_row = symm_at(p.symm, slot, tl.seg);
+        } else {
+          dst_row = p.c + static_cast<uint64_t>(row) * p.ldc;
+        }
+        const bool vec_ok = (p.mode == kGemmReduceScatter) ? (p.N % 8 == 0) : (p.ldc % 8 == 0);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + b * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
+          tmem_ld_wait();
+          const int col0 = tl.n0 + c * 32;
+          if (row_ok && col0 < p.N) {
+            if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                st_v4(dst_row + col0 + 8 * j, o);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst_row[col0 + j] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          }
+        }
+        // accumulator buffer b may be overwritten by the MMA warp
+        tc_fence_before_sync();
+        mbar_arrive(&tmem_empty[b]);
+        if (p.mode == kGemmReduceScatter) {
+          // all 128 epilogue threads have issued their peer stores
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (warp == 2 && lane == 0) {
+            fence_acq_rel_sys();
+            uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.max_tiles +
+                             tl.mt * p.tiles_n + tl.nt;
+            st_release_sys(symm_at(p.symm, flag, tl.seg), epoch);
+          }
+        }
+      }
+      if (!ok) *abort_flag = 1;
+    }
+
+    // ------------------------------------------------------------ teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+      tc_fence_after_sync();
+      tmem_dealloc(tmem_base, 2 * BN);
+    }
+    if (p.mode == kGemmReduceScatter && *abort_flag == 0) rs_reduce(p, epoch, BN);
+  }
+
+  // last CTA out advances the call epoch
+  if (p.ctx != nullptr) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const uint32_t prev = atomicAdd(&p.ctx->done, 1u);
+      if (prev == gridDim.x - 1) {
+        p.ctx->done = 0;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(&p.ctx->epoch) = epoch + 1;
+      }
+    }
+  }
+}
+
+template <int BN>
+cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  const int smem = L::kTotal + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  KParams p;
+  p.mode = a.mode;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.c = reinterpret_cast<__nv_bfloat16*>(a.c);
+  p.ldc = a.ldc;
+  const bool fused = a.mode != kGemmPlain;
+  p.num_seg = fused ? a.symm.world : 1;
+  p.seg_rows = fused ? a.seg_rows : a.M;
+  p.tiles_m_seg = (p.seg_rows + kBM - 1) / kBM;
+  p.tiles_n = (a.N + BN - 1) / BN;
+  p.seg_first = a.mode == kGemmAllGather ? a.symm.rank
+               : a.mode == kGemmReduceScatter ? (a.symm.rank + 1) % a.symm.world : 0;
+  p.n_comm = a.mode == kGemmAllGather ? a.n_comm_ctas : 0;
+  p.a_local = reinterpret_cast<const __nv_bfloat16*>(a.a_local);
+  p.ag_ws = reinterpret_cast<__nv_bfloat16*>(a.ag_ws);
+  p.ag_buf_elems = static_cast<uint64_t>(a.symm.world) * a.max_seg_rows * static_cast<uint64_t>(a.K);
+  p.ag_flags = a.ag_flags;
+  p.max_chunks = a.max_chunks;
+  p.use_mc = a.use_multimem && a.symm.mc_base != 0;
+  p.rs_slots = reinterpret_cast<__nv_bfloat16*>(a.rs_slots);
+  p.rs_slot_elems = static_cast<uint64_t>(a.max_seg_rows) * a.N;
+  p.rs_flags = a.rs_flags;
+  p.max_tiles = a.max_tiles;
+  p.rs_out = reinterpret_cast<__nv_bfloat16*>(a.rs_out);
+  p.ld_out = a.ld_out;
+  p.ctx = a.ctx;
+  static_assert(sizeof(SymmInfo) == sizeof(SymmInfoHost), "SymmInfo mirrors must match");
+  memcpy(&p.symm, &a.symm, sizeof(SymmInfo));
+  if (a.mode == kGemmAllGather && p.tiles_m_seg > a.max_chunks) return cudaErrorInvalidValue;
+  if (a.mode == kGemmReduceScatter && p.tiles_m_seg * p.tiles_n > a.max_tiles) return cudaErrorInvalidValue;
+  if (a.mode == kGemmAllGather && (a.n_comm_ctas < 1 || a.n_comm_ctas >= a.num_ctas)) return cudaErrorInvalidValue;
+  if (a.K % 8 != 0) return cudaErrorInvalidValue;
+
+  CUtensorMap ta, tb;
+  memcpy(&ta, a.tmap_a.bytes, sizeof(CUtensorMap));
+  memcpy(&tb, a.tmap_b.bytes, sizeof(CUtensorMap));
+  gemm_kernel<BN><<<a.num_ctas, kThreads, smem, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+int gemm_smem_bytes(int block_n) {
+  return (block_n == 256 ? SmemLayout<256>::kTotal : SmemLayout<128>::kTotal) + 1024;
+}
+
+cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
+  if (a.block_n == 256) return launch_impl<256>(a, stream);
+  if (a.block_n == 128) return launch_impl<128>(a, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace tdb

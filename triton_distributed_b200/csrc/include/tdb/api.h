@@ -1,0 +1,86 @@
+// Host-side C++ API of the native library: launchers take raw device pointers
+// and a CUDA stream, never allocate, and return a cudaError_t (0 = success).
+// The torch binding (bind.cc) and the C entry points are thin wrappers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "status.h"
+
+namespace tdb {
+
+constexpr int kMaxRanksHost = 8;
+
+// Host mirror of the device-side SymmInfo (symm_device.cuh).
+struct SymmInfoHost {
+  uint64_t peer_base[kMaxRanksHost];
+  uint64_t mc_base;
+  uint64_t heap_bytes;
+  StatusPage* status;
+  int32_t rank;
+  int32_t world;
+  uint64_t timeout_ns;
+};
+
+// 128-byte opaque CUtensorMap image.
+struct alignas(64) TensorMap {
+  unsigned char bytes[128];
+};
+
+enum DType : int { kBF16 = 0, kF16 = 1, kF32 = 2, kE4M3 = 3, kU8 = 4, kI32 = 5 };
+
+// 2-D row-major tensor [rows, cols] with `row_stride_bytes`; box = [box_rows, box_cols];
+// swizzle_bytes in {0, 32, 64, 128}.  Returns 0 on success, CUresult otherwise.
+int encode_tensor_map_2d(TensorMap* out, const void* base, DType dtype, uint64_t rows, uint64_t cols,
+                         uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle_bytes);
+// 3-D [d2, rows, cols] (used for grouped / batched weights).
+int encode_tensor_map_3d(TensorMap* out, const void* base, DType dtype, uint64_t d2, uint64_t rows, uint64_t cols,
+                         uint64_t row_stride_bytes, uint64_t d2_stride_bytes, uint32_t box_rows, uint32_t box_cols,
+                         int swizzle_bytes);
+
+// Per-context device state of the fused kernels: call epoch (bumped by the last
+// CTA of every launch, so CUDA-graph replays advance it) and a CTA exit counter.
+struct CtxDev {
+  uint32_t epoch;
+  uint32_t done;
+  uint32_t grid_bar;   // word for in-kernel grid barriers
+  uint32_t pad[5];
+};
+
+// ---------------------------------------------------------------------------
+// GEMM family (gemm_sm100.cu): C[M,N] = A[M,K] * B[N,K]^T, bf16 in, fp32 accumulate.
+// ---------------------------------------------------------------------------
+enum GemmMode : int { kGemmPlain = 0, kGemmAllGather = 1, kGemmReduceScatter = 2 };
+
+struct GemmArgs {
+  int mode;
+  int M, N, K;
+  // plain: output
+  void* c;          // bf16 [M, ldc]
+  int64_t ldc;
+  // tensor maps: A tiles [128 x 64], B tiles [BN x 64], 128-byte swizzle
+  TensorMap tmap_a;
+  TensorMap tmap_b;
+  int block_n;      // 128 or 256
+  int num_ctas;     // grid size (<= SM count)
+  // fused modes
+  int seg_rows;     // rows per rank segment (M = world * seg_rows)
+  int max_seg_rows; // capacity the context was created with (per segment)
+  int n_comm_ctas;  // all-gather: CTAs that only push
+  const void* a_local;   // all-gather: local shard [seg_rows, K]
+  void* ag_ws;           // all-gather: heap workspace [2][world*max_seg_rows][K]
+  uint32_t* ag_flags;    // heap, [2][world][max_chunks]
+  int max_chunks;
+  void* rs_slots;        // reduce-scatter: heap [2][world][max_seg_rows][N]
+  uint32_t* rs_flags;    // heap [2][world][max_tiles]
+  int max_tiles;
+  void* rs_out;          // [seg_rows, N] bf16
+  int64_t ld_out;
+  CtxDev* ctx;           // device memory
+  SymmInfoHost symm;
+  int use_multimem;      // all-gather push through the multicast mapping
+};
+cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream);
+int gemm_smem_bytes(int block_n);
+
+}  // namespace tdb

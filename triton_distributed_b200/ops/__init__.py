@@ -1,0 +1,15 @@
+"""Overlapped ops, collectives and single-GPU kernels (the reference's ``triton_dist.kernels.nvidia``)."""
+from .gemm import gemm, linear, gemm_reference  # noqa: F401
+from .ag_gemm import (AllGatherGEMMTensorParallelContext, create_ag_gemm_context, ag_gemm,  # noqa: F401
+                      ag_gemm_reference)
+from .gemm_rs import (GEMMReduceScatterTensorParallelContext, create_gemm_rs_context, gemm_rs,  # noqa: F401
+                      gemm_rs_reference)
+from .allreduce import (AllReduceMethod, AllReduceContext, create_allreduce_ctx, all_reduce,  # noqa: F401
+                        get_auto_allreduce_method)
+from .reduce_scatter import (ReduceScatter2DContext, create_reduce_scater_2d_ctx, create_reduce_scatter_2d_ctx,  # noqa: F401
+                             reduce_scatter_2d_op, ring_reduce)
+from .allgather import (AllGatherMethod, get_auto_all_gather_method, FastAllGatherContext,  # noqa: F401
+                        create_fast_allgather_context, fast_allgather, all_gather_ll, all_gather,
+                        cp_engine_producer_all_gather_intra_node)
+from .elementwise import (rmsnorm, silu_mul, residual_add, qk_norm_rope_kv, embedding, argmax, sample_token,  # noqa: F401
+                          abs_sum)

@@ -1,0 +1,139 @@
+"""AllGather -> GEMM in one kernel launch (``ag_gemm``).
+
+API of the reference: ``create_ag_gemm_context`` / ``ag_gemm``
+(python/triton_dist/kernels/nvidia/allgather_gemm.py:489, :534).  Inputs: ``a`` [M/W, K] (rows sharded over the
+ranks), ``b`` [N/W, K] (column-parallel weight, K-major); output [M, N/W].
+
+GPU path: ``csrc/gemm_sm100.cu`` in all-gather mode - comm CTAs of the launch push the local shard into
+every rank's workspace through NVLS ``multimem.st`` (or peer stores) and set per-chunk epoch flags; the
+tcgen05 GEMM CTAs wait for exactly the chunk a tile needs and compute the local shard first.
+CPU / reference path: ``all_gather_into_tensor`` + ``matmul`` (what the reference's ``torch_ag_gemm`` does,
+layers/nvidia/tp_mlp.py:231-242).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _native
+from ..runtime import Runtime, get_runtime
+from .common import new_ctx_dev, ref_all_gather, sm_count
+
+BLOCK_M = 128
+
+
+@dataclass
+class AllGatherGEMMTensorParallelContext:
+    rt: Runtime
+    rank: int
+    num_ranks: int
+    max_M: int                 # global rows the workspace can hold
+    K: int
+    dtype: torch.dtype
+    BLOCK_N: int = 256
+    n_comm_ctas: int = 0       # 0 = automatic
+    num_ctas: int = 0
+    use_multimem: bool = True
+    for_correctness: bool = False
+    workspace: Optional[torch.Tensor] = None   # heap [2][max_M][K]
+    flags: Optional[torch.Tensor] = None       # heap [2][W][max_chunks]
+    ctx_dev: Optional[torch.Tensor] = None
+    max_chunks: int = 0
+    calls: int = 0
+
+    @property
+    def max_seg_rows(self) -> int:
+        return self.max_M // self.num_ranks
+
+    def finalize(self):
+        if self.workspace is not None:
+            self.rt.symm_free(self.workspace)
+            self.rt.symm_free(self.flags)
+            self.workspace = None
+            self.flags = None
+
+
+def create_ag_gemm_context(tensor_A: Optional[torch.Tensor] = None, tensor_B: Optional[torch.Tensor] = None,
+                           rank: Optional[int] = None, num_ranks: Optional[int] = None, max_M: Optional[int] = None,
+                           num_local_ranks: int = 8, BLOCK_M: int = 128, BLOCK_N: int = 256, BLOCK_K: int = 64,
+                           stages: int = 3, ag_intranode_stream=None, ag_internode_stream=None,
+                           for_correctness: bool = False, K: Optional[int] = None, dtype: Optional[torch.dtype] = None,
+                           n_comm_ctas: int = 0, use_multimem: bool = True) -> AllGatherGEMMTensorParallelContext:
+    """Allocate the symmetric workspace and flags (collective call: every rank, same arguments).
+
+    ``max_M`` is the gathered row count (``world * rows_per_rank``).  Stream / tile arguments of the
+    reference signature are accepted and ignored: the all-gather runs inside the GEMM launch and the tile
+    shape is fixed by the tcgen05 kernel (128 x BLOCK_N x 64).
+    """
+    rt = get_runtime()
+    rank = rt.rank if rank is None else rank
+    num_ranks = rt.world_size if num_ranks is None else num_ranks
+    if tensor_A is not None:
+        K = tensor_A.shape[-1] if K is None else K
+        dtype = tensor_A.dtype if dtype is None else dtype
+        if max_M is None:
+            max_M = tensor_A.shape[0] * num_ranks
+    if K is None or max_M is None:
+        raise ValueError("create_ag_gemm_context needs tensor_A or (max_M, K)")
+    dtype = dtype or torch.bfloat16
+    max_M = (max_M + num_ranks - 1) // num_ranks * num_ranks
+    ctx = AllGatherGEMMTensorParallelContext(rt=rt, rank=rank, num_ranks=num_ranks, max_M=max_M, K=K, dtype=dtype,
+                                             BLOCK_N=BLOCK_N if BLOCK_N in (128, 256) else 256,
+                                             n_comm_ctas=n_comm_ctas, use_multimem=use_multimem,
+                                             for_correctness=for_correctness)
+    if rt.is_cuda and num_ranks > 1:
+        ctx.max_chunks = (ctx.max_seg_rows + BLOCK_M - 1) // BLOCK_M
+        ctx.workspace = rt.symm_tensor((2, max_M, K), dtype, zero=False)
+        ctx.flags = rt.symm_tensor((2, num_ranks, ctx.max_chunks), torch.int32)
+        ctx.ctx_dev = new_ctx_dev(rt)
+        torch.cuda.synchronize()
+        rt.host_barrier()
+    return ctx
+
+
+def ag_gemm_reference(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Tensor:
+    """all_gather(a) @ b^T with torch.distributed + torch.matmul."""
+    return torch.matmul(ref_all_gather(a, group), b.t())
+
+
+def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelContext, persistent: bool = True,
+            autotune: bool = False, straggler_option: Optional[Tuple[int, float]] = None,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a`` [M/W, K], ``b`` [N_local, K] -> [M, N_local].
+
+    ``straggler_option=(rank, seconds)`` delays that rank on the host before the launch (a test aid; the
+    reference delays inside the kernel, allgather_gemm.py:602).
+    """
+    rt = ctx.rt
+    if straggler_option is not None and straggler_option[0] == ctx.rank:
+        time.sleep(float(straggler_option[1]))
+    if not _native.use_native(a, b) or a.dtype != torch.bfloat16:
+        res = ag_gemm_reference(a, b, rt.group)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    lib = _native.load(True)
+    W = ctx.num_ranks
+    if W == 1:
+        from .gemm import gemm
+        return gemm(a, b, out=out)
+    a = a.contiguous()
+    if b.stride(-1) != 1:
+        b = b.contiguous()
+    m, K = a.shape
+    N = b.shape[0]
+    if K != ctx.K:
+        raise ValueError(f"ag_gemm: K={K} differs from the context's K={ctx.K}")
+    if out is None:
+        out = torch.empty((m * W, N), dtype=a.dtype, device=a.device)
+    n_sms = ctx.num_ctas or sm_count(a.device)
+    n_comm = ctx.n_comm_ctas or (8 if (rt.has_multicast and ctx.use_multimem) else 16)
+    n_comm = max(1, min(n_comm, n_sms - 1))
+    lib.ag_gemm_bf16(rt.heap, a, b, out, ctx.workspace, ctx.flags, ctx.ctx_dev, ctx.max_seg_rows, ctx.max_chunks,
+                     n_comm, ctx.BLOCK_N, n_sms, bool(ctx.use_multimem and rt.has_multicast), rt.config.wait_timeout_s)
+    ctx.calls += 1
+    return out

@@ -1,0 +1,43 @@
+"""Single-GPU tcgen05 GEMM: ``C[M,N] = A[M,K] @ B[N,K]^T`` (bf16 in, fp32 accumulate, bf16 out).
+
+B is stored K-major ("weight layout", the same convention the reference uses for its TP layers,
+python/triton_dist/kernels/nvidia/allgather_gemm.py:656 ``gemm_persistent``).  On CPU tensors the
+torch reference is used.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _native
+
+
+def gemm_reference(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """fp32 reference: A @ B^T."""
+    return (a.float() @ b.float().t()).to(a.dtype)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, block_n: int = 0,
+         num_ctas: int = 0) -> torch.Tensor:
+    """``a`` [M,K] x ``b`` [N,K] -> [M,N].  bf16 CUDA tensors run the sm_100a kernel."""
+    if _native.use_native(a, b) and a.dtype == torch.bfloat16:
+        lib = _native.load(True)
+        if a.stride(-1) != 1:
+            a = a.contiguous()
+        if b.stride(-1) != 1:
+            b = b.contiguous()
+        lead = a.shape[:-1]
+        a2 = a.reshape(-1, a.shape[-1])
+        if out is None:
+            out = torch.empty((a2.shape[0], b.shape[0]), dtype=a.dtype, device=a.device)
+        lib.gemm_bf16(a2, b, out.view(a2.shape[0], b.shape[0]), block_n, num_ctas)
+        return out.view(*lead, b.shape[0])
+    res = torch.matmul(a, b.t())
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+linear = gemm
