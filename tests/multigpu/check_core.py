@@ -1,0 +1,188 @@
+"""Multi-GPU checks (torchrun, one rank per GPU): heap + device API, collectives, fused AG-GEMM / GEMM-RS.
+
+Every check compares against torch.distributed (NCCL) + torch fp32 math on the same data.  Exits non-zero on the
+first failing rank.  Optional args: --quick (small sizes only), --nvls 0|1.
+"""
+import argparse
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+import triton_distributed_b200 as tdb  # noqa: E402
+from triton_distributed_b200 import _native, ops  # noqa: E402
+
+
+def log(rt, *a):
+    if rt.rank == 0:
+        print(*a, flush=True)
+
+
+def check_primitives(rt):
+    lib = _native.load(True)
+    W, n = rt.world_size, 300
+    data = rt.symm_tensor((W * n,), torch.int32)
+    scratch = rt.symm_tensor((2 * n,), torch.int32)
+    sig = rt.symm_tensor((32,), torch.int32)
+    bar = rt.symm_tensor((16,), torch.int32)
+    torch.cuda.synchronize()
+    rt.host_barrier()
+    for epoch in (1, 2, 3):
+        lib.primitives_test(rt.heap, data, scratch, sig, bar, n, epoch, 5.0)
+        torch.cuda.synchronize()
+        rt.check_status()
+        prev = (rt.rank + W - 1) % W
+        pp = (prev + W - 1) % W
+        ar = torch.arange(n, device="cuda", dtype=torch.int32)
+        assert torch.equal(data[prev * n:(prev + 1) * n], ar + (prev + 1) * 1000), "putmem_signal_block"
+        assert torch.equal(scratch[:n], ar + (pp + 1) * 1000), "getmem_warp"
+        assert sig[0].item() == epoch
+        for r in range(W):
+            assert sig[8 + r].item() == epoch * 100 + r, "thread put"
+    # peer views and the multicast view
+    t = rt.symm_tensor((16,), torch.float32)
+    t.fill_(float(rt.rank + 1))
+    torch.cuda.synchronize()
+    rt.barrier_all_on_stream()
+    torch.cuda.synchronize()
+    for r in range(W):
+        assert rt.peer_view(t, r)[0].item() == float(r + 1), "peer view"
+    rt.barrier_all_on_stream()
+    torch.cuda.synchronize()
+    log(rt, f"OK primitives (heap mode {rt.heap.mode}, multicast {rt.has_multicast})")
+
+
+def check_allreduce(rt, quick):
+    W = rt.world_size
+    ctx = ops.create_allreduce_ctx(64 << 20)
+    methods = [ops.AllReduceMethod.OneShot, ops.AllReduceMethod.TwoShot]
+    if rt.has_multicast:
+        methods += [ops.AllReduceMethod.OneShot_Multimem, ops.AllReduceMethod.TwoShot_Multimem]
+    sizes = [8, 1000, 8192, 65536 + 8, 1 << 20] + ([] if quick else [4 << 20, (16 << 20) + 24])
+    for dtype in (torch.bfloat16, torch.float32, torch.float16):
+        for n in sizes:
+            x = (torch.randn(n, device="cuda") * 0.01 * (rt.rank + 1)).to(dtype)
+            ref = x.clone()
+            dist.all_reduce(ref, group=rt.group)
+            for m in methods:
+                if n * x.element_size() > (4 << 20) and m == ops.AllReduceMethod.OneShot:
+                    continue
+                out = ops.all_reduce(x, method=m, ctx=ctx)
+                torch.cuda.synchronize()
+                rt.check_status()
+                tol = 2e-2 if dtype != torch.float32 else 1e-4
+                err = (out.float() - ref.float()).abs().max().item()
+                assert err <= tol * max(1.0, ref.float().abs().max().item()), f"all_reduce {m} {dtype} n={n}: err {err}"
+    # back-to-back calls without host sync (buffer parity / epoch logic), plus auto method
+    x = torch.randn(4096, device="cuda", dtype=torch.bfloat16)
+    outs = [ops.all_reduce(x * (i + 1), ctx=ctx) for i in range(8)]
+    ref = x.clone().float()
+    dist.all_reduce(ref, group=rt.group)
+    torch.cuda.synchronize()
+    for i, o in enumerate(outs):
+        assert (o.float() - ref * (i + 1)).abs().max().item() < 0.05 * (i + 1) * W, "back-to-back all_reduce"
+    log(rt, "OK all_reduce", [m.name for m in methods])
+
+
+def check_rs_ag(rt):
+    W = rt.world_size
+    M, N = 64 * W, 512
+    ctx = ops.create_reduce_scater_2d_ctx(M, N, dtype=torch.bfloat16)
+    for use_nvls in ([True, False] if rt.has_multicast else [False]):
+        ctx.use_nvls = use_nvls
+        x = (torch.randn(M, N, device="cuda") * 0.1 * (rt.rank + 1)).to(torch.bfloat16)
+        out = ops.reduce_scatter_2d_op(x, ctx)
+        ref = torch.empty(M // W, N, device="cuda", dtype=torch.bfloat16)
+        dist.reduce_scatter_tensor(ref, x, group=rt.group)
+        torch.cuda.synchronize()
+        rt.check_status()
+        assert (out.float() - ref.float()).abs().max().item() < 0.05 * W, f"reduce_scatter nvls={use_nvls}"
+    agc = ops.create_fast_allgather_context()
+    for mode in [ops.AllGatherMethod.All2All_IntraNode, ops.AllGatherMethod.All2All_Pull] + (
+            [ops.AllGatherMethod.NVLS] if rt.has_multicast else []):
+        for n in (16, 4096, 1 << 18):
+            buf = rt.symm_tensor((W, n), torch.float32)
+            mine = torch.randn(n, device="cuda")
+            buf[rt.rank].copy_(mine)
+            ref = torch.empty(W, n, device="cuda")
+            dist.all_gather_into_tensor(ref, mine, group=rt.group)
+            ops.fast_allgather(buf, agc, mode)
+            torch.cuda.synchronize()
+            rt.check_status()
+            assert torch.equal(buf, ref), f"fast_allgather {mode} n={n}"
+            rt.host_barrier()
+            rt.symm_free(buf)
+    for n in (2, 64, 4096):
+        x = torch.randn(n, device="cuda")
+        ref = torch.empty(W, n, device="cuda")
+        dist.all_gather_into_tensor(ref, x, group=rt.group)
+        for _ in range(3):
+            out = ops.all_gather_ll(x, agc)
+        torch.cuda.synchronize()
+        rt.check_status()
+        assert torch.equal(out, ref), f"all_gather_ll n={n}"
+    log(rt, "OK reduce_scatter / all_gather")
+
+
+def check_fused_gemms(rt, quick):
+    W = rt.world_size
+    shapes = [(128, 256, 256), (300, 520, 264), (1024, 1024, 512)] + ([] if quick else [(1024, 3584, 8192)])
+    for (m, N, K) in shapes:   # m = rows per rank
+        for use_mc in ([True, False] if rt.has_multicast else [False]):
+            ctx = ops.create_ag_gemm_context(max_M=m * W, K=K, dtype=torch.bfloat16, use_multimem=use_mc)
+            for it in range(3):
+                a = (torch.randn(m, K, device="cuda") * (0.5 + 0.1 * rt.rank)).to(torch.bfloat16)
+                b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+                strag = (it % W, 0.02) if it == 1 else None
+                out = ops.ag_gemm(a, b, ctx, straggler_option=strag)
+                full = torch.empty(m * W, K, device="cuda", dtype=torch.bfloat16)
+                dist.all_gather_into_tensor(full, a, group=rt.group)
+                ref = full.float() @ b.float().t()
+                torch.cuda.synchronize()
+                rt.check_status()
+                err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+                assert err < 2e-2, f"ag_gemm m={m} N={N} K={K} mc={use_mc} it={it}: rel err {err}"
+            ctx.finalize()
+    for (m, N, K) in shapes:   # m = rows per rank of the output
+        ctx = ops.create_gemm_rs_context(max_M=m * W, N=N)
+        for it in range(3):
+            a = (torch.randn(m * W, K, device="cuda") * 0.1 * (rt.rank + 1)).to(torch.bfloat16)
+            b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+            out = ops.gemm_rs(a, b, ctx)
+            part = a.float() @ b.float().t()
+            dist.all_reduce(part, group=rt.group)
+            ref = part[rt.rank * m:(rt.rank + 1) * m]
+            torch.cuda.synchronize()
+            rt.check_status()
+            err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+            assert err < 3e-2, f"gemm_rs m={m} N={N} K={K} it={it}: rel err {err}"
+        ctx.finalize()
+    log(rt, "OK ag_gemm / gemm_rs")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--only", default="")
+    args = ap.parse_args()
+    tdb.initialize_distributed(seed=42)
+    rt = tdb.get_runtime()
+    t0 = time.time()
+    checks = {"primitives": lambda: check_primitives(rt), "allreduce": lambda: check_allreduce(rt, args.quick),
+              "rs_ag": lambda: check_rs_ag(rt), "fused": lambda: check_fused_gemms(rt, args.quick)}
+    for name, fn in checks.items():
+        if args.only and name not in args.only.split(","):
+            continue
+        fn()
+        torch.cuda.synchronize()
+        rt.host_barrier()
+    log(rt, f"ALL OK in {time.time() - t0:.1f}s")
+    tdb.finalize_distributed()
+
+
+if __name__ == "__main__":
+    main()

@@ -50,7 +50,12 @@ at::Tensor heap_tensor(SymmHeap& h, uint64_t offset, std::vector<int64_t> sizes,
   int dev = 0;
   check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
   auto opts = at::TensorOptions().dtype(dtype).device(at::kCUDA, dev);
-  return at::from_blob(reinterpret_cast<void*>(base + offset), sizes, [](void*) {}, opts);
+  // target_device: a peer / multicast mapping is physically remote, but this process addresses it from `dev`
+  return at::for_blob(reinterpret_cast<void*>(base + offset), sizes)
+      .options(opts)
+      .target_device(at::Device(at::kCUDA, dev))
+      .deleter([](void*) {})
+      .make_tensor();
 }
 
 uint64_t heap_offset_of(SymmHeap& h, const at::Tensor& t) {
