@@ -43,6 +43,7 @@ def check_primitives(rt):
         assert sig[0].item() == epoch
         for r in range(W):
             assert sig[8 + r].item() == epoch * 100 + r, "thread put"
+        rt.host_barrier()   # a faster peer must not start the next epoch's puts while this rank still checks
     # peer views and the multicast view
     t = rt.symm_tensor((16,), torch.float32)
     t.fill_(float(rt.rank + 1))
