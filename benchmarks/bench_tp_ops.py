@@ -1,0 +1,113 @@
+"""Per-op timing of the fused tensor-parallel GEMMs against their NCCL + cuBLAS baselines (torchrun, any N).
+
+  torchrun --nproc-per-node N benchmarks/bench_tp_ops.py [--M 8192 --K 8192 --N 28672] [--iters 20]
+
+Device-timed with CUDA events, L2 flushed between iterations, max over ranks.  Prints one JSON line per op.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import triton_distributed_b200 as tdb  # noqa: E402
+from triton_distributed_b200 import ops  # noqa: E402
+from triton_distributed_b200.utils import L2Flusher, fused_roofline  # noqa: E402
+
+
+def timed(fn, iters, warmup, fl, rt):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        fl.flush()
+        if rt.world_size > 1:
+            dist.barrier(group=rt.group)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    t = torch.tensor(ts, device="cuda", dtype=torch.float64)
+    if rt.world_size > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=rt.group)
+    return statistics.median(t.tolist())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--M", type=int, default=8192)
+    ap.add_argument("--K", type=int, default=8192)
+    ap.add_argument("--N", type=int, default=28672)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--n-comm", default="8")
+    ap.add_argument("--multimem", type=int, default=0)
+    args = ap.parse_args()
+    tdb.initialize_distributed(seed=0)
+    rt = tdb.get_runtime()
+    W, dev = rt.world_size, rt.device
+    M, K, N = args.M, args.K, args.N
+    m, n = M // W, N // W
+    fl = L2Flusher(dev)
+    a = torch.randn(m, K, device=dev, dtype=torch.bfloat16)
+    w1 = (torch.randn(n, K, device=dev) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(K, n, device=dev) * 0.02).to(torch.bfloat16)
+    h = torch.empty(M, n, device=dev, dtype=torch.bfloat16)
+    o = torch.empty(m, K, device=dev, dtype=torch.bfloat16)
+    full = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+    part = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+    w1t, w2t = w1.t(), w2.t()
+    flops = 2.0 * M * K * n
+    link_bytes = (W - 1) / W * M * K * 2
+
+    def emit(name, ms, extra=None):
+        if rt.rank == 0:
+            rec = {"op": name, "world": W, "M": M, "K": K, "N": N, "ms": ms}
+            rec.update(fused_roofline(flops, link_bytes if W > 1 else 0.0, ms))
+            if extra:
+                rec.update(extra)
+            print(json.dumps(rec), flush=True)
+
+    # baselines
+    def t_ag_gemm():
+        if W > 1:
+            dist.all_gather_into_tensor(full, a, group=rt.group)
+            torch.matmul(full, w1t, out=h)
+        else:
+            torch.matmul(a, w1t, out=h)
+
+    def t_gemm_rs():
+        if W > 1:
+            torch.matmul(h, w2t, out=part)
+            dist.reduce_scatter_tensor(o, part, group=rt.group)
+        else:
+            torch.matmul(h, w2t, out=o)
+
+    emit("torch_ag_gemm", timed(t_ag_gemm, args.iters, args.warmup, fl, rt))
+    emit("torch_gemm_rs", timed(t_gemm_rs, args.iters, args.warmup, fl, rt))
+    emit("torch_gemm_only_ag_shape", timed(lambda: torch.matmul(full, w1t, out=h), args.iters, args.warmup, fl, rt))
+    emit("own_gemm_only_ag_shape", timed(lambda: ops.gemm(full, w1, out=h), args.iters, args.warmup, fl, rt))
+    emit("own_gemm_only_rs_shape", timed(lambda: ops.gemm(h, w2, out=part), args.iters, args.warmup, fl, rt))
+    for nc in [int(v) for v in args.n_comm.split(",")]:
+        ag_ctx = ops.create_ag_gemm_context(max_M=M, K=K, dtype=torch.bfloat16, n_comm_ctas=nc,
+                                            use_multimem=bool(args.multimem))
+        emit("own_ag_gemm", timed(lambda: ops.ag_gemm(a, w1, ag_ctx, out=h), args.iters, args.warmup, fl, rt),
+             {"n_comm": nc, "multimem": args.multimem})
+        rt.check_status()
+        ag_ctx.finalize()
+    rs_ctx = ops.create_gemm_rs_context(max_M=M, N=K)
+    emit("own_gemm_rs", timed(lambda: ops.gemm_rs(h, w2, rs_ctx, out=o), args.iters, args.warmup, fl, rt))
+    rt.check_status()
+    tdb.finalize_distributed()
+
+
+if __name__ == "__main__":
+    main()

@@ -124,6 +124,10 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int bloc
   g.block_n = pick_block_n(N, block_n);
   g.tmap_a = make_tmap3(a.data_ptr(), tdb::kBF16, 1, M, K, a.stride(0) * 2, a.stride(0) * 2 * M, 128, 64);
   g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, g.block_n, 64);
+  if (c.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15u) == 0) {
+    g.tmap_c = make_tmap3(c.data_ptr(), tdb::kBF16, 1, M, N, c.stride(0) * 2, c.stride(0) * 2 * M, 128, 64);
+    g.use_tma_store = 1;
+  }
   const int tiles = ((M + 127) / 128) * ((N + g.block_n - 1) / g.block_n);
   g.num_ctas = std::min<int>(num_ctas > 0 ? num_ctas : sm_count(), tiles);
   g.symm.world = 1;
@@ -155,6 +159,10 @@ void ag_gemm_bf16(SymmHeap& h, const at::Tensor& a_local, const at::Tensor& b, a
   g.block_n = pick_block_n(N, block_n);
   g.tmap_a = make_tmap3(ws.data_ptr(), tdb::kBF16, 2, M, K, K * 2, buf_elems * 2, 128, 64);
   g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, g.block_n, 64);
+  if (c.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15u) == 0) {
+    g.tmap_c = make_tmap3(c.data_ptr(), tdb::kBF16, W, m, N, c.stride(0) * 2, c.stride(0) * 2 * m, 128, 64);
+    g.use_tma_store = 1;
+  }
   g.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
   g.seg_rows = m;
   g.max_seg_rows = max_seg_rows;
@@ -194,6 +202,15 @@ void gemm_rs_bf16(SymmHeap& h, const at::Tensor& a, const at::Tensor& b, at::Ten
   g.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
   g.seg_rows = m;
   g.max_seg_rows = max_seg_rows;
+  {
+    // one store map per owner rank over that rank's slots (peer-mapped addresses of the same heap offset)
+    const uint64_t off = heap_offset_of(h, slots);
+    for (int r = 0; r < W; ++r) {
+      g.tmap_peer_c[r] = make_tmap3(reinterpret_cast<void*>(h.peer_base(r) + off), tdb::kBF16, 2 * W, m, N, N * 2,
+                                    static_cast<uint64_t>(max_seg_rows) * N * 2, 128, 64);
+    }
+    g.use_tma_store = 1;
+  }
   g.rs_slots = slots.data_ptr();
   g.rs_flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
   g.max_tiles = max_tiles;

@@ -1,0 +1,133 @@
+// Python bindings of the attention kernels.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "tdb/attn.h"
+#include "tdb/symm_heap.h"
+
+namespace py = pybind11;
+using tdb::SymmHeap;
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+void check_cuda(cudaError_t e, const char* what) { TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e)); }
+
+tdb::AttnKV make_kv(const at::Tensor& k_cache, const at::Tensor& v_cache, const at::Tensor& block_table) {
+  TORCH_CHECK(k_cache.dim() == 4 && v_cache.dim() == 4, "KV cache must be [pages, page_size, Hkv, D]");
+  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous(), "KV cache must be contiguous");
+  TORCH_CHECK(k_cache.scalar_type() == at::kBFloat16 && v_cache.scalar_type() == at::kBFloat16, "bf16 KV cache expected");
+  TORCH_CHECK(block_table.scalar_type() == at::kInt && block_table.dim() == 2 && block_table.is_contiguous(),
+              "block_table must be contiguous int32 [B, max_pages]");
+  tdb::AttnKV kv;
+  kv.k_cache = k_cache.data_ptr();
+  kv.v_cache = v_cache.data_ptr();
+  kv.block_table = block_table.data_ptr<int32_t>();
+  kv.max_pages = block_table.size(1);
+  kv.page_size = k_cache.size(1);
+  kv.num_kv_heads = k_cache.size(2);
+  return kv;
+}
+
+void check_i32(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), name, ": contiguous int32 CUDA tensor expected");
+}
+
+at::Tensor flash_fwd(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
+                     const at::Tensor& block_table, const at::Tensor& cu_seqlens_q, const at::Tensor& kv_lens,
+                     c10::optional<at::Tensor> q_pos0, int64_t max_q_len, bool causal, double scale, double softcap,
+                     c10::optional<at::Tensor> lse) {
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && q.scalar_type() == at::kBFloat16, "q must be contiguous bf16 [T, Hq, D]");
+  check_i32(cu_seqlens_q, "cu_seqlens_q");
+  check_i32(kv_lens, "kv_lens");
+  c10::cuda::CUDAGuard guard(q.device());
+  tdb::FlashFwdArgs a;
+  at::Tensor out = at::empty_like(q);
+  a.q = q.data_ptr();
+  a.out = out.data_ptr();
+  a.lse = nullptr;
+  if (lse.has_value()) {
+    TORCH_CHECK(lse->scalar_type() == at::kFloat && lse->is_contiguous() && lse->numel() == q.size(0) * q.size(1),
+                "lse must be contiguous fp32 [Hq, T]");
+    a.lse = lse->data_ptr<float>();
+  }
+  a.cu_seqlens_q = cu_seqlens_q.data_ptr<int32_t>();
+  a.q_pos0 = nullptr;
+  if (q_pos0.has_value()) {
+    check_i32(*q_pos0, "q_pos0");
+    a.q_pos0 = q_pos0->data_ptr<int32_t>();
+  }
+  a.kv_lens = kv_lens.data_ptr<int32_t>();
+  a.kv = make_kv(k_cache, v_cache, block_table);
+  a.batch = kv_lens.numel();
+  a.max_q_len = max_q_len;
+  a.num_q_heads = q.size(1);
+  a.head_dim = q.size(2);
+  a.total_q = q.size(0);
+  a.causal = causal ? 1 : 0;
+  a.scale = scale;
+  a.softcap = softcap;
+  TORCH_CHECK(k_cache.size(3) == a.head_dim, "head_dim mismatch between q and the cache");
+  check_cuda(tdb::launch_flash_fwd(a, cur_stream()), "launch_flash_fwd");
+  return out;
+}
+
+tdb::DecodeArgs decode_args(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
+                            const at::Tensor& block_table, const at::Tensor& kv_lens, at::Tensor& workspace,
+                            int64_t splits, double scale, double softcap) {
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && q.scalar_type() == at::kBFloat16, "q must be contiguous bf16 [B, Hq, D]");
+  check_i32(kv_lens, "kv_lens");
+  TORCH_CHECK(workspace.scalar_type() == at::kFloat && workspace.is_contiguous(), "workspace must be fp32");
+  tdb::DecodeArgs a;
+  a.q = q.data_ptr();
+  a.workspace = workspace.data_ptr<float>();
+  a.kv_lens = kv_lens.data_ptr<int32_t>();
+  a.kv = make_kv(k_cache, v_cache, block_table);
+  a.batch = q.size(0);
+  a.num_q_heads = q.size(1);
+  a.head_dim = q.size(2);
+  a.splits = splits;
+  a.scale = scale;
+  a.softcap = softcap;
+  TORCH_CHECK(k_cache.size(3) == a.head_dim, "head_dim mismatch between q and the cache");
+  TORCH_CHECK(workspace.numel() >= tdb::decode_workspace_floats(a.batch, a.num_q_heads, a.head_dim, a.splits),
+              "decode workspace too small");
+  return a;
+}
+
+// Split-KV decode + local combine.  Any of out / out_lse / out_f32 may be None.
+void decode_attn(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, const at::Tensor& block_table,
+                 const at::Tensor& kv_lens, at::Tensor& workspace, int64_t splits, double scale, double softcap,
+                 c10::optional<at::Tensor> out, c10::optional<at::Tensor> out_lse, c10::optional<at::Tensor> out_f32) {
+  c10::cuda::CUDAGuard guard(q.device());
+  tdb::DecodeArgs a = decode_args(q, k_cache, v_cache, block_table, kv_lens, workspace, splits, scale, softcap);
+  check_cuda(tdb::launch_decode_splitkv(a, cur_stream()), "launch_decode_splitkv");
+  check_cuda(tdb::launch_decode_combine(a, out.has_value() ? out->data_ptr() : nullptr,
+                                        out_lse.has_value() ? out_lse->data_ptr<float>() : nullptr,
+                                        out_f32.has_value() ? out_f32->data_ptr<float>() : nullptr, cur_stream()),
+             "launch_decode_combine");
+}
+
+// Distributed flash-decode: local split-KV, then the fused combine + cross-rank exchange + LSE merge.
+void dist_decode_attn(SymmHeap& h, const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
+                      const at::Tensor& block_table, const at::Tensor& kv_lens, at::Tensor& workspace, int64_t splits,
+                      double scale, double softcap, at::Tensor& out, at::Tensor& staging, at::Tensor& ctx,
+                      double timeout_s) {
+  c10::cuda::CUDAGuard guard(q.device());
+  tdb::DecodeArgs a = decode_args(q, k_cache, v_cache, block_table, kv_lens, workspace, splits, scale, softcap);
+  check_cuda(tdb::launch_decode_splitkv(a, cur_stream()), "launch_decode_splitkv");
+  check_cuda(tdb::launch_dist_combine(a, out.data_ptr(), staging.data_ptr(), staging.numel() * staging.element_size() / 16,
+                                      reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr()),
+                                      h.info(static_cast<uint64_t>(timeout_s * 1e9)), cur_stream()),
+             "launch_dist_combine");
+}
+
+}  // namespace
+
+void bind_attn(py::module_& m) {
+  m.def("flash_fwd", &flash_fwd);
+  m.def("decode_attn", &decode_attn);
+  m.def("dist_decode_attn", &dist_decode_attn);
+  m.def("decode_workspace_floats", &tdb::decode_workspace_floats);
+}

@@ -219,7 +219,10 @@ void abs_sum(const at::Tensor& x, at::Tensor& out) {
 }  // namespace
 
 
+void bind_attn(py::module_& m);
+
 void bind_more(py::module_& m) {
+  bind_attn(m);
   m.def("all_reduce", &all_reduce);
   m.def("barrier_all", &barrier_all);
   m.def("all_gather", &all_gather);

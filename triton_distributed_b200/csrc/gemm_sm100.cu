@@ -3,20 +3,21 @@
 //
 //   plain           C[M,N] = A[M,K] * B[N,K]^T
 //   all-gather      A is sharded by rows over the ranks; "comm" CTAs of the same
-//                   launch push the local shard into every rank's workspace
-//                   (NVLS multimem.st, or plain peer stores) chunk by chunk and
-//                   set a per-chunk epoch flag; GEMM CTAs wait for exactly the
-//                   chunk a tile needs, then TMA-load it from LOCAL memory.
-//   reduce-scatter  every rank computes a partial C; the epilogue stores each
-//                   tile straight into the owner rank's slot over NVLink and
-//                   sets a per-tile epoch flag there; after its last tile every
-//                   CTA joins the owner-side reduction of the arrived slots.
+//                   launch push the local shard into every rank's workspace with
+//                   bulk-TMA copies (local memory -> shared memory -> peer memory,
+//                   nearest consumer first) or NVLS multimem.st, and set a
+//                   per-chunk epoch flag; GEMM CTAs wait for exactly the chunk a
+//                   tile needs, then TMA-load it from LOCAL memory.
+//   reduce-scatter  every rank computes a partial C; the epilogue TMA-stores each
+//                   tile straight into the owner rank's slot over NVLink and sets
+//                   a per-tile epoch flag there; after its last tile every CTA
+//                   joins the owner-side reduction of the arrived slots.
 //
 // Roles inside a CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer
-// (one elected lane) and TMEM owner, warps 2-5 = epilogue (TMEM -> registers ->
-// bf16 -> global / peer memory).  Accumulators are double-buffered in TMEM
-// (2 x BLOCK_N fp32 columns) so the epilogue of tile i overlaps the main loop of
-// tile i+1.
+// (one elected lane) and TMEM owner, warps 2-5 = epilogue: TMEM -> registers ->
+// bf16 -> swizzled shared-memory staging -> TMA store (local or peer memory).
+// Accumulators are double-buffered in TMEM (2 x BLOCK_N fp32 columns) so the
+// epilogue of tile i overlaps the main loop of tile i+1.
 //
 // Reference behaviour being matched (not its code):
 //   AG+GEMM   python/triton_dist/kernels/nvidia/allgather_gemm.py:159-264 (consumer GEMM waits per rank
@@ -41,6 +42,8 @@ constexpr int kBK = 64;           // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
 constexpr int kGroupM = 8;
+constexpr int kEpiCols = 64;      // columns per epilogue staging buffer (128-byte rows)
+constexpr int kEpiBytes = kBM * kEpiCols * 2;
 constexpr uint64_t kMbarTimeoutNs = 4000000000ull;  // 4 s
 
 template <int BN>
@@ -49,9 +52,19 @@ struct SmemLayout {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kEpiOffset = kStages * kStageBytes;          // 2 staging buffers, 1024-aligned
+  static constexpr int kBarOffset = kEpiOffset + 2 * kEpiBytes;
   // full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], tmem_base, abort
   static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 16;
+};
+
+// ring used by the comm CTAs of the all-gather mode (same dynamic shared memory)
+constexpr int kPushPiece = 32 * 1024;
+constexpr int kPushSlots = 6;
+constexpr int kPushAhead = 3;
+
+struct PeerMaps {
+  CUtensorMap m[kMaxRanks];
 };
 
 struct KParams {
@@ -65,6 +78,7 @@ struct KParams {
   int seg_first;     // first segment in this rank's tile order
   int seg_rows;
   int n_comm;
+  int tma_store;     // epilogue through shared memory + TMA store
   // all-gather
   const __nv_bfloat16* a_local;
   __nv_bfloat16* ag_ws;
@@ -106,8 +120,10 @@ __device__ __forceinline__ Tile decode_tile(const KParams& p, int t, int BN) {
   return r;
 }
 
-// Push this rank's shard into every rank's workspace (comm CTAs of the all-gather mode).
-__device__ void ag_push(const KParams& p, uint32_t epoch) {
+// ---------------------------------------------------------------------------
+// All-gather push, NVLS flavour: SM-issued multimem.st (one store reaches all ranks).
+// ---------------------------------------------------------------------------
+__device__ void ag_push_multimem(const KParams& p, uint32_t epoch) {
   const int buf = epoch & 1;
   const int W = p.symm.world, rank = p.symm.rank;
   const int chunks = (p.seg_rows + kBM - 1) / kBM;
@@ -116,56 +132,121 @@ __device__ void ag_push(const KParams& p, uint32_t epoch) {
   for (int c = blockIdx.x; c < chunks; c += p.n_comm) {
     const int r0 = c * kBM;
     const int rows = min(kBM, p.seg_rows - r0);
-    const uint64_t bytes = rows * row_bytes;
+    const uint64_t nvec = (rows * row_bytes) >> 4;
     const char* src = reinterpret_cast<const char*>(p.a_local) + r0 * row_bytes;
-    char* dst_local = ws_local + (static_cast<uint64_t>(rank) * p.seg_rows + r0) * row_bytes;
-    const uint64_t nvec = bytes >> 4;
-    if (p.use_mc) {
-      char* dst = mc_ptr(p.symm, dst_local);
-      uint64_t i = threadIdx.x;
-      for (; i + 3ull * kThreads < nvec; i += 4ull * kThreads) {
-        uint4 v0 = ld_nc_v4(src + (i << 4));
-        uint4 v1 = ld_nc_v4(src + ((i + kThreads) << 4));
-        uint4 v2 = ld_nc_v4(src + ((i + 2 * kThreads) << 4));
-        uint4 v3 = ld_nc_v4(src + ((i + 3 * kThreads) << 4));
-        multimem_st_v4(dst + (i << 4), v0);
-        multimem_st_v4(dst + ((i + kThreads) << 4), v1);
-        multimem_st_v4(dst + ((i + 2 * kThreads) << 4), v2);
-        multimem_st_v4(dst + ((i + 3 * kThreads) << 4), v3);
-      }
-      for (; i < nvec; i += kThreads) multimem_st_v4(dst + (i << 4), ld_nc_v4(src + (i << 4)));
-    } else {
-      char* dsts[kMaxRanks];
-#pragma unroll
-      for (int j = 0; j < kMaxRanks; ++j) dsts[j] = symm_at(p.symm, dst_local, j < W ? (rank + j) % W : rank);
-      uint64_t i = threadIdx.x;
-      for (; i + kThreads < nvec; i += 2ull * kThreads) {
-        uint4 v0 = ld_nc_v4(src + (i << 4));
-        uint4 v1 = ld_nc_v4(src + ((i + kThreads) << 4));
-#pragma unroll
-        for (int j = 0; j < kMaxRanks; ++j) {
-          if (j < W) {
-            st_v4(dsts[j] + (i << 4), v0);
-            st_v4(dsts[j] + ((i + kThreads) << 4), v1);
-          }
-        }
-      }
-      for (; i < nvec; i += kThreads) {
-        uint4 v0 = ld_nc_v4(src + (i << 4));
-#pragma unroll
-        for (int j = 0; j < kMaxRanks; ++j)
-          if (j < W) st_v4(dsts[j] + (i << 4), v0);
-      }
+    char* dst = mc_ptr(p.symm, ws_local + (static_cast<uint64_t>(rank) * p.seg_rows + r0) * row_bytes);
+    uint64_t i = threadIdx.x;
+    for (; i + 3ull * kThreads < nvec; i += 4ull * kThreads) {
+      uint4 v0 = ld_nc_v4(src + (i << 4));
+      uint4 v1 = ld_nc_v4(src + ((i + kThreads) << 4));
+      uint4 v2 = ld_nc_v4(src + ((i + 2 * kThreads) << 4));
+      uint4 v3 = ld_nc_v4(src + ((i + 3 * kThreads) << 4));
+      multimem_st_v4(dst + (i << 4), v0);
+      multimem_st_v4(dst + ((i + kThreads) << 4), v1);
+      multimem_st_v4(dst + ((i + 2 * kThreads) << 4), v2);
+      multimem_st_v4(dst + ((i + 3 * kThreads) << 4), v3);
     }
+    for (; i < nvec; i += kThreads) multimem_st_v4(dst + (i << 4), ld_nc_v4(src + (i << 4)));
     __syncthreads();
     if (threadIdx.x < W) {
-      // every lane orders the CTA's stores (made visible to it by the barrier)
-      // before its own flag store
+      // every lane orders the CTA's stores (made visible to it by the barrier) before its own flag store
       fence_acq_rel_sys();
       uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * W + rank) * p.max_chunks + c;
       st_release_sys(symm_at(p.symm, flag, (rank + threadIdx.x) % W), epoch);
     }
   }
+}
+
+// ---------------------------------------------------------------------------
+// All-gather push, bulk-TMA flavour: one thread drives a ring of shared-memory
+// slots: bulk load (local A -> smem), bulk store (smem -> the peer's workspace).
+// Destinations are visited nearest consumer first: rank r's shard is the d-th
+// segment rank (r - d) computes, so it goes to (r - 1), (r - 2), ... in turn and
+// every receiver takes in one source at full link rate at a time.
+// ---------------------------------------------------------------------------
+__device__ void ag_push_bulk(const KParams& p, uint32_t epoch, uint8_t* smem) {
+  if (threadIdx.x != 0) return;
+  const int buf = epoch & 1;
+  const int W = p.symm.world, rank = p.symm.rank;
+  const int chunks = (p.seg_rows + kBM - 1) / kBM;
+  const uint64_t row_bytes = static_cast<uint64_t>(p.K) * 2;
+  char* ws_local = reinterpret_cast<char*>(p.ag_ws + buf * p.ag_buf_elems);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPushSlots * kPushPiece);
+  for (int i = 0; i < kPushSlots; ++i) mbar_init(&bars[i], 1);
+  fence_mbar_init();
+
+  // work list of this CTA: for d in 0..W-1 (0 = own workspace), for its chunks, for the pieces of a chunk
+  const int my_chunks = chunks > static_cast<int>(blockIdx.x) ? (chunks - blockIdx.x + p.n_comm - 1) / p.n_comm : 0;
+  uint32_t ld_i = 0, st_i = 0;                 // pieces loaded / stored so far (global counters over the ring)
+  int ld_d = 0, ld_c = 0;
+  uint64_t ld_off = 0;                          // load cursor: (distance, chunk ordinal, byte offset in chunk)
+  int st_d = 0, st_c = 0;
+  uint64_t st_off = 0;                          // store cursor
+  bool ok = true;
+  auto chunk_bytes = [&](int ordinal) -> uint64_t {
+    const int c = blockIdx.x + ordinal * p.n_comm;
+    return static_cast<uint64_t>(min(kBM, p.seg_rows - c * kBM)) * row_bytes;
+  };
+  const uint64_t total_pieces = [&]() {
+    uint64_t n = 0;
+    for (int o = 0; o < my_chunks; ++o) n += (chunk_bytes(o) + kPushPiece - 1) / kPushPiece;
+    return n * W;
+  }();
+  for (uint64_t step = 0; step < total_pieces + kPushAhead && ok; ++step) {
+    if (step < total_pieces) {
+      // ---- issue the load of piece `ld_i`
+      const int slot = ld_i % kPushSlots;
+      // the store that last read this slot is at most (kPushSlots - kPushAhead - 1) groups behind the newest
+      bulk_wait_read<kPushSlots - kPushAhead - 1>();
+      const int c = blockIdx.x + ld_c * p.n_comm;
+      const uint64_t cb = chunk_bytes(ld_c);
+      const uint32_t bytes = static_cast<uint32_t>((cb - ld_off) < (uint64_t)kPushPiece ? (cb - ld_off) : (uint64_t)kPushPiece);
+      const char* src = reinterpret_cast<const char*>(p.a_local) + static_cast<uint64_t>(c) * kBM * row_bytes + ld_off;
+      mbar_arrive_expect_tx(&bars[slot], bytes);
+      bulk_load(smem + slot * kPushPiece, src, bytes, &bars[slot]);
+      ++ld_i;
+      ld_off += bytes;
+      if (ld_off >= cb) {
+        ld_off = 0;
+        if (++ld_c >= my_chunks) {
+          ld_c = 0;
+          ++ld_d;
+        }
+      }
+    }
+    if (step >= kPushAhead) {
+      // ---- store piece `st_i`
+      const int slot = st_i % kPushSlots;
+      if (!mbar_wait(&bars[slot], (st_i / kPushSlots) & 1, nullptr, kMbarTimeoutNs)) {
+        report(p.symm, kTimeoutMbarrier, kKernelAgGemm, 40, -1, slot, 0, static_cast<int>(st_i));
+        ok = false;
+        break;
+      }
+      const int c = blockIdx.x + st_c * p.n_comm;
+      const uint64_t cb = chunk_bytes(st_c);
+      const uint32_t bytes = static_cast<uint32_t>((cb - st_off) < (uint64_t)kPushPiece ? (cb - st_off) : (uint64_t)kPushPiece);
+      const int peer = (rank - st_d + W) % W;
+      char* dst_local = ws_local + (static_cast<uint64_t>(rank) * p.seg_rows + static_cast<uint64_t>(c) * kBM) * row_bytes + st_off;
+      bulk_store(symm_at(p.symm, dst_local, peer), smem + slot * kPushPiece, bytes);
+      bulk_commit();
+      ++st_i;
+      st_off += bytes;
+      if (st_off >= cb) {
+        // chunk complete on `peer`: wait for the writes, then raise its flag there
+        bulk_wait<0>();
+        fence_proxy_async();
+        fence_acq_rel_sys();
+        uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * W + rank) * p.max_chunks + c;
+        st_release_sys(symm_at(p.symm, flag, peer), epoch);
+        st_off = 0;
+        if (++st_c >= my_chunks) {
+          st_c = 0;
+          ++st_d;
+        }
+      }
+    }
+  }
+  bulk_wait<0>();
 }
 
 // Owner-side reduction of the reduce-scatter mode: out[rows of my segment] = sum over sources.
@@ -213,9 +294,12 @@ __device__ void rs_reduce(const KParams& p, uint32_t epoch, int BN) {
   }
 }
 
+TDB_DEVICE void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ PeerMaps peer_maps,
             const KParams p) {
   using L = SmemLayout<BN>;
   constexpr int kStages = L::kStages;
@@ -236,7 +320,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const bool is_comm = (p.mode == kGemmAllGather) && (static_cast<int>(blockIdx.x) < p.n_comm);
   if (is_comm) {
-    ag_push(p, epoch);
+    if (p.use_mc) {
+      ag_push_multimem(p, epoch);
+    } else {
+      ag_push_bulk(p, epoch, smem);
+    }
   } else {
     // ------------------------------------------------------------------ setup
     if (threadIdx.x == 0) {
@@ -252,6 +340,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       fence_mbar_init();
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_b);
+      if (p.tma_store && p.mode != kGemmReduceScatter) tma_prefetch_desc(&tmap_c);
     }
     if (warp == 1) {
       tmem_alloc(tmem_base_smem, 2 * BN);
@@ -348,6 +437,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     } else {
       // ------------------------------------------------------------ epilogue (warps 2..5)
       const int q = warp & 3;  // TMEM lane quarter this warp may access
+      const bool leader = (warp == 2 && lane == 0);
+      uint8_t* stage_base = smem + L::kEpiOffset;
+      const int row_in_tile = q * 32 + lane;
+      uint32_t chunk_ctr = 0;   // staging buffers alternate over all chunks of all tiles
       int local = 0;
       bool ok = true;
       for (int t = g_idx; t < num_tiles && ok; t += n_gemm, ++local) {
@@ -360,56 +453,114 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           break;
         }
         tc_fence_after_sync();
-        const int row = tl.m0 + q * 32 + lane;
-        const bool row_ok = row < tl.m_end;
-        __nv_bfloat16* dst_row;
-        if (p.mode == kGemmReduceScatter) {
-          __nv_bfloat16* slot = p.rs_slots + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.rs_slot_elems +
-                                static_cast<uint64_t>(row - tl.seg * p.seg_rows) * p.N;
-          dst_row = symm_at(p.symm, slot, tl.seg);
-        } else {
-          dst_row = p.c + static_cast<uint64_t>(row) * p.ldc;
-        }
-        const bool vec_ok = (p.mode == kGemmReduceScatter) ? (p.N % 8 == 0) : (p.ldc % 8 == 0);
+        const uint32_t t_acc = tmem_base + b * BN + (static_cast<uint32_t>(q * 32) << 16);
+        if (p.tma_store) {
+          const CUtensorMap* cmap = (p.mode == kGemmReduceScatter) ? &peer_maps.m[tl.seg] : &tmap_c;
+          const int c2 = (p.mode == kGemmReduceScatter) ? (buf * p.symm.world + p.symm.rank) : tl.seg;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + b * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
-          tmem_ld_wait();
-          const int col0 = tl.n0 + c * 32;
-          if (row_ok && col0 < p.N) {
-            if (vec_ok && col0 + 32 <= p.N) {
+          for (int c = 0; c < BN / kEpiCols; ++c, ++chunk_ctr) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(t_acc + c * kEpiCols, r0);
+            tmem_ld_32x32(t_acc + c * kEpiCols + 32, r1);
+            tmem_ld_wait();
+            if (c == BN / kEpiCols - 1) {
+              // whole accumulator is in registers / staged: hand the TMEM buffer back to the MMA warp
+              tc_fence_before_sync();
+              mbar_arrive(&tmem_empty[b]);
+            }
+            uint8_t* stg = stage_base + (chunk_ctr & 1) * kEpiBytes;
+            // the store that read this staging buffer two chunks ago must have drained it
+            if (leader) bulk_wait_read<1>();
+            epi_bar();
+            uint8_t* srow = stg + row_in_tile * 128;
+            const int sw = row_in_tile & 7;
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 o;
-                o.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-                o.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-                o.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-                o.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-                st_v4(dst_row + col0 + 8 * j, o);
-              }
-            } else {
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+              *reinterpret_cast<uint4*>(srow + ((j ^ sw) << 4)) = o;
+            }
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) dst_row[col0 + j] = __float2bfloat16(__uint_as_float(r[j]));
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+              *reinterpret_cast<uint4*>(srow + (((j + 4) ^ sw) << 4)) = o;
+            }
+            fence_proxy_async_smem();
+            epi_bar();
+            if (leader && tl.n0 + c * kEpiCols < p.N) {
+              tma_store_3d(cmap, stg, tl.n0 + c * kEpiCols, tl.mt * kBM, c2);
+              bulk_commit();
             }
           }
-        }
-        // accumulator buffer b may be overwritten by the MMA warp
-        tc_fence_before_sync();
-        mbar_arrive(&tmem_empty[b]);
-        if (p.mode == kGemmReduceScatter) {
-          // all 128 epilogue threads have issued their peer stores
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (warp == 2 && lane == 0) {
+          if (p.mode == kGemmReduceScatter && leader) {
+            // the tile's stores must have landed in the owner's memory before its flag does
+            bulk_wait<0>();
+            fence_proxy_async();
             fence_acq_rel_sys();
             uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.max_tiles +
                              tl.mt * p.tiles_n + tl.nt;
             st_release_sys(symm_at(p.symm, flag, tl.seg), epoch);
           }
+        } else {
+          // direct stores (any N / leading dimension)
+          const int row = tl.m0 + row_in_tile;
+          const bool row_ok = row < tl.m_end;
+          __nv_bfloat16* dst_row;
+          if (p.mode == kGemmReduceScatter) {
+            __nv_bfloat16* slot = p.rs_slots + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.rs_slot_elems +
+                                  static_cast<uint64_t>(row - tl.seg * p.seg_rows) * p.N;
+            dst_row = symm_at(p.symm, slot, tl.seg);
+          } else {
+            dst_row = p.c + static_cast<uint64_t>(row) * p.ldc;
+          }
+          const bool vec_ok = (p.mode == kGemmReduceScatter) ? (p.N % 8 == 0) : (p.ldc % 8 == 0);
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_acc + c * 32, r);
+            tmem_ld_wait();
+            const int col0 = tl.n0 + c * 32;
+            if (row_ok && col0 < p.N) {
+              if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  uint4 o;
+                  o.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                  o.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                  o.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                  o.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                  st_v4(dst_row + col0 + 8 * j, o);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) dst_row[col0 + j] = __float2bfloat16(__uint_as_float(r[j]));
+              }
+            }
+          }
+          tc_fence_before_sync();
+          mbar_arrive(&tmem_empty[b]);
+          if (p.mode == kGemmReduceScatter) {
+            epi_bar();
+            if (leader) {
+              fence_acq_rel_sys();
+              uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.max_tiles +
+                               tl.mt * p.tiles_n + tl.nt;
+              st_release_sys(symm_at(p.symm, flag, tl.seg), epoch);
+            }
+          }
         }
       }
       if (!ok) *abort_flag = 1;
+      // shared memory must stay valid until the last TMA store has read it, and the stores must be complete
+      if (leader) bulk_wait<0>();
     }
 
     // ------------------------------------------------------------ teardown
@@ -440,6 +591,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 template <int BN>
 cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
   using L = SmemLayout<BN>;
+  static_assert(kPushSlots * kPushPiece + kPushSlots * 8 <= L::kTotal, "push ring must fit the GEMM's shared memory");
   const int smem = L::kTotal + 1024;
   static bool attr_set = false;
   if (!attr_set) {
@@ -460,6 +612,7 @@ cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
   p.seg_first = a.mode == kGemmAllGather ? a.symm.rank
                : a.mode == kGemmReduceScatter ? (a.symm.rank + 1) % a.symm.world : 0;
   p.n_comm = a.mode == kGemmAllGather ? a.n_comm_ctas : 0;
+  p.tma_store = a.use_tma_store;
   p.a_local = reinterpret_cast<const __nv_bfloat16*>(a.a_local);
   p.ag_ws = reinterpret_cast<__nv_bfloat16*>(a.ag_ws);
   p.ag_buf_elems = static_cast<uint64_t>(a.symm.world) * a.max_seg_rows * static_cast<uint64_t>(a.K);
@@ -480,10 +633,13 @@ cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
   if (a.mode == kGemmAllGather && (a.n_comm_ctas < 1 || a.n_comm_ctas >= a.num_ctas)) return cudaErrorInvalidValue;
   if (a.K % 8 != 0) return cudaErrorInvalidValue;
 
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tc;
   memcpy(&ta, a.tmap_a.bytes, sizeof(CUtensorMap));
   memcpy(&tb, a.tmap_b.bytes, sizeof(CUtensorMap));
-  gemm_kernel<BN><<<a.num_ctas, kThreads, smem, stream>>>(ta, tb, p);
+  memcpy(&tc, a.tmap_c.bytes, sizeof(CUtensorMap));
+  PeerMaps pm;
+  memcpy(&pm, a.tmap_peer_c, sizeof(PeerMaps));
+  gemm_kernel<BN><<<a.num_ctas, kThreads, smem, stream>>>(ta, tb, tc, pm, p);
   return cudaGetLastError();
 }
 

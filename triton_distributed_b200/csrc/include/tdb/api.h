@@ -61,6 +61,11 @@ struct GemmArgs {
   // tensor maps: A tiles [128 x 64], B tiles [BN x 64], 128-byte swizzle
   TensorMap tmap_a;
   TensorMap tmap_b;
+  // output through shared memory + TMA store: C as [segments][rows per segment][N], box [128 x 64], 128-byte swizzle;
+  // reduce-scatter: one map per owner rank over its slots [2*world][rows per segment][N]
+  TensorMap tmap_c;
+  TensorMap tmap_peer_c[kMaxRanksHost];
+  int use_tma_store;
   int block_n;      // 128 or 256
   int num_ctas;     // grid size (<= SM count)
   // fused modes

@@ -125,6 +125,12 @@ TDB_DEVICE void tma_store_2d(const void* tmap, const void* smem_src, int32_t c0,
                "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
                : "memory");
 }
+TDB_DEVICE void tma_store_3d(const void* tmap, const void* smem_src, int32_t c0, int32_t c1, int32_t c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
 TDB_DEVICE void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }

@@ -13,3 +13,6 @@ from .allgather import (AllGatherMethod, get_auto_all_gather_method, FastAllGath
                         cp_engine_producer_all_gather_intra_node)
 from .elementwise import (rmsnorm, silu_mul, residual_add, qk_norm_rope_kv, embedding, argmax, sample_token,  # noqa: F401
                           abs_sum)
+from .attention import (flash_attn_varlen, gqa_fwd_batch_decode, gqa_fwd_batch_decode_intra_rank,  # noqa: F401
+                        gqa_fwd_batch_decode_persistent, attention_reference, merge_attention_partials,
+                        dense_block_table, decode_workspace, pick_kv_splits)

@@ -5,7 +5,7 @@ API of the reference: ``create_ag_gemm_context`` / ``ag_gemm``
 ranks), ``b`` [N/W, K] (column-parallel weight, K-major); output [M, N/W].
 
 GPU path: ``csrc/gemm_sm100.cu`` in all-gather mode - comm CTAs of the launch push the local shard into
-every rank's workspace through NVLS ``multimem.st`` (or peer stores) and set per-chunk epoch flags; the
+every rank's workspace with bulk-TMA copies (or NVLS ``multimem.st``) and set per-chunk epoch flags; the
 tcgen05 GEMM CTAs wait for exactly the chunk a tile needs and compute the local shard first.
 CPU / reference path: ``all_gather_into_tensor`` + ``matmul`` (what the reference's ``torch_ag_gemm`` does,
 layers/nvidia/tp_mlp.py:231-242).
@@ -36,7 +36,7 @@ class AllGatherGEMMTensorParallelContext:
     BLOCK_N: int = 256
     n_comm_ctas: int = 0       # 0 = automatic
     num_ctas: int = 0
-    use_multimem: bool = True
+    use_multimem: bool = False
     for_correctness: bool = False
     workspace: Optional[torch.Tensor] = None   # heap [2][max_M][K]
     flags: Optional[torch.Tensor] = None       # heap [2][W][max_chunks]
@@ -61,7 +61,7 @@ def create_ag_gemm_context(tensor_A: Optional[torch.Tensor] = None, tensor_B: Op
                            num_local_ranks: int = 8, BLOCK_M: int = 128, BLOCK_N: int = 256, BLOCK_K: int = 64,
                            stages: int = 3, ag_intranode_stream=None, ag_internode_stream=None,
                            for_correctness: bool = False, K: Optional[int] = None, dtype: Optional[torch.dtype] = None,
-                           n_comm_ctas: int = 0, use_multimem: bool = True) -> AllGatherGEMMTensorParallelContext:
+                           n_comm_ctas: int = 0, use_multimem: bool = False) -> AllGatherGEMMTensorParallelContext:
     """Allocate the symmetric workspace and flags (collective call: every rank, same arguments).
 
     ``max_M`` is the gathered row count (``world * rows_per_rank``).  Stream / tile arguments of the
@@ -131,7 +131,7 @@ def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelCo
     if out is None:
         out = torch.empty((m * W, N), dtype=a.dtype, device=a.device)
     n_sms = ctx.num_ctas or sm_count(a.device)
-    n_comm = ctx.n_comm_ctas or (8 if (rt.has_multicast and ctx.use_multimem) else 16)
+    n_comm = ctx.n_comm_ctas or 8
     n_comm = max(1, min(n_comm, n_sms - 1))
     lib.ag_gemm_bf16(rt.heap, a, b, out, ctx.workspace, ctx.flags, ctx.ctx_dev, ctx.max_seg_rows, ctx.max_chunks,
                      n_comm, ctx.BLOCK_N, n_sms, bool(ctx.use_multimem and rt.has_multicast), rt.config.wait_timeout_s)
