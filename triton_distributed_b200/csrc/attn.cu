@@ -636,3 +636,89 @@ cudaError_t launch_dist_combine(const DecodeArgs& a, void* out_bf16, void* stagi
 }
 
 }  // namespace tdb
+
+// ---------------------------------------------------------------------------
+// Allocation-free decode attention (see tdb/noalloc.h for the contract and for who needs it).
+// The split-KV partials live in a fixed array of the library image.  In host code the array's name is only a
+// stand-in for the symbol, not a device address, so the address is fetched per device with
+// cudaGetSymbolAddress before it is handed to the kernels.
+// ---------------------------------------------------------------------------
+#include <cstdio>
+
+#include "tdb/noalloc.h"
+
+namespace {
+
+constexpr int64_t kNoAllocFloats = 1 << 20;  // 4 MiB
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) float g_decode_scratch[kNoAllocFloats];
+
+float* g_scratch_addr[kNoAllocMaxDevices] = {nullptr};
+thread_local char g_noalloc_err[256] = "";
+
+int noalloc_fail(int code, const char* what, const char* detail) {
+  snprintf(g_noalloc_err, sizeof(g_noalloc_err), "%s%s%s", what, detail ? ": " : "", detail ? detail : "");
+  return code;
+}
+
+}  // namespace
+
+extern "C" int64_t tdb_decode_attn_noalloc_capacity(void) { return kNoAllocFloats; }
+
+extern "C" const char* tdb_noalloc_last_error(void) { return g_noalloc_err; }
+
+extern "C" int tdb_decode_attn_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                       const int32_t* block_table, const int32_t* kv_lens, void* out, int batch,
+                                       int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
+                                       int splits, float scale, float softcap, void* stream) {
+  if (q == nullptr || k_cache == nullptr || v_cache == nullptr || block_table == nullptr || kv_lens == nullptr ||
+      out == nullptr)
+    return noalloc_fail(TDB_NOALLOC_BAD_ARGUMENT, "null pointer argument", nullptr);
+  if (batch < 0 || num_q_heads < 1 || num_kv_heads < 1 || num_q_heads % num_kv_heads != 0 || page_size < 1 ||
+      max_pages < 1 || splits < 1 || (head_dim != 64 && head_dim != 128))
+    return noalloc_fail(TDB_NOALLOC_BAD_ARGUMENT, "bad shape argument (head_dim must be 64 or 128, heads divisible)",
+                        nullptr);
+  const int64_t need = static_cast<int64_t>(batch) * num_q_heads * splits * (head_dim + 1);
+  if (need > kNoAllocFloats) {
+    char msg[160];
+    snprintf(msg, sizeof(msg), "batch*heads*splits*(head_dim+1) = %lld floats exceeds the built-in scratch of %lld floats",
+             static_cast<long long>(need), static_cast<long long>(kNoAllocFloats));
+    return noalloc_fail(TDB_NOALLOC_TOO_LARGE, "request too large", msg);
+  }
+  if (batch == 0) return TDB_NOALLOC_OK;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return noalloc_fail(TDB_NOALLOC_CUDA_ERROR, "cudaGetDevice", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return noalloc_fail(TDB_NOALLOC_BAD_ARGUMENT, "device ordinal out of range", nullptr);
+  if (g_scratch_addr[dev] == nullptr) {
+    // first call on this device (it is the current one): resolve the symbol to its address on this device
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_decode_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return noalloc_fail(TDB_NOALLOC_CUDA_ERROR, "cudaGetSymbolAddress", cudaGetErrorString(e));
+    g_scratch_addr[dev] = p;
+  }
+  tdb::DecodeArgs a;
+  a.q = q;
+  a.workspace = g_scratch_addr[dev];
+  a.kv_lens = kv_lens;
+  a.kv.k_cache = k_cache;
+  a.kv.v_cache = v_cache;
+  a.kv.block_table = block_table;
+  a.kv.max_pages = max_pages;
+  a.kv.page_size = page_size;
+  a.kv.num_kv_heads = num_kv_heads;
+  a.batch = batch;
+  a.num_q_heads = num_q_heads;
+  a.head_dim = head_dim;
+  a.splits = splits;
+  a.scale = scale;
+  a.softcap = softcap;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  e = tdb::launch_decode_splitkv(a, s);
+  if (e != cudaSuccess) return noalloc_fail(TDB_NOALLOC_CUDA_ERROR, "split-KV launch", cudaGetErrorString(e));
+  e = tdb::launch_decode_combine(a, out, nullptr, nullptr, s);
+  if (e != cudaSuccess) return noalloc_fail(TDB_NOALLOC_CUDA_ERROR, "combine launch", cudaGetErrorString(e));
+  return TDB_NOALLOC_OK;
+}
