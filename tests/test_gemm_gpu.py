@@ -48,3 +48,20 @@ def test_gemm_strided_views():
     out = gemm(a, b)
     ref = a.float() @ b.float().t()
     assert (out.float() - ref).abs().max().item() / ref.abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("shape", [(1, 5120, 3200), (8, 1280, 5120), (32, 6400, 5120), (128, 5120, 3200), (200, 520, 264),
+                                   (16, 18992, 5120), (3, 136, 64)])
+def test_skinny_gemm_split_k(shape):
+    from triton_distributed_b200.ops import skinny_gemm
+
+    M, N, K = shape
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    for splits in (0, 1, 3):
+        for _ in range(2):   # twice: the kernel must leave its scratch clean
+            out = skinny_gemm(a, b, splits=splits)
+        torch.cuda.synchronize()
+        err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+        assert err < 2e-2, f"skinny {shape} splits={splits}: rel err {err}"

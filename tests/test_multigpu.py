@@ -21,3 +21,9 @@ def test_core_two_gpus():
 def test_core_without_nvls():
     out = run_gpu_script("check_core.py", 2, ["--quick"], env={"TDB200_NVLS": "0", "NCCL_NVLS_ENABLE": "0"})
     assert "ALL OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
+def test_model_two_gpus():
+    out = run_gpu_script("check_model.py", 2)
+    assert "MODEL OK" in out

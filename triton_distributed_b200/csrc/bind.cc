@@ -158,6 +158,7 @@ void ag_gemm_bf16(SymmHeap& h, const at::Tensor& a_local, const at::Tensor& b, a
   g.ldc = c.stride(0);
   g.block_n = pick_block_n(N, block_n);
   g.tmap_a = make_tmap3(ws.data_ptr(), tdb::kBF16, 2, M, K, K * 2, buf_elems * 2, 128, 64);
+  g.tmap_a_local = make_tmap3(a_local.data_ptr(), tdb::kBF16, 1, m, K, K * 2, static_cast<uint64_t>(m) * K * 2, 128, 64);
   g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, g.block_n, 64);
   if (c.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15u) == 0) {
     g.tmap_c = make_tmap3(c.data_ptr(), tdb::kBF16, W, m, N, c.stride(0) * 2, c.stride(0) * 2 * m, 128, 64);
@@ -221,6 +222,86 @@ void gemm_rs_bf16(SymmHeap& h, const at::Tensor& a, const at::Tensor& b, at::Ten
   check_cuda(tdb::launch_gemm(g, cur_stream()), "launch_gemm(reduce-scatter)");
 }
 
+// Small-M GEMM (decode): out[M,N] = x[M,K] @ w[N,K]^T with split-K; acc / counters are caller-kept scratch.
+void skinny_gemm_bf16(const at::Tensor& x, const at::Tensor& w, at::Tensor& out, at::Tensor& acc, at::Tensor& counters,
+                      int splits, int num_ctas) {
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16,
+              "skinny_gemm: bf16 expected");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1,
+              "skinny_gemm: 2-D tensors with contiguous rows expected");
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && out.size(0) == M && out.size(1) == N, "skinny_gemm: shape mismatch");
+  TORCH_CHECK(M >= 1 && M <= 256, "skinny_gemm: 1 <= M <= 256");
+  c10::cuda::CUDAGuard guard(x.device());
+  tdb::SkinnyGemmArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.M = M; a.N = N; a.K = K;
+  const int mpad = tdb::skinny_gemm_mpad(M);
+  tdb::TensorMap m;
+  int r = tdb::encode_tensor_map_2d(&m, w.data_ptr(), tdb::kBF16, N, K, w.stride(0) * 2, 128, 64, 128);
+  TORCH_CHECK(r == 0, "tensor map (w) failed: ", r);
+  a.tmap_w = m;
+  r = tdb::encode_tensor_map_2d(&m, x.data_ptr(), tdb::kBF16, M, K, x.stride(0) * 2, mpad, 64, 128);
+  TORCH_CHECK(r == 0, "tensor map (x) failed: ", r);
+  a.tmap_x = m;
+  a.out = out.data_ptr();
+  a.ld_out = out.stride(0);
+  a.splits = splits > 0 ? splits : tdb::skinny_gemm_pick_splits(N, K, sm_count());
+  a.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
+  if (a.splits > 1) {
+    TORCH_CHECK(acc.scalar_type() == at::kFloat && acc.numel() >= M * N, "skinny_gemm: accumulation buffer too small");
+    TORCH_CHECK(counters.scalar_type() == at::kInt && counters.numel() >= (N + 127) / 128, "skinny_gemm: counters too small");
+    a.acc = acc.data_ptr<float>();
+    a.counters = reinterpret_cast<uint32_t*>(counters.data_ptr());
+  }
+  a.symm.world = 1;
+  a.symm.timeout_ns = 2000000000ull;
+  check_cuda(tdb::launch_skinny_gemm(a, cur_stream()), "launch_skinny_gemm");
+}
+
+// Small-M GEMM + all-reduce in one launch.
+void gemm_ar_bf16(SymmHeap& h, const at::Tensor& x, const at::Tensor& w, at::Tensor& out, at::Tensor& acc,
+                  at::Tensor& counters, at::Tensor& partial, at::Tensor& flags, at::Tensor& ctx, int64_t m_cap,
+                  int64_t max_tiles, int splits, int num_ctas, bool use_multimem, double timeout_s) {
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16,
+              "gemm_ar: bf16 expected");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm_ar: contiguous rows expected");
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && out.size(0) == M && out.size(1) == N, "gemm_ar: shape mismatch");
+  TORCH_CHECK(M >= 1 && M <= m_cap && m_cap <= 256, "gemm_ar: M exceeds the context's capacity (<= 256)");
+  const int W = h.world();
+  const bool mc = use_multimem && h.has_multicast();
+  TORCH_CHECK(static_cast<uint64_t>(partial.numel()) >= 2ull * (mc ? 1 : W) * m_cap * N, "gemm_ar: partial buffer too small");
+  TORCH_CHECK(acc.numel() >= m_cap * N && counters.numel() >= (N + 127) / 128, "gemm_ar: scratch too small");
+  c10::cuda::CUDAGuard guard(x.device());
+  tdb::SkinnyGemmArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.M = M; a.N = N; a.K = K;
+  const int mpad = tdb::skinny_gemm_mpad(M);
+  tdb::TensorMap m;
+  int r = tdb::encode_tensor_map_2d(&m, w.data_ptr(), tdb::kBF16, N, K, w.stride(0) * 2, 128, 64, 128);
+  TORCH_CHECK(r == 0, "tensor map (w) failed: ", r);
+  a.tmap_w = m;
+  r = tdb::encode_tensor_map_2d(&m, x.data_ptr(), tdb::kBF16, M, K, x.stride(0) * 2, mpad, 64, 128);
+  TORCH_CHECK(r == 0, "tensor map (x) failed: ", r);
+  a.tmap_x = m;
+  a.out = out.data_ptr();
+  a.ld_out = out.stride(0);
+  a.splits = splits > 0 ? splits : tdb::skinny_gemm_pick_splits(N, K, sm_count());
+  a.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
+  a.acc = acc.data_ptr<float>();
+  a.counters = reinterpret_cast<uint32_t*>(counters.data_ptr());
+  a.all_reduce = 1;
+  a.use_multimem = mc ? 1 : 0;
+  a.partial = partial.data_ptr();
+  a.flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
+  a.max_tiles = max_tiles;
+  a.m_cap = m_cap;
+  a.ctx = reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr());
+  a.symm = h.info(static_cast<uint64_t>(timeout_s * 1e9));
+  check_cuda(tdb::launch_skinny_gemm(a, cur_stream()), "launch_skinny_gemm(all-reduce)");
+}
+
 }  // namespace
 
 void bind_more(py::module_& m);  // bind_ops.inc-style split kept in this file for build simplicity
@@ -275,5 +356,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ag_gemm_bf16", &ag_gemm_bf16);
   m.def("gemm_rs_bf16", &gemm_rs_bf16);
   m.def("gemm_smem_bytes", &tdb::gemm_smem_bytes);
+  m.def("skinny_gemm_bf16", &skinny_gemm_bf16);
+  m.def("gemm_ar_bf16", &gemm_ar_bf16);
+  m.def("skinny_gemm_pick_splits", &tdb::skinny_gemm_pick_splits);
   bind_more(m);
 }

@@ -106,6 +106,13 @@ void timeout_probe(SymmHeap& h, at::Tensor& flag, int64_t expected, double timeo
              "launch_timeout_probe");
 }
 
+void p2p_copy(at::Tensor& dst, const at::Tensor& src, int64_t num_ctas, int64_t mode) {
+  TORCH_CHECK(dst.is_contiguous() && src.is_contiguous(), "p2p_copy: contiguous tensors expected");
+  const uint64_t bytes = static_cast<uint64_t>(src.numel()) * src.element_size();
+  TORCH_CHECK(static_cast<uint64_t>(dst.numel()) * dst.element_size() >= bytes, "p2p_copy: destination too small");
+  check_cuda(tdb::launch_p2p_copy(dst.data_ptr(), src.data_ptr(), bytes, num_ctas, mode, cur_stream()), "launch_p2p_copy");
+}
+
 // ------------------------------------------------------------------ elementwise
 void check_bf16(const at::Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, name, ": CUDA bf16 tensor expected");
@@ -229,6 +236,7 @@ void bind_more(py::module_& m) {
   m.def("all_gather_ll", &all_gather_ll);
   m.def("primitives_test", &primitives_test);
   m.def("timeout_probe", &timeout_probe);
+  m.def("p2p_copy", &p2p_copy);
   m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("residual") = py::none());
   m.def("silu_mul", &silu_mul);
   m.def("add", &add);

@@ -454,6 +454,63 @@ __global__ void timeout_probe_kernel(const uint32_t* flag, uint32_t expected, co
   if (threadIdx.x == 0) wait_until(symm, flag, expected, kCmpGe, kKernelPrimitive, 99, -1, 0);
 }
 
+// ---------------------------------------------------------------------------
+// Plain copy kernel between any two device-visible buffers (local or peer-mapped): the transport of the
+// pipeline-parallel CommOp and the calibration kernel for NVLink bandwidth.
+//   mode 0: every thread moves 16-byte vectors (4 loads in flight per thread)
+//   mode 1: one thread per CTA drives a ring of bulk-TMA copies (global -> shared -> global)
+// ---------------------------------------------------------------------------
+constexpr int kCopyPiece = 32 * 1024;
+constexpr int kCopySlots = 6;
+constexpr int kCopyAhead = 4;
+
+__global__ void __launch_bounds__(kCollThreads) p2p_copy_kernel(char* dst, const char* src, uint64_t bytes, int mode) {
+  extern __shared__ __align__(128) uint8_t cp_smem[];
+  uint64_t lo, hi;
+  if (mode == 0) {
+    cta_range(bytes >> 4, &lo, &hi);
+    uint64_t i = lo + threadIdx.x;
+    const uint64_t T = blockDim.x;
+    for (; i + 3 * T < hi; i += 4 * T) {
+      const uint4 a = ld_v4(src + (i << 4)), b = ld_v4(src + ((i + T) << 4)), c = ld_v4(src + ((i + 2 * T) << 4)),
+                  d = ld_v4(src + ((i + 3 * T) << 4));
+      st_v4(dst + (i << 4), a);
+      st_v4(dst + ((i + T) << 4), b);
+      st_v4(dst + ((i + 2 * T) << 4), c);
+      st_v4(dst + ((i + 3 * T) << 4), d);
+    }
+    for (; i < hi; i += T) st_v4(dst + (i << 4), ld_v4(src + (i << 4)));
+    return;
+  }
+  if (threadIdx.x != 0) return;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(cp_smem + kCopySlots * kCopyPiece);
+  for (int i = 0; i < kCopySlots; ++i) mbar_init(&bars[i], 1);
+  fence_mbar_init();
+  const uint64_t npieces_total = (bytes + kCopyPiece - 1) / kCopyPiece;
+  cta_range(npieces_total, &lo, &hi);
+  const uint64_t n = hi - lo;
+  for (uint64_t step = 0; step < n + kCopyAhead; ++step) {
+    if (step < n) {
+      const int slot = step % kCopySlots;
+      bulk_wait_read<kCopySlots - kCopyAhead - 1>();
+      const uint64_t off = (lo + step) * kCopyPiece;
+      const uint32_t sz = static_cast<uint32_t>(bytes - off < (uint64_t)kCopyPiece ? bytes - off : (uint64_t)kCopyPiece);
+      mbar_arrive_expect_tx(&bars[slot], sz);
+      bulk_load(cp_smem + slot * kCopyPiece, src + off, sz, &bars[slot]);
+    }
+    if (step >= kCopyAhead) {
+      const uint64_t j = step - kCopyAhead;
+      const int slot = j % kCopySlots;
+      if (!mbar_wait(&bars[slot], (j / kCopySlots) & 1, nullptr, 2000000000ull)) break;
+      const uint64_t off = (lo + j) * kCopyPiece;
+      const uint32_t sz = static_cast<uint32_t>(bytes - off < (uint64_t)kCopyPiece ? bytes - off : (uint64_t)kCopyPiece);
+      bulk_store(dst + off, cp_smem + slot * kCopyPiece, sz);
+      bulk_commit();
+    }
+  }
+  bulk_wait<0>();
+}
+
 SymmInfo to_dev(const SymmInfoHost& h) {
   SymmInfo s;
   static_assert(sizeof(SymmInfo) == sizeof(SymmInfoHost), "SymmInfo mirrors must match");
@@ -535,6 +592,25 @@ cudaError_t launch_allgather_ll(const AllGatherLLArgs& a, cudaStream_t stream) {
   if (static_cast<uint64_t>(a.symm.world) * p.shard_u64 * 16 > a.staging_half_bytes) return cudaErrorInvalidValue;
   int ctas = a.num_ctas < 1 ? 1 : a.num_ctas;
   allgather_ll_kernel<<<ctas, kCollThreads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_p2p_copy(void* dst, const void* src, uint64_t bytes, int num_ctas, int mode, cudaStream_t stream) {
+  if ((bytes & 15) != 0 || ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) != 0)
+    return cudaErrorInvalidValue;
+  if (bytes == 0) return cudaSuccess;
+  const int smem = mode == 1 ? kCopySlots * kCopyPiece + 64 : 0;
+  if (mode == 1) {
+    static bool set = false;
+    if (!set) {
+      cudaError_t e = cudaFuncSetAttribute(p2p_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return e;
+      set = true;
+    }
+  }
+  if (num_ctas < 1) num_ctas = 1;
+  p2p_copy_kernel<<<num_ctas, kCollThreads, smem, stream>>>(reinterpret_cast<char*>(dst), reinterpret_cast<const char*>(src),
+                                                            bytes, mode);
   return cudaGetLastError();
 }
 

@@ -1,0 +1,403 @@
+// Small-M ("decode") GEMM with split-K and an optional fused all-reduce:
+//
+//     out[M, N] = sum over ranks ( X[M, K_local] * W[N, K_local]^T ),   M <= 256
+//
+// The problem is swapped so that the weight rows fill the 128-row dimension of tcgen05.mma: the A operand is a
+// 128 x 64 weight tile, the B operand the M_pad x 64 activation tile, and the accumulator in TMEM is
+// [128 lanes = output columns] x [M_pad columns = tokens].  A work item is (128 output columns, one K split); the
+// persistent grid streams the weights exactly once through a deep TMA ring, which is what bounds decode GEMMs.
+// Split-K partials are added with red.global.add.f32 into an accumulation buffer; the CTA that arrives last on a
+// column tile converts it, clears the buffer again (self-cleaning, CUDA-graph safe) and, in all-reduce mode, runs
+// the cross-rank sum for that tile right away:
+//     NVLS:  store the bf16 partial tile to the heap, flag all ranks, wait for all ranks' flags of this tile,
+//            multimem.ld_reduce the tile (summed inside the switch) -> out
+//     push:  store the partial tile into slot [rank] on every peer, flag, wait, sum the W slots -> out
+// so the all-reduce of early tiles overlaps the GEMM of later ones and there is one launch per layer op.
+//
+// Reference behaviour being matched (not its code): python/triton_dist/kernels/nvidia/gemm_allreduce.py:124-315
+// (per-tile flags, consumer CTAs reduce with multimem.ld_reduce, double-buffered phases :74-92), layer wrapper
+// layers/nvidia/gemm_allreduce_layer.py:32-116.
+#include <cuda.h>
+
+#include "tdb/api.h"
+#include "tdb/symm_device.cuh"
+
+namespace tdb {
+
+namespace {
+
+constexpr int kTN = 128;    // output columns per tile (MMA M)
+constexpr int kBK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr uint64_t kMbarTimeoutNs = 4000000000ull;
+
+template <int MPAD>
+struct Layout {
+  static constexpr int kWBytes = kTN * kBK * 2;        // 16 KB
+  static constexpr int kXBytesRaw = MPAD * kBK * 2;
+  static constexpr int kXBytes = (kXBytesRaw + 1023) / 1024 * 1024;   // keep every operand 1024-byte aligned
+  static constexpr int kStageBytes = kWBytes + kXBytes;
+  static constexpr int kStages = (200 * 1024) / kStageBytes > 12 ? 12 : (200 * 1024) / kStageBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 32;
+  static constexpr int kTmemCols = (2 * MPAD) < 32 ? 32 : 2 * MPAD;
+};
+
+struct KP {
+  int M, N, K;
+  int tiles_n, splits, kb_total;
+  __nv_bfloat16* out;        // [M, N]
+  int64_t ld_out;
+  float* acc;                // [M_cap, N] fp32 split-K accumulation (all zero between calls)
+  uint32_t* counters;        // [tiles_n] arrivals per tile (zero between calls)
+  int mode;                  // 0 plain, 1 all-reduce
+  int use_mc;
+  __nv_bfloat16* partial;    // heap: NVLS [2][M_cap][N]; push [2][W][M_cap][N]
+  uint64_t partial_half;     // elements per parity buffer
+  uint32_t* flags;           // heap [W][max_tiles] epochs
+  int max_tiles;
+  int m_cap;
+  CtxDev* ctx;
+  SymmInfo symm;
+};
+
+TDB_DEVICE void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int MPAD>
+__global__ void __launch_bounds__(kThreads, 1)
+skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const KP p) {
+  using L = Layout<MPAD>;
+  constexpr int kStages = L::kStages;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_smem + 1);
+  volatile int* is_last = reinterpret_cast<volatile int*>(tmem_base_smem + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t epoch = (p.ctx != nullptr) ? ld_volatile(&p.ctx->epoch) : 1u;
+  const int par = epoch & 1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 128);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_smem, L::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_smem;
+
+  const int items = p.tiles_n * p.splits;
+  const int kb_per = (p.kb_total + p.splits - 1) / p.splits;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0, issued = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+        const int nt = w / p.splits, sp = w - nt * p.splits;
+        const int kb0 = sp * kb_per, kb1 = min(p.kb_total, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kMbarTimeoutNs)) {
+            ok = false;
+            report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 10, -1, s, (int)ph, w);
+            break;
+          }
+          uint8_t* sw = smem + s * L::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[s], L::kWBytes + L::kXBytesRaw);
+          tma_load_2d(sw, &tmap_w, &full_bar[s], kb * kBK, nt * kTN);
+          tma_load_2d(sw + L::kWBytes, &tmap_x, &full_bar[s], kb * kBK, 0);
+          ++issued;
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        const uint32_t first = issued > (uint32_t)kStages ? issued - kStages : 0;
+        for (uint32_t j = first; j < issued; ++j) mbar_wait(&full_bar[j % kStages], (j / kStages) & 1, nullptr, 200000000ull);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(1u, kTN, MPAD);
+      uint32_t it = 0;
+      int local = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++local) {
+        const int nt = w / p.splits, sp = w - nt * p.splits;
+        const int kb0 = sp * kb_per, kb1 = min(p.kb_total, kb0 + kb_per);
+        const int b = local & 1;
+        const uint32_t aph = (local >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[b], aph ^ 1, abort_flag, kMbarTimeoutNs)) {
+          ok = false;
+          report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 20, -1, b, (int)aph, w);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + b * MPAD;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, kMbarTimeoutNs)) {
+            ok = false;
+            report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 21, -1, s, (int)ph, w);
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sw = smem_u32(smem + s * L::kStageBytes);
+          const uint64_t adesc = make_smem_desc_sw128(sw);
+          const uint64_t bdesc = make_smem_desc_sw128(sw + L::kWBytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+        }
+        // an empty K range (more splits than k-blocks) still has to release the epilogue: commit with no MMAs
+        if (ok) umma_commit(&tmem_full[b]);
+      }
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    const int q = warp & 3;
+    const bool leader = (warp == 2 && lane == 0);
+    const int W = p.symm.world, rank = p.symm.rank;
+    int local = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++local) {
+      const int nt = w / p.splits, sp = w - nt * p.splits;
+      const int kb0 = sp * kb_per, kb1 = min(p.kb_total, kb0 + kb_per);
+      const int b = local & 1;
+      const uint32_t aph = (local >> 1) & 1;
+      if (!mbar_wait(&tmem_full[b], aph, abort_flag, kMbarTimeoutNs)) {
+        ok = false;
+        if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 30, -1, b, (int)aph, w);
+        break;
+      }
+      tc_fence_after_sync();
+      const int n = nt * kTN + q * 32 + lane;   // this thread's output column
+      const bool n_ok = n < p.N;
+      const bool direct = (p.splits == 1 && p.mode == 0);
+      const bool has_k = kb1 > kb0;
+#pragma unroll 1
+      for (int c = 0; c < MPAD / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld_32x16(tmem_base + b * MPAD + c * 16 + (static_cast<uint32_t>(q * 32) << 16), r);
+        tmem_ld_wait();
+        if (!has_k || !n_ok) continue;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = c * 16 + j;
+          if (m < p.M) {
+            if (direct) {
+              p.out[static_cast<int64_t>(m) * p.ld_out + n] = __float2bfloat16(__uint_as_float(r[j]));
+            } else {
+              atomicAdd(p.acc + static_cast<int64_t>(m) * p.N + n, __uint_as_float(r[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tmem_empty[b]);
+      if (direct) continue;
+      // ---- tile arrival: the last split to finish owns the tile's finalisation
+      __threadfence();
+      epi_bar();
+      if (leader) {
+        const uint32_t prev = atomicAdd(p.counters + nt, 1u);
+        *is_last = (prev == static_cast<uint32_t>(p.splits) - 1) ? 1 : 0;
+        if (*is_last) p.counters[nt] = 0;
+      }
+      epi_bar();
+      if (*is_last == 0) continue;
+      __threadfence();
+      // finalise: fp32 accumulation -> bf16 (out, or the heap partial for the all-reduce); clear the accumulator
+      __nv_bfloat16* dst;
+      int64_t ld_dst;
+      if (p.mode == 0) {
+        dst = p.out;
+        ld_dst = p.ld_out;
+      } else if (p.use_mc) {
+        dst = p.partial + par * p.partial_half;
+        ld_dst = p.N;
+      } else {
+        dst = p.partial + par * p.partial_half + static_cast<uint64_t>(rank) * p.m_cap * p.N;
+        ld_dst = p.N;
+      }
+      if (n_ok) {
+        for (int m = 0; m < p.M; ++m) {
+          float* a = p.acc + static_cast<int64_t>(m) * p.N + n;
+          const float v = __ldcg(a);
+          *a = 0.f;
+          dst[static_cast<int64_t>(m) * ld_dst + n] = __float2bfloat16(v);
+        }
+      }
+      if (p.mode == 0) continue;
+      // ---- cross-rank sum of this tile
+      const int tn = min(kTN, p.N - nt * kTN);   // valid columns of the tile (multiple of 8)
+      if (!p.use_mc) {
+        // push the tile into slot [rank] of every peer
+        epi_bar();
+        const int vec_per_row = tn / 8;
+        const int et = threadIdx.x - 64;
+        for (int v = et; v < p.M * vec_per_row; v += 128) {
+          const int m = v / vec_per_row, cv = v - m * vec_per_row;
+          __nv_bfloat16* src = dst + static_cast<int64_t>(m) * p.N + nt * kTN + cv * 8;
+          const uint4 u = ld_v4(src);
+          for (int j = 1; j < W; ++j) st_v4(symm_at(p.symm, src, (rank + j) % W), u);
+        }
+      }
+      epi_bar();
+      const int et = threadIdx.x - 64;   // 0..127 within the epilogue warps
+      bool wok = true;
+      if (et < W) {
+        fence_acq_rel_sys();
+        st_release_sys(symm_at(p.symm, p.flags + static_cast<int64_t>(rank) * p.max_tiles + nt, (rank + et) % W), epoch);
+        wok = wait_until(p.symm, p.flags + static_cast<int64_t>(et) * p.max_tiles + nt, epoch, kCmpGe, kKernelGemmAr, 40,
+                         et, nt);
+      }
+      // combine the per-thread results without leaving the named barrier unbalanced
+      __shared__ int s_wok;
+      if (et == 0) s_wok = 1;
+      epi_bar();
+      if (!wok) s_wok = 0;
+      epi_bar();
+      if (s_wok == 0) {
+        ok = false;
+        break;
+      }
+      const int vec_per_row = tn / 8;
+      for (int v = et; v < p.M * vec_per_row; v += 128) {
+        const int m = v / vec_per_row, cv = v - m * vec_per_row;
+        const int col = nt * kTN + cv * 8;
+        uint4 o;
+        if (p.use_mc) {
+          const __nv_bfloat16* src = p.partial + par * p.partial_half + static_cast<int64_t>(m) * p.N + col;
+          o = multimem_ld_reduce_bf16x8(mc_ptr(p.symm, src));
+        } else {
+          float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int s = 0; s < W; ++s) {
+            const __nv_bfloat16* src = p.partial + par * p.partial_half + (static_cast<uint64_t>(s) * p.m_cap + m) * p.N + col;
+            const uint4 u = ld_relaxed_sys_v4(src);
+            const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+            accv[0] += f0.x; accv[1] += f0.y; accv[2] += f1.x; accv[3] += f1.y;
+            accv[4] += f2.x; accv[5] += f2.y; accv[6] += f3.x; accv[7] += f3.y;
+          }
+          o.x = pack_bf16x2(accv[0], accv[1]); o.y = pack_bf16x2(accv[2], accv[3]);
+          o.z = pack_bf16x2(accv[4], accv[5]); o.w = pack_bf16x2(accv[6], accv[7]);
+        }
+        st_v4(p.out + static_cast<int64_t>(m) * p.ld_out + col, o);
+      }
+    }
+    if (!ok) *abort_flag = 1;
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, L::kTmemCols);
+  }
+  if (p.ctx != nullptr) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const uint32_t prev = atomicAdd(&p.ctx->done, 1u);
+      if (prev == gridDim.x - 1) {
+        p.ctx->done = 0;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(&p.ctx->epoch) = epoch + 1;
+      }
+    }
+  }
+}
+
+template <int MPAD>
+cudaError_t launch_t(const SkinnyGemmArgs& a, const KP& p, int grid, cudaStream_t stream) {
+  using L = Layout<MPAD>;
+  const int smem = L::kTotal + 1024;
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    set = true;
+  }
+  CUtensorMap tw, tx;
+  memcpy(&tw, a.tmap_w.bytes, sizeof(CUtensorMap));
+  memcpy(&tx, a.tmap_x.bytes, sizeof(CUtensorMap));
+  skinny_gemm_kernel<MPAD><<<grid, kThreads, smem, stream>>>(tw, tx, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+int skinny_gemm_mpad(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : M <= 256 ? 256 : -1; }
+
+int skinny_gemm_pick_splits(int N, int K, int num_sms) {
+  const int tiles = (N + kTN - 1) / kTN;
+  const int kb = (K + kBK - 1) / kBK;
+  int s = num_sms / tiles;
+  if (s < 1) s = 1;
+  if (s > kb / 4) s = kb / 4 > 0 ? kb / 4 : 1;   // at least 4 k-blocks per split
+  if (s > 16) s = 16;
+  return s;
+}
+
+cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream) {
+  if (a.M < 1 || a.M > 256 || a.K % 8 != 0) return cudaErrorInvalidValue;
+  if (a.all_reduce && a.N % 8 != 0) return cudaErrorInvalidValue;
+  KP p;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.tiles_n = (a.N + kTN - 1) / kTN;
+  p.splits = a.splits < 1 ? 1 : a.splits;
+  p.kb_total = (a.K + kBK - 1) / kBK;
+  if (p.splits > p.kb_total) p.splits = p.kb_total;
+  p.out = reinterpret_cast<__nv_bfloat16*>(a.out);
+  p.ld_out = a.ld_out;
+  p.acc = a.acc;
+  p.counters = a.counters;
+  p.mode = a.all_reduce ? 1 : 0;
+  p.use_mc = (a.use_multimem && a.symm.mc_base != 0) ? 1 : 0;
+  p.partial = reinterpret_cast<__nv_bfloat16*>(a.partial);
+  p.m_cap = a.m_cap;
+  p.partial_half = p.use_mc ? static_cast<uint64_t>(a.m_cap) * a.N : static_cast<uint64_t>(a.symm.world) * a.m_cap * a.N;
+  p.flags = a.flags;
+  p.max_tiles = a.max_tiles;
+  p.ctx = a.ctx;
+  static_assert(sizeof(SymmInfo) == sizeof(SymmInfoHost), "SymmInfo mirrors must match");
+  memcpy(&p.symm, &a.symm, sizeof(SymmInfo));
+  if ((p.splits > 1 || p.mode == 1) && (a.acc == nullptr || a.counters == nullptr)) return cudaErrorInvalidValue;
+  if (p.mode == 1 && (p.tiles_n > a.max_tiles || a.M > a.m_cap || a.ctx == nullptr)) return cudaErrorInvalidValue;
+  const int items = p.tiles_n * p.splits;
+  int grid = a.num_ctas < items ? a.num_ctas : items;
+  if (grid < 1) grid = 1;
+  switch (skinny_gemm_mpad(a.M)) {
+    case 16: return launch_t<16>(a, p, grid, stream);
+    case 32: return launch_t<32>(a, p, grid, stream);
+    case 64: return launch_t<64>(a, p, grid, stream);
+    case 128: return launch_t<128>(a, p, grid, stream);
+    case 256: return launch_t<256>(a, p, grid, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace tdb

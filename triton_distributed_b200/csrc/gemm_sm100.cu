@@ -60,8 +60,8 @@ struct SmemLayout {
 
 // ring used by the comm CTAs of the all-gather mode (same dynamic shared memory)
 constexpr int kPushPiece = 32 * 1024;
-constexpr int kPushSlots = 6;
-constexpr int kPushAhead = 3;
+constexpr int kPushSlots = 7;
+constexpr int kPushAhead = 5;
 
 struct PeerMaps {
   CUtensorMap m[kMaxRanks];
@@ -175,13 +175,26 @@ __device__ void ag_push_bulk(const KParams& p, uint32_t epoch, uint8_t* smem) {
   for (int i = 0; i < kPushSlots; ++i) mbar_init(&bars[i], 1);
   fence_mbar_init();
 
-  // work list of this CTA: for d in 0..W-1 (0 = own workspace), for its chunks, for the pieces of a chunk
+  // work list of this CTA: for d in 1..W-1 (the GEMM reads the local shard in place), for its chunks, for the
+  // pieces of a chunk
   const int my_chunks = chunks > static_cast<int>(blockIdx.x) ? (chunks - blockIdx.x + p.n_comm - 1) / p.n_comm : 0;
   uint32_t ld_i = 0, st_i = 0;                 // pieces loaded / stored so far (global counters over the ring)
-  int ld_d = 0, ld_c = 0;
+  int ld_d = 1, ld_c = 0;
   uint64_t ld_off = 0;                          // load cursor: (distance, chunk ordinal, byte offset in chunk)
-  int st_d = 0, st_c = 0;
+  int st_d = 1, st_c = 0;
   uint64_t st_off = 0;                          // store cursor
+  // flags whose chunk has been committed but not yet confirmed complete (raised two groups later, so the
+  // pipeline never drains in the middle)
+  constexpr int kPend = 4;
+  uint32_t pend_group[kPend];
+  int pend_peer[kPend], pend_chunk[kPend];
+  int pend_n = 0;
+  auto raise_flag = [&](int peer, int c) {
+    fence_proxy_async();
+    fence_acq_rel_sys();
+    uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * W + rank) * p.max_chunks + c;
+    st_release_sys(symm_at(p.symm, flag, peer), epoch);
+  };
   bool ok = true;
   auto chunk_bytes = [&](int ordinal) -> uint64_t {
     const int c = blockIdx.x + ordinal * p.n_comm;
@@ -190,7 +203,7 @@ __device__ void ag_push_bulk(const KParams& p, uint32_t epoch, uint8_t* smem) {
   const uint64_t total_pieces = [&]() {
     uint64_t n = 0;
     for (int o = 0; o < my_chunks; ++o) n += (chunk_bytes(o) + kPushPiece - 1) / kPushPiece;
-    return n * W;
+    return n * (W - 1);
   }();
   for (uint64_t step = 0; step < total_pieces + kPushAhead && ok; ++step) {
     if (step < total_pieces) {
@@ -232,21 +245,42 @@ __device__ void ag_push_bulk(const KParams& p, uint32_t epoch, uint8_t* smem) {
       ++st_i;
       st_off += bytes;
       if (st_off >= cb) {
-        // chunk complete on `peer`: wait for the writes, then raise its flag there
-        bulk_wait<0>();
-        fence_proxy_async();
-        fence_acq_rel_sys();
-        uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * W + rank) * p.max_chunks + c;
-        st_release_sys(symm_at(p.symm, flag, peer), epoch);
+        // last piece of this chunk for `peer` committed as group st_i - 1: its flag follows once that group is done
+        if (pend_n == kPend) {
+          bulk_wait<0>();
+          for (int j = 0; j < pend_n; ++j) raise_flag(pend_peer[j], pend_chunk[j]);
+          pend_n = 0;
+        }
+        pend_group[pend_n] = st_i - 1;
+        pend_peer[pend_n] = peer;
+        pend_chunk[pend_n] = c;
+        ++pend_n;
         st_off = 0;
         if (++st_c >= my_chunks) {
           st_c = 0;
           ++st_d;
         }
       }
+      // groups older than the two newest are complete after wait_group 2
+      if (pend_n > 0 && (st_i - 1) - pend_group[0] >= 2) {
+        bulk_wait<2>();
+        int keep = 0;
+        for (int j = 0; j < pend_n; ++j) {
+          if ((st_i - 1) - pend_group[j] >= 2) {
+            raise_flag(pend_peer[j], pend_chunk[j]);
+          } else {
+            pend_group[keep] = pend_group[j];
+            pend_peer[keep] = pend_peer[j];
+            pend_chunk[keep] = pend_chunk[j];
+            ++keep;
+          }
+        }
+        pend_n = keep;
+      }
     }
   }
   bulk_wait<0>();
+  for (int j = 0; j < pend_n; ++j) raise_flag(pend_peer[j], pend_chunk[j]);
 }
 
 // Owner-side reduction of the reduce-scatter mode: out[rows of my segment] = sum over sources.
@@ -300,7 +334,7 @@ template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ PeerMaps peer_maps,
-            const KParams p) {
+            const __grid_constant__ CUtensorMap tmap_a_local, const KParams p) {
   using L = SmemLayout<BN>;
   constexpr int kStages = L::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -340,6 +374,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       fence_mbar_init();
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_b);
+      if (p.mode == kGemmAllGather) tma_prefetch_desc(&tmap_a_local);
       if (p.tma_store && p.mode != kGemmReduceScatter) tma_prefetch_desc(&tmap_c);
     }
     if (warp == 1) {
@@ -364,7 +399,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         bool ok = true;
         for (int t = g_idx; t < num_tiles && ok; t += n_gemm) {
           const Tile tl = decode_tile(p, t, BN);
-          if (p.mode == kGemmAllGather) {
+          // all-gather mode: the local shard is read where it is, remote shards from the workspace once they arrived
+          const bool local_seg = (p.mode == kGemmAllGather) && tl.seg == p.symm.rank;
+          if (p.mode == kGemmAllGather && !local_seg) {
             const uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * p.symm.world + tl.seg) * p.max_chunks + tl.mt;
             ok = wait_until(p.symm, flag, epoch, kCmpGe, kKernelAgGemm, 1, tl.seg, tl.mt);
             if (!ok) break;
@@ -381,7 +418,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint8_t* sa = smem + s * L::kStageBytes;
             uint8_t* sb = sa + L::kABytes;
             mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
-            tma_load_3d(sa, &tmap_a, &full_bar[s], kb * kBK, tl.m0, (p.mode == kGemmAllGather) ? buf : 0);
+            if (local_seg) {
+              tma_load_3d(sa, &tmap_a_local, &full_bar[s], kb * kBK, tl.mt * kBM, 0);
+            } else {
+              tma_load_3d(sa, &tmap_a, &full_bar[s], kb * kBK, tl.m0, (p.mode == kGemmAllGather) ? buf : 0);
+            }
             tma_load_3d(sb, &tmap_b, &full_bar[s], kb * kBK, tl.n0, 0);
             ++issued;
           }
@@ -633,13 +674,14 @@ cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
   if (a.mode == kGemmAllGather && (a.n_comm_ctas < 1 || a.n_comm_ctas >= a.num_ctas)) return cudaErrorInvalidValue;
   if (a.K % 8 != 0) return cudaErrorInvalidValue;
 
-  CUtensorMap ta, tb, tc;
+  CUtensorMap ta, tb, tc, tl;
+  memcpy(&tl, a.tmap_a_local.bytes, sizeof(CUtensorMap));
   memcpy(&ta, a.tmap_a.bytes, sizeof(CUtensorMap));
   memcpy(&tb, a.tmap_b.bytes, sizeof(CUtensorMap));
   memcpy(&tc, a.tmap_c.bytes, sizeof(CUtensorMap));
   PeerMaps pm;
   memcpy(&pm, a.tmap_peer_c, sizeof(PeerMaps));
-  gemm_kernel<BN><<<a.num_ctas, kThreads, smem, stream>>>(ta, tb, tc, pm, p);
+  gemm_kernel<BN><<<a.num_ctas, kThreads, smem, stream>>>(ta, tb, tc, pm, tl, p);
   return cudaGetLastError();
 }
 

@@ -64,6 +64,7 @@ struct GemmArgs {
   // output through shared memory + TMA store: C as [segments][rows per segment][N], box [128 x 64], 128-byte swizzle;
   // reduce-scatter: one map per owner rank over its slots [2*world][rows per segment][N]
   TensorMap tmap_c;
+  TensorMap tmap_a_local;   // all-gather: the local shard [seg_rows, K], read in place
   TensorMap tmap_peer_c[kMaxRanksHost];
   int use_tma_store;
   int block_n;      // 128 or 256
@@ -87,5 +88,32 @@ struct GemmArgs {
 };
 cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream);
 int gemm_smem_bytes(int block_n);
+
+// ---------------------------------------------------------------------------
+// Small-M GEMM with split-K and optional fused all-reduce (gemm_ar_sm100.cu):
+// out[M,N] = (sum over ranks) X[M,K] * W[N,K]^T, M <= 256.
+// ---------------------------------------------------------------------------
+struct SkinnyGemmArgs {
+  int M, N, K;
+  TensorMap tmap_w;        // W [N, K], box [128 x 64], 128-byte swizzle
+  TensorMap tmap_x;        // X [M, K], box [M_pad x 64], 128-byte swizzle
+  void* out;               // bf16 [M, ld_out]
+  int64_t ld_out;
+  int splits;              // K splits (>= 1)
+  int num_ctas;
+  float* acc;              // fp32 [m_cap, N], all zero between calls (needed when splits > 1 or all_reduce)
+  uint32_t* counters;      // [ceil(N/128)], zero between calls
+  int all_reduce;
+  int use_multimem;
+  void* partial;           // heap: NVLS [2][m_cap][N] bf16, push [2][world][m_cap][N] bf16
+  uint32_t* flags;         // heap [world][max_tiles]
+  int max_tiles;
+  int m_cap;
+  CtxDev* ctx;
+  SymmInfoHost symm;
+};
+cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream);
+int skinny_gemm_mpad(int M);
+int skinny_gemm_pick_splits(int N, int K, int num_sms);
 
 }  // namespace tdb

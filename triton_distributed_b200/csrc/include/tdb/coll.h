@@ -56,6 +56,9 @@ struct AllGatherLLArgs {
 };
 cudaError_t launch_allgather_ll(const AllGatherLLArgs& a, cudaStream_t stream);
 
+// Copy `bytes` (multiple of 16) between device-visible buffers; mode 0 = vector ld/st, 1 = bulk-TMA ring.
+cudaError_t launch_p2p_copy(void* dst, const void* src, uint64_t bytes, int num_ctas, int mode, cudaStream_t stream);
+
 cudaError_t launch_primitives_test(int32_t* data, int32_t* scratch, uint32_t* sig, uint32_t* bar_flags, int n,
                                    uint32_t epoch, const SymmInfoHost& symm, cudaStream_t stream);
 cudaError_t launch_timeout_probe(const uint32_t* flag, uint32_t expected, const SymmInfoHost& symm,

@@ -94,6 +94,17 @@ def create_ag_gemm_context(tensor_A: Optional[torch.Tensor] = None, tensor_B: Op
     return ctx
 
 
+def pick_comm_ctas(rows_per_rank: int, n_local: int, world: int, block_n: int, n_sms: int) -> int:
+    """Comm CTAs of the fused launch: at least enough push bandwidth for the remote shards to stay ahead of the GEMM
+    (about 45 GB/s per bulk-TMA CTA; a segment of the GEMM consumes its shard in 1/world of the GEMM time), and every
+    SM that the tile count leaves idle in the last wave anyway."""
+    tiles = world * ((rows_per_rank + BLOCK_M - 1) // BLOCK_M) * ((n_local + block_n - 1) // block_n)
+    n_min = 4 if world <= 2 else 8
+    waves = max(1, -(-tiles // (n_sms - n_min)))
+    n_gemm = -(-tiles // waves)
+    return int(max(n_min, min(32, n_sms - n_gemm)))
+
+
 def ag_gemm_reference(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Tensor:
     """all_gather(a) @ b^T with torch.distributed + torch.matmul."""
     return torch.matmul(ref_all_gather(a, group), b.t())
@@ -131,7 +142,7 @@ def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelCo
     if out is None:
         out = torch.empty((m * W, N), dtype=a.dtype, device=a.device)
     n_sms = ctx.num_ctas or sm_count(a.device)
-    n_comm = ctx.n_comm_ctas or 8
+    n_comm = ctx.n_comm_ctas or pick_comm_ctas(m, N, W, ctx.BLOCK_N, n_sms)
     n_comm = max(1, min(n_comm, n_sms - 1))
     lib.ag_gemm_bf16(rt.heap, a, b, out, ctx.workspace, ctx.flags, ctx.ctx_dev, ctx.max_seg_rows, ctx.max_chunks,
                      n_comm, ctx.BLOCK_N, n_sms, bool(ctx.use_multimem and rt.has_multicast), rt.config.wait_timeout_s)

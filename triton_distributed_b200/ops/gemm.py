@@ -13,6 +13,9 @@ import torch
 from .. import _native
 
 
+SKINNY_M = 128   # up to this many rows the weight-streaming kernel wins
+
+
 def gemm_reference(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """fp32 reference: A @ B^T."""
     return (a.float() @ b.float().t()).to(a.dtype)
@@ -31,7 +34,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, b
         a2 = a.reshape(-1, a.shape[-1])
         if out is None:
             out = torch.empty((a2.shape[0], b.shape[0]), dtype=a.dtype, device=a.device)
-        lib.gemm_bf16(a2, b, out.view(a2.shape[0], b.shape[0]), block_n, num_ctas)
+        if 0 < a2.shape[0] <= SKINNY_M and block_n == 0 and a2.shape[1] % 8 == 0:
+            # decode-size M: stream the weights once with the swap-AB split-K kernel
+            from .gemm_ar import skinny_gemm
+            skinny_gemm(a2, b, out=out.view(a2.shape[0], b.shape[0]))
+        else:
+            lib.gemm_bf16(a2, b, out.view(a2.shape[0], b.shape[0]), block_n, num_ctas)
         return out.view(*lead, b.shape[0])
     res = torch.matmul(a, b.t())
     if out is not None:

@@ -1,0 +1,156 @@
+"""Decode-size GEMM (M <= 256) with split-K, and GEMM -> AllReduce in one launch.
+
+API of the reference: ``create_gemm_ar_context`` / ``create_ll_gemm_ar_context`` / ``gemm_allreduce_op`` /
+``low_latency_gemm_allreduce_op`` (python/triton_dist/kernels/nvidia/gemm_allreduce.py:94, :111, :546, :509).
+Inputs ``a`` [M, K/W], ``b`` [N, K/W] (row-parallel weight, K-major) -> ``[M, N]`` summed over the ranks.
+
+GPU path: ``csrc/gemm_ar_sm100.cu`` (swap-AB tcgen05 kernel; the last split-K CTA of every 128-column tile runs that
+tile's cross-rank sum through NVLS ``multimem.ld_reduce`` or peer stores).  For M > 256 the op falls back to the
+large-tile GEMM followed by the all-reduce library.  CPU / reference path: ``matmul`` + ``all_reduce``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .. import _native
+from ..runtime import Runtime, get_runtime
+from .common import new_ctx_dev, ref_all_reduce, sm_count
+
+MAX_SKINNY_M = 256
+_SCRATCH: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _scratch(device, need_acc: int, need_tiles: int):
+    """Per-device split-K scratch (fp32 accumulator + tile counters); the kernel leaves both zeroed."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), 0)
+    cur = _SCRATCH.get(key)
+    if cur is None or cur[0].numel() < need_acc or cur[1].numel() < need_tiles:
+        acc = torch.zeros(max(need_acc, 1 << 20), dtype=torch.float32, device=device)
+        cnt = torch.zeros(max(need_tiles, 4096), dtype=torch.int32, device=device)
+        _SCRATCH[key] = (acc, cnt)
+        cur = _SCRATCH[key]
+    return cur
+
+
+def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, splits: int = 0) -> torch.Tensor:
+    """``x`` [M<=256, K] @ ``w`` [N, K]^T with the weight-streaming split-K kernel."""
+    lib = _native.load(True)
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    acc, cnt = _scratch(x.device, M * N, (N + 127) // 128)
+    lib.skinny_gemm_bf16(x, w, out, acc, cnt, splits, 0)
+    return out
+
+
+@dataclass
+class GemmARContext:
+    rt: Runtime
+    rank: int
+    world_size: int
+    max_M: int
+    N: int
+    dtype: torch.dtype
+    m_cap: int = 0
+    use_multimem: bool = True
+    partial: Optional[torch.Tensor] = None   # heap
+    flags: Optional[torch.Tensor] = None     # heap [W][max_tiles]
+    acc: Optional[torch.Tensor] = None
+    counters: Optional[torch.Tensor] = None
+    ctx_dev: Optional[torch.Tensor] = None
+    max_tiles: int = 0
+    ar_ctx: object = None                    # all-reduce library context for the large-M path
+    calls: int = 0
+
+    def finalize(self):
+        if self.partial is not None:
+            self.rt.symm_free(self.partial)
+            self.rt.symm_free(self.flags)
+            self.partial = None
+        if self.ar_ctx is not None:
+            self.ar_ctx.finalize()
+            self.ar_ctx = None
+
+
+LLGemmARContext = GemmARContext
+
+
+def create_gemm_ar_context(ar_stream=None, rank: Optional[int] = None, world_size: Optional[int] = None,
+                           local_world_size: Optional[int] = None, max_M: int = 256, N: int = 0,
+                           dtype: torch.dtype = torch.bfloat16, MIN_BLOCK_SIZE_M: int = 16, MIN_BLOCK_SIZE_N: int = 16,
+                           NUM_COMM_SMS: int = 132, use_multimem: bool = True) -> GemmARContext:
+    """Allocate the heap partial-tile buffer and per-tile flags (collective call)."""
+    from .allreduce import create_allreduce_ctx
+
+    rt = get_runtime()
+    rank = rt.rank if rank is None else rank
+    world_size = rt.world_size if world_size is None else world_size
+    ctx = GemmARContext(rt=rt, rank=rank, world_size=world_size, max_M=max_M, N=N, dtype=dtype,
+                        use_multimem=use_multimem)
+    if rt.is_cuda and world_size > 1:
+        ctx.m_cap = min(max_M, MAX_SKINNY_M)
+        ctx.max_tiles = (N + 127) // 128
+        slots = 1 if (use_multimem and rt.has_multicast) else world_size
+        ctx.partial = rt.symm_tensor((2, slots, ctx.m_cap, N), dtype, zero=False)
+        ctx.flags = rt.symm_tensor((world_size, ctx.max_tiles), torch.int32)
+        ctx.acc = torch.zeros(ctx.m_cap * N, dtype=torch.float32, device=rt.device)
+        ctx.counters = torch.zeros(ctx.max_tiles, dtype=torch.int32, device=rt.device)
+        ctx.ctx_dev = new_ctx_dev(rt)
+        if max_M > MAX_SKINNY_M:
+            ctx.ar_ctx = create_allreduce_ctx(max(4 * max_M * N * 2, 1 << 20))
+        torch.cuda.synchronize()
+        rt.host_barrier()
+    return ctx
+
+
+def create_ll_gemm_ar_context(rank: Optional[int] = None, world_size: Optional[int] = None,
+                              local_world_size: Optional[int] = None, max_M: int = 256, N: int = 0,
+                              dtype: torch.dtype = torch.bfloat16, MIN_BLOCK_SIZE_M: int = 16,
+                              MIN_BLOCK_SIZE_N: int = 16, NUM_COMM_SMS: int = 16, num_phases: int = 2) -> GemmARContext:
+    return create_gemm_ar_context(None, rank, world_size, local_world_size, max_M, N, dtype)
+
+
+def gemm_ar_reference(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Tensor:
+    return ref_all_reduce(torch.matmul(a, b.t()), group)
+
+
+def gemm_allreduce_op(ctx: GemmARContext, a: torch.Tensor, b: torch.Tensor, cfg=None, output: Optional[torch.Tensor] = None,
+                      straggler_option=None) -> torch.Tensor:
+    """``a`` [M, K_local] @ ``b`` [N, K_local]^T summed over ranks -> [M, N] on every rank."""
+    rt = ctx.rt
+    if not _native.use_native(a, b) or a.dtype != torch.bfloat16:
+        res = gemm_ar_reference(a, b, rt.group)
+        if output is not None:
+            output.copy_(res)
+            return output
+        return res
+    lib = _native.load(True)
+    M, K = a.shape
+    N = b.shape[0]
+    if output is None:
+        output = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    if a.stride(-1) != 1:
+        a = a.contiguous()
+    if ctx.world_size == 1:
+        from .gemm import gemm
+        if M <= MAX_SKINNY_M:
+            return skinny_gemm(a, b, out=output)
+        return gemm(a, b, out=output)
+    if M > ctx.m_cap:
+        from .allreduce import all_reduce
+        from .gemm import gemm
+        part = gemm(a, b)
+        return all_reduce(part, ctx=ctx.ar_ctx, output=output)
+    if N != ctx.N:
+        raise ValueError(f"gemm_allreduce_op: N={N} differs from the context's N={ctx.N}")
+    lib.gemm_ar_bf16(rt.heap, a, b, output, ctx.acc, ctx.counters, ctx.partial, ctx.flags, ctx.ctx_dev, ctx.m_cap,
+                     ctx.max_tiles, 0, 0, bool(ctx.use_multimem), rt.config.wait_timeout_s)
+    ctx.calls += 1
+    return output
+
+
+low_latency_gemm_allreduce_op = gemm_allreduce_op

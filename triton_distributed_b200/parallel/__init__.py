@@ -1,1 +1,5 @@
-"""placeholder, filled in below."""
+"""Parallel layers: TP (MLP / attention / MoE), EP, SP (flash-decode, all-gather attention, Ulysses), PP transport
+(the reference's ``triton_dist.layers.nvidia``)."""
+from .tp_mlp import TP_MLP  # noqa: F401
+from .tp_attn import TP_Attn  # noqa: F401
+from .sp_flash_decode import SpGQAFlashDecodeAttention  # noqa: F401

@@ -246,11 +246,8 @@ class Runtime:
             self._barrier_flags = None
             self.heap.destroy()
             self.heap = None
-        if self._own_pg and dist.is_initialized():
-            try:
-                dist.destroy_process_group()
-            except Exception:
-                pass
+        # The process group is left to torch's own exit handling: destroying it here can block when CUDA graphs that
+        # captured NCCL work are still alive in the caller.
 
 
 class Watchdog:
