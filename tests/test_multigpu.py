@@ -27,3 +27,9 @@ def test_core_without_nvls():
 def test_model_two_gpus():
     out = run_gpu_script("check_model.py", 2)
     assert "MODEL OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
+def test_moe_two_gpus():
+    out = run_gpu_script("check_moe.py", 2)
+    assert "MOE OK" in out

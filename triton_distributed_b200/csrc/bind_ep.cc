@@ -1,0 +1,146 @@
+// Python bindings of the expert-parallel all-to-all kernels.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "tdb/ep.h"
+#include "tdb/symm_heap.h"
+
+namespace py = pybind11;
+using tdb::SymmHeap;
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+void check_cuda(cudaError_t e, const char* what) { TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e)); }
+int32_t* i32(const at::Tensor& t) { return reinterpret_cast<int32_t*>(t.data_ptr()); }
+tdb::CtxDev* ctxp(const at::Tensor& t) { return reinterpret_cast<tdb::CtxDev*>(t.data_ptr()); }
+uint64_t ns(double s) { return static_cast<uint64_t>(s * 1e9); }
+
+void ep_dispatch(SymmHeap& h, const at::Tensor& x, const at::Tensor& topk_ids, int64_t E, bool quant, int64_t max_tokens,
+                 at::Tensor& recv_x, at::Tensor& recv_scale, at::Tensor& recv_meta, at::Tensor& recv_count,
+                 at::Tensor& flags, int64_t rows_per_parity, c10::optional<at::Tensor> base, at::Tensor& cursor,
+                 at::Tensor& sent_row, at::Tensor& ctx, int64_t num_ctas, double timeout_s) {
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(), "ep_dispatch: x bf16 [T,H]");
+  TORCH_CHECK(topk_ids.scalar_type() == at::kInt && topk_ids.dim() == 2 && topk_ids.is_contiguous(), "ep_dispatch: int32 ids [T,k]");
+  TORCH_CHECK(x.size(0) <= max_tokens, "ep_dispatch: more tokens than the context was created for");
+  c10::cuda::CUDAGuard guard(x.device());
+  tdb::EpDispatchArgs a;
+  a.x = x.data_ptr();
+  a.topk_ids = i32(topk_ids);
+  a.T = x.size(0); a.H = x.size(1); a.k = topk_ids.size(1); a.E = E;
+  a.quant = quant ? 1 : 0;
+  a.max_tokens = max_tokens;
+  a.recv_x = recv_x.data_ptr();
+  a.recv_scale = recv_scale.data_ptr<float>();
+  a.recv_meta = i32(recv_meta);
+  a.recv_count = i32(recv_count);
+  a.flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
+  a.rows_per_parity = rows_per_parity;
+  a.base = base.has_value() ? i32(*base) : nullptr;
+  a.cursor = i32(cursor);
+  a.sent_row = i32(sent_row);
+  a.num_ctas = num_ctas;
+  a.ctx = ctxp(ctx);
+  a.symm = h.info(ns(timeout_s));
+  check_cuda(tdb::launch_ep_dispatch(a, cur_stream()), "launch_ep_dispatch");
+}
+
+void ep_count(const at::Tensor& ids, int64_t E, at::Tensor& counts) {
+  check_cuda(tdb::launch_ep_count(i32(ids), ids.numel(), E, i32(counts), cur_stream()), "launch_ep_count");
+}
+void ep_layout(const at::Tensor& counts_all, at::Tensor& base, int64_t epr, int64_t W, int64_t E) {
+  check_cuda(tdb::launch_ep_layout(i32(counts_all), i32(base), epr, W, E, cur_stream()), "launch_ep_layout");
+}
+void ep_recv_ids(const at::Tensor& recv_count, c10::optional<at::Tensor> base_self, at::Tensor& row_expert, int64_t epr,
+                 int64_t W, int64_t max_tokens, const at::Tensor& dispatch_ctx) {
+  check_cuda(tdb::launch_ep_recv_ids(i32(recv_count), base_self.has_value() ? i32(*base_self) : nullptr, i32(row_expert), epr, W,
+                                     max_tokens, row_expert.numel(), ctxp(dispatch_ctx), cur_stream()),
+             "launch_ep_recv_ids");
+}
+at::Tensor ep_gather_rows(const at::Tensor& recv_x, const at::Tensor& recv_scale, const at::Tensor& sorted_ids,
+                          const at::Tensor& meta, int64_t H, bool quant, int64_t rows_per_parity, const at::Tensor& dispatch_ctx) {
+  c10::cuda::CUDAGuard guard(recv_x.device());
+  at::Tensor out = at::empty({sorted_ids.numel(), H}, recv_x.options().dtype(at::kBFloat16));
+  check_cuda(tdb::launch_ep_gather_rows(recv_x.data_ptr(), recv_scale.data_ptr<float>(), i32(sorted_ids), i32(meta), out.data_ptr(),
+                                        sorted_ids.numel(), H, quant ? 1 : 0, rows_per_parity, ctxp(dispatch_ctx), cur_stream()),
+             "launch_ep_gather_rows");
+  return out;
+}
+
+at::Tensor ep_combine(SymmHeap& h, const at::Tensor& y, const at::Tensor& pos_of, const at::Tensor& recv_meta,
+                      const at::Tensor& dispatch_ctx, c10::optional<at::Tensor> base_self, int64_t max_tokens,
+                      int64_t recv_rows, at::Tensor& ret, at::Tensor& flags, const at::Tensor& topk_ids,
+                      c10::optional<at::Tensor> topk_w, int64_t E, at::Tensor& ctx, int64_t num_ctas, double timeout_s) {
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.is_contiguous(), "ep_combine: y bf16 [rows,H]");
+  c10::cuda::CUDAGuard guard(y.device());
+  const int64_t T = topk_ids.size(0), k = topk_ids.size(1), H = y.size(1);
+  at::Tensor out = at::empty({T, H}, y.options());
+  tdb::EpCombineArgs a;
+  a.y = y.data_ptr();
+  a.pos_of = i32(pos_of);
+  a.recv_meta = i32(recv_meta);
+  a.dispatch_ctx = ctxp(dispatch_ctx);
+  a.base_self = base_self.has_value() ? i32(*base_self) : nullptr;
+  a.max_tokens = max_tokens;
+  a.recv_rows = recv_rows;
+  a.ret = ret.data_ptr();
+  a.ret_half = static_cast<uint64_t>(ret.numel()) / 2;
+  a.flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
+  a.topk_ids = i32(topk_ids);
+  a.topk_w = nullptr;
+  if (topk_w.has_value()) {
+    TORCH_CHECK(topk_w->scalar_type() == at::kFloat && topk_w->is_contiguous(), "ep_combine: fp32 weights");
+    a.topk_w = topk_w->data_ptr<float>();
+  }
+  a.out = out.data_ptr();
+  a.T = T; a.H = H; a.k = k; a.E = E;
+  a.num_ctas = num_ctas;
+  a.ctx = ctxp(ctx);
+  a.symm = h.info(ns(timeout_s));
+  TORCH_CHECK(a.ret_half >= static_cast<uint64_t>(T) * k * H, "ep_combine: return buffer too small");
+  check_cuda(tdb::launch_ep_combine(a, cur_stream()), "launch_ep_combine");
+  return out;
+}
+
+void a2a_single(SymmHeap& h, const at::Tensor& in, at::Tensor& out, const at::Tensor& splits_all, at::Tensor& flags,
+                at::Tensor& ctx, int64_t parts, double timeout_s) {
+  TORCH_CHECK(in.is_contiguous() && out.is_contiguous(), "a2a_single: contiguous tensors");
+  const int64_t row_bytes = in.dim() > 1 ? in.stride(0) * in.element_size() : in.element_size();
+  check_cuda(tdb::launch_a2a_single(in.data_ptr(), out.data_ptr(), i32(splits_all), row_bytes,
+                                    reinterpret_cast<uint32_t*>(flags.data_ptr()), ctxp(ctx), h.info(ns(timeout_s)), parts,
+                                    cur_stream()),
+             "launch_a2a_single");
+}
+
+std::vector<at::Tensor> fp8_quant(const at::Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(), "fp8_quant: bf16 [T,H]");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t T = x.size(0), H = x.size(1);
+  at::Tensor q = at::empty({T, H}, x.options().dtype(at::kFloat8_e4m3fn));
+  at::Tensor s = at::empty({T, H / 128}, x.options().dtype(at::kFloat));
+  check_cuda(tdb::launch_fp8_quant(x.data_ptr(), q.data_ptr(), s.data_ptr<float>(), T, H, cur_stream()), "launch_fp8_quant");
+  return {q, s};
+}
+at::Tensor fp8_dequant(const at::Tensor& q, const at::Tensor& s) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 2 && q.is_contiguous() && s.is_contiguous(), "fp8_dequant: [T,H] fp8 + [T,H/128] fp32");
+  c10::cuda::CUDAGuard guard(q.device());
+  at::Tensor out = at::empty({q.size(0), q.size(1)}, q.options().dtype(at::kBFloat16));
+  check_cuda(tdb::launch_fp8_dequant(q.data_ptr(), s.data_ptr<float>(), out.data_ptr(), q.size(0), q.size(1), cur_stream()),
+             "launch_fp8_dequant");
+  return out;
+}
+
+}  // namespace
+
+void bind_ep(py::module_& m) {
+  m.def("ep_dispatch", &ep_dispatch);
+  m.def("ep_count", &ep_count);
+  m.def("ep_layout", &ep_layout);
+  m.def("ep_recv_ids", &ep_recv_ids);
+  m.def("ep_gather_rows", &ep_gather_rows);
+  m.def("ep_combine", &ep_combine);
+  m.def("a2a_single", &a2a_single);
+  m.def("fp8_quant", &fp8_quant);
+  m.def("fp8_dequant", &fp8_dequant);
+}

@@ -1,0 +1,545 @@
+// Expert-parallel all-to-all: dispatch (optionally quantising rows to fp8 e4m3 with one fp32 scale per 128 elements
+// while they are sent) and combine (rows return to the token's owner, where the top-k weighted sum is taken in the same
+// kernel); plus torch.distributed.all_to_all_single semantics with uneven splits, and stand-alone quant / dequant.
+//
+// Reference behaviour being matched (not its code):
+//   low-latency all-to-all   kernels/nvidia/low_latency_all_to_all.py:36-279 (fixed-stride receive areas, split counts
+//                            travel with the data, double buffering by call parity, monotonically increasing signal)
+//   fused fp8 quantisation   tutorials/04-deepseek-infer-all2all.py:93-275 (scale = amax / 448 per 128 elements)
+//   throughput dispatch      kernels/nvidia/ep_a2a.py:38-447 (slot ranges private to the source rank, so only LOCAL
+//                            atomics are needed; slot remembered for combine), layers/nvidia/ep_a2a_layer.py:154-341
+//   all_to_all_single_2d     kernels/nvidia/all_to_all_single_2d.py:41-171
+// Differences by design: receive counts never travel through the CPU; the weighted top-k reduction of combine is fused;
+// all waits are bounded.
+#include <cuda_fp8.h>
+
+#include "tdb/ep.h"
+#include "tdb/symm_device.cuh"
+
+namespace tdb {
+
+namespace {
+
+constexpr int kEpThreads = 256;
+constexpr int kQuantBlock = 128;
+
+TDB_DEVICE uint32_t quant4(float a, float b, float c, float d, float inv_scale) {
+  const uint32_t q0 = __nv_cvt_float_to_fp8(a * inv_scale, __NV_SATFINITE, __NV_E4M3);
+  const uint32_t q1 = __nv_cvt_float_to_fp8(b * inv_scale, __NV_SATFINITE, __NV_E4M3);
+  const uint32_t q2 = __nv_cvt_float_to_fp8(c * inv_scale, __NV_SATFINITE, __NV_E4M3);
+  const uint32_t q3 = __nv_cvt_float_to_fp8(d * inv_scale, __NV_SATFINITE, __NV_E4M3);
+  return q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+}
+TDB_DEVICE float fp8_to_float(uint32_t byte) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+
+// One warp quantises one bf16 row of H elements (H % 128 == 0) into fp8 + H/128 scales and writes both.
+TDB_DEVICE void warp_quant_row(const __nv_bfloat16* src, uint8_t* dst_q, float* dst_s, int H) {
+  const int lane = lane_id();
+  for (int b = 0; b < H / kQuantBlock; ++b) {
+    const uint2 u = *reinterpret_cast<const uint2*>(src + b * kQuantBlock + lane * 4);
+    const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y);
+    float amax = fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y)));
+    amax = fmaxf(warp_max(amax), 1e-10f);
+    const float scale = amax / 448.f;
+    reinterpret_cast<uint32_t*>(dst_q + b * kQuantBlock)[lane] = quant4(f0.x, f0.y, f1.x, f1.y, 1.f / scale);
+    if (lane == 0) dst_s[b] = scale;
+  }
+}
+
+struct DispatchParams {
+  const __nv_bfloat16* x;        // [T, H] local tokens
+  const int32_t* topk_ids;       // [T, k] global expert ids (>= E or < 0: dropped)
+  int T, H, k, E, epr;
+  int quant;                     // 1: send fp8 + scales
+  int max_tokens;                // per-rank token capacity M
+  // heap (symmetric) receive side, indexed [parity]
+  uint8_t* recv_x;               // rows of row_bytes
+  float* recv_scale;             // [rows][H/128]
+  int32_t* recv_meta;            // [rows] source pair index t*k+j
+  int32_t* recv_count;           // [epr][W]
+  uint32_t* flags;               // [W] epoch per source
+  uint64_t rows_per_parity;
+  // slot layout
+  const int32_t* base;           // [W dst][epr][W src] first row of (dst, local expert, src) on dst; null = fixed stride
+  int32_t* cursor;               // local [E] (zero on entry)
+  int32_t* sent_row;             // local [T*k] row each pair went to (-1 dropped)
+  CtxDev* ctx;
+  SymmInfo symm;
+  int wait_recv;                 // the last CTA also waits for all sources' flags
+};
+
+__global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const DispatchParams p) {
+  const uint32_t epoch = ld_volatile(&p.ctx->epoch);
+  const int par = epoch & 1;
+  const int W = p.symm.world, rank = p.symm.rank;
+  const int warps = kEpThreads / 32;
+  const int lane = threadIdx.x & 31;
+  const int row_bytes = p.quant ? p.H : p.H * 2;
+  const int nsc = p.H / kQuantBlock;
+  uint8_t* rx = p.recv_x + par * p.rows_per_parity * row_bytes;
+  float* rs = p.recv_scale + par * p.rows_per_parity * nsc;
+  int32_t* rm = p.recv_meta + par * p.rows_per_parity;
+  const int64_t pairs = static_cast<int64_t>(p.T) * p.k;
+  for (int64_t pr = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); pr < pairs;
+       pr += static_cast<int64_t>(gridDim.x) * warps) {
+    const int e = p.topk_ids[pr];
+    if (e < 0 || e >= p.E) {
+      if (lane == 0) p.sent_row[pr] = -1;
+      continue;
+    }
+    const int dst = e / p.epr, le = e - dst * p.epr;
+    int idx = 0;
+    if (lane == 0) idx = atomicAdd(p.cursor + e, 1);
+    idx = __shfl_sync(0xffffffffu, idx, 0);
+    const int64_t base = p.base ? p.base[(static_cast<int64_t>(dst) * p.epr + le) * W + rank]
+                                : (static_cast<int64_t>(le) * W + rank) * p.max_tokens;
+    const int64_t row = base + idx;
+    if (lane == 0) p.sent_row[pr] = static_cast<int32_t>(row);
+    const __nv_bfloat16* src = p.x + (pr / p.k) * p.H;
+    uint8_t* drow = symm_at(p.symm, rx + row * row_bytes, dst);
+    if (p.quant) {
+      warp_quant_row(src, drow, symm_at(p.symm, rs + row * nsc, dst), p.H);
+    } else {
+      for (int i = lane; i < (p.H >> 3); i += 32) st_v4(drow + i * 16, ld_nc_v4(src + i * 8));
+    }
+    if (lane == 0) *symm_at(p.symm, rm + row, dst) = static_cast<int32_t>(pr);
+  }
+  // ---- completion: the last CTA of the grid publishes counts and flags
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(&p.ctx->grid_bar, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    int32_t* rc = p.recv_count + par * p.epr * W;
+    for (int i = threadIdx.x; i < p.E; i += kEpThreads) {
+      const int dst = i / p.epr, le = i - dst * p.epr;
+      *symm_at(p.symm, rc + le * W + rank, dst) = p.cursor[i];
+      p.cursor[i] = 0;   // ready for the next call
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x < W) {
+      fence_acq_rel_sys();
+      st_release_sys(symm_at(p.symm, p.flags + rank, (rank + threadIdx.x) % W), epoch);
+      if (p.wait_recv) ok = wait_until(p.symm, p.flags + threadIdx.x, epoch, kCmpGe, kKernelEpDispatch, 1, threadIdx.x, 0);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      p.ctx->grid_bar = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(&p.ctx->epoch) = epoch + 1;
+    }
+  }
+}
+
+// For every receive row of the previous dispatch (its parity): expert id of the row (local expert index) or `epr`
+// (= "no token") so that the generic sort kernel can build the grouped-GEMM layout.
+// Parity of the receive buffers the last finished dispatch of `dctx` wrote (it has already advanced the epoch).
+TDB_DEVICE int last_parity(const CtxDev* dctx) { return static_cast<int>((ld_volatile(&dctx->epoch) + 1u) & 1u); }
+
+__global__ void ep_recv_ids_kernel(const int32_t* __restrict__ recv_count_base, const int32_t* __restrict__ base_self,
+                                   int32_t* __restrict__ row_expert, int epr, int W, int max_tokens, int64_t rows,
+                                   const CtxDev* dctx) {
+  const int32_t* recv_count = recv_count_base + last_parity(dctx) * epr * W;
+  // fixed stride: row = (le * W + src) * max_tokens + i ; packed: rows of (le, src) start at base_self[le * W + src]
+  for (int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; r < rows;
+       r += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int ex = epr;
+    if (base_self == nullptr) {
+      const int64_t blk = r / max_tokens;
+      const int i = static_cast<int>(r - blk * max_tokens);
+      if (blk < static_cast<int64_t>(epr) * W && i < recv_count[blk]) ex = static_cast<int>(blk / W);
+    } else {
+      // binary search over the (le, src) blocks
+      int lo = 0, hi = epr * W - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (base_self[mid] <= r) lo = mid; else hi = mid - 1;
+      }
+      if (r - base_self[lo] < recv_count[lo]) ex = lo / W;
+    }
+    row_expert[r] = ex;
+  }
+}
+
+// Exclusive offsets of the packed layout: base[d][le][s] = sum of counts[s'][d*epr+le'] over (le', s') before (le, s).
+// counts_all [W src][E] (all-gathered).  One CTA per destination rank.
+__global__ void ep_layout_kernel(const int32_t* __restrict__ counts_all, int32_t* __restrict__ base, int epr, int W, int E) {
+  const int d = blockIdx.x;
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int le = 0; le < epr; ++le) {
+      for (int s = 0; s < W; ++s) {
+        base[(static_cast<int64_t>(d) * epr + le) * W + s] = acc;
+        acc += counts_all[static_cast<int64_t>(s) * E + d * epr + le];
+      }
+    }
+  }
+}
+
+// counts[e] per expert of the local routing (for the throughput layout exchange)
+__global__ void ep_count_kernel(const int32_t* __restrict__ ids, int64_t n, int E, int32_t* counts) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(counts + e, 1);
+  }
+}
+
+// Gather receive rows into the expert-sorted layout, de-quantising fp8 rows on the way.
+__global__ void ep_gather_rows_kernel(const uint8_t* __restrict__ recv_x_base, const float* __restrict__ recv_scale_base,
+                                      const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ meta,
+                                      __nv_bfloat16* __restrict__ out, int H, int quant, int64_t rows_per_parity,
+                                      const CtxDev* dctx) {
+  const int par = last_parity(dctx);
+  const uint8_t* recv_x = recv_x_base + par * rows_per_parity * (quant ? H : 2 * H);
+  const float* recv_scale = recv_scale_base + par * rows_per_parity * (H / kQuantBlock);
+  const int64_t r = blockIdx.x;
+  if (r >= meta[0]) return;
+  const int id = sorted_ids[r];
+  __nv_bfloat16* dst = out + r * H;
+  if (id < 0) {
+    for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  if (!quant) {
+    const uint4* s = reinterpret_cast<const uint4*>(recv_x + static_cast<int64_t>(id) * H * 2);
+    for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = s[i];
+    return;
+  }
+  const uint8_t* q = recv_x + static_cast<int64_t>(id) * H;
+  const float* sc = recv_scale + static_cast<int64_t>(id) * (H / kQuantBlock);
+  for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
+    const uint32_t w = reinterpret_cast<const uint32_t*>(q)[i];
+    const float s = sc[(i * 4) / kQuantBlock];
+    uint2 o;
+    o.x = pack_bf16x2(fp8_to_float(w & 0xff) * s, fp8_to_float((w >> 8) & 0xff) * s);
+    o.y = pack_bf16x2(fp8_to_float((w >> 16) & 0xff) * s, fp8_to_float(w >> 24) * s);
+    reinterpret_cast<uint2*>(dst)[i] = o;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Combine: y_sorted rows (expert outputs, bf16) go back to the source rank of their token, into ret[pair]; when all
+// expert ranks have flagged, every CTA reduces its share of the local tokens: out[t] = sum_j w[t,j] * ret[t*k+j].
+// ---------------------------------------------------------------------------
+struct CombineParams {
+  const __nv_bfloat16* y;        // [rows_sorted, H] expert outputs in the sorted layout
+  const int32_t* pos_of;         // [recv rows] sorted row of every receive row (-1: no token)
+  const int32_t* recv_meta;      // [2][recv rows] pair index at the source (parity of the matching dispatch)
+  const CtxDev* dctx;            // the dispatch context (gives that parity)
+  const int32_t* base_self;      // packed layout: [epr*W] first row of block; null = fixed stride
+  int epr, max_tokens;
+  int64_t recv_rows;
+  __nv_bfloat16* ret;            // heap [2][max_tokens*k][H]
+  uint64_t ret_half;             // elements per parity
+  uint32_t* flags;               // heap [W]
+  // local reduction
+  const int32_t* topk_ids;       // [T, k]
+  const float* topk_w;           // [T, k] or null
+  __nv_bfloat16* out;            // [T, H]
+  int T, H, k, E;
+  CtxDev* ctx;
+  SymmInfo symm;
+};
+
+__global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const CombineParams p) {
+  const uint32_t epoch = ld_volatile(&p.ctx->epoch);
+  const int par = epoch & 1;
+  const int W = p.symm.world, rank = p.symm.rank;
+  const int warps = kEpThreads / 32, lane = threadIdx.x & 31;
+  __nv_bfloat16* ret = p.ret + par * p.ret_half;
+  const int32_t* recv_meta = p.recv_meta + last_parity(p.dctx) * p.recv_rows;
+  // ---- send: one warp per receive row
+  const int blocks = p.epr * W;
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); r < p.recv_rows;
+       r += static_cast<int64_t>(gridDim.x) * warps) {
+    const int pos = p.pos_of[r];
+    if (pos < 0) continue;
+    int src;
+    if (p.base_self == nullptr) {
+      src = static_cast<int>((r / p.max_tokens) % W);
+    } else {
+      int lo = 0, hi = blocks - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (p.base_self[mid] <= r) lo = mid; else hi = mid - 1;
+      }
+      src = lo % W;
+    }
+    const int pair = recv_meta[r];
+    const uint4* s = reinterpret_cast<const uint4*>(p.y + static_cast<int64_t>(pos) * p.H);
+    uint4* d = reinterpret_cast<uint4*>(symm_at(p.symm, ret + static_cast<int64_t>(pair) * p.H, src));
+    for (int i = lane; i < (p.H >> 3); i += 32) st_v4(d + i, s[i]);
+  }
+  __shared__ int s_last;
+  __shared__ int s_ok;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(&p.ctx->grid_bar, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    s_ok = 1;
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x < W) {
+    __threadfence();
+    fence_acq_rel_sys();
+    st_release_sys(symm_at(p.symm, p.flags + rank, (rank + threadIdx.x) % W), epoch);
+  }
+  // ---- wait for every expert rank, then reduce
+  if (threadIdx.x < W) {
+    if (!wait_until(p.symm, p.flags + threadIdx.x, epoch, kCmpGe, kKernelEpCombine, 1, threadIdx.x, 0)) s_ok = 0;
+  }
+  __syncthreads();
+  if (s_ok) {
+    for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+      for (int i = threadIdx.x; i < (p.H >> 3); i += kEpThreads) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < p.k; ++j) {
+          const int e = p.topk_ids[t * p.k + j];
+          if (e < 0 || e >= p.E) continue;
+          const float wj = p.topk_w ? p.topk_w[t * p.k + j] : 1.f;
+          const uint4 u = ld_relaxed_sys_v4(ret + (static_cast<int64_t>(t) * p.k + j) * p.H + i * 8);
+          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+          acc[0] += wj * f0.x; acc[1] += wj * f0.y; acc[2] += wj * f1.x; acc[3] += wj * f1.y;
+          acc[4] += wj * f2.x; acc[5] += wj * f2.y; acc[6] += wj * f3.x; acc[7] += wj * f3.y;
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+        reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(t) * p.H)[i] = o;
+      }
+    }
+  }
+  // ---- last CTA out advances the epoch (second counter: `done`)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(&p.ctx->done, 1u);
+    if (prev == gridDim.x - 1) {
+      p.ctx->done = 0;
+      p.ctx->grid_bar = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(&p.ctx->epoch) = epoch + 1;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// all_to_all_single with uneven splits: rows [in_off[d], in_off[d+1]) of `in` go to rank d, which stores the rows of
+// source s at out_off[d][s] = sum of splits[s'][d] for s' < s.  splits_all [W src][W dst] all-gathered beforehand.
+// out lives in the heap; the kernel returns when all sources' rows have arrived.
+// ---------------------------------------------------------------------------
+struct A2AParams {
+  const char* in;
+  char* out;                    // heap
+  const int32_t* splits_all;    // [W][W]
+  int64_t row_bytes;
+  uint32_t* flags;              // heap [W]
+  CtxDev* ctx;
+  SymmInfo symm;
+};
+
+__global__ void __launch_bounds__(kEpThreads) a2a_single_kernel(const A2AParams p) {
+  const uint32_t epoch = ld_volatile(&p.ctx->epoch);
+  const int W = p.symm.world, rank = p.symm.rank;
+  // CTA b serves destination b % W, part b / W of gridDim.x / W parts
+  const int parts = gridDim.x / W;
+  const int dst = blockIdx.x % W, part = blockIdx.x / W;
+  if (part < parts) {
+    int64_t in_row = 0;
+    for (int d = 0; d < dst; ++d) in_row += p.splits_all[rank * W + d];
+    int64_t out_row = 0;
+    for (int s = 0; s < rank; ++s) out_row += p.splits_all[s * W + dst];
+    const int64_t bytes = static_cast<int64_t>(p.splits_all[rank * W + dst]) * p.row_bytes;
+    const int64_t per = ((bytes / 16 + parts - 1) / parts) * 16;
+    const int64_t lo = min(bytes, per * part), hi = min(bytes, lo + per);
+    const char* s = p.in + in_row * p.row_bytes;
+    char* d = symm_at(p.symm, p.out + out_row * p.row_bytes, dst);
+    for (int64_t i = lo + threadIdx.x * 16; i < hi; i += static_cast<int64_t>(kEpThreads) * 16) st_v4(d + i, ld_nc_v4(s + i));
+  }
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(&p.ctx->grid_bar, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x < W) {
+      __threadfence();
+      fence_acq_rel_sys();
+      st_release_sys(symm_at(p.symm, p.flags + rank, (rank + threadIdx.x) % W), epoch);
+      wait_until(p.symm, p.flags + threadIdx.x, epoch, kCmpGe, kKernelA2A, 1, threadIdx.x, 0);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      p.ctx->grid_bar = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(&p.ctx->epoch) = epoch + 1;
+    }
+  }
+}
+
+// ---- stand-alone quantisation ---------------------------------------------------------------------------------
+__global__ void fp8_quant_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ s, int64_t T,
+                                 int H) {
+  const int warps = blockDim.x >> 5;
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); t < T;
+       t += static_cast<int64_t>(gridDim.x) * warps)
+    warp_quant_row(x + t * H, q + t * H, s + t * (H / kQuantBlock), H);
+}
+__global__ void fp8_dequant_kernel(const uint8_t* __restrict__ q, const float* __restrict__ s, __nv_bfloat16* __restrict__ out,
+                                   int64_t T, int H) {
+  const int64_t n4 = T * H / 4;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint32_t w = reinterpret_cast<const uint32_t*>(q)[i];
+    const int64_t el = i * 4;
+    const float sc = s[(el / H) * (H / kQuantBlock) + (el % H) / kQuantBlock];
+    uint2 o;
+    o.x = pack_bf16x2(fp8_to_float(w & 0xff) * sc, fp8_to_float((w >> 8) & 0xff) * sc);
+    o.y = pack_bf16x2(fp8_to_float((w >> 16) & 0xff) * sc, fp8_to_float(w >> 24) * sc);
+    reinterpret_cast<uint2*>(out)[i] = o;
+  }
+}
+
+SymmInfo to_dev(const SymmInfoHost& h) {
+  SymmInfo s;
+  static_assert(sizeof(SymmInfo) == sizeof(SymmInfoHost), "SymmInfo mirrors must match");
+  memcpy(&s, &h, sizeof(s));
+  return s;
+}
+
+int grid_1d(int64_t n, int threads, int cap) {
+  int64_t g = (n + threads - 1) / threads;
+  return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace
+
+cudaError_t launch_ep_dispatch(const EpDispatchArgs& a, cudaStream_t s) {
+  if (a.H % kQuantBlock != 0 || a.E % a.symm.world != 0) return cudaErrorInvalidValue;
+  DispatchParams p;
+  p.x = reinterpret_cast<const __nv_bfloat16*>(a.x);
+  p.topk_ids = a.topk_ids;
+  p.T = a.T; p.H = a.H; p.k = a.k; p.E = a.E;
+  p.epr = a.E / a.symm.world;
+  p.quant = a.quant;
+  p.max_tokens = a.max_tokens;
+  p.recv_x = reinterpret_cast<uint8_t*>(a.recv_x);
+  p.recv_scale = a.recv_scale;
+  p.recv_meta = a.recv_meta;
+  p.recv_count = a.recv_count;
+  p.flags = a.flags;
+  p.rows_per_parity = a.rows_per_parity;
+  p.base = a.base;
+  p.cursor = a.cursor;
+  p.sent_row = a.sent_row;
+  p.ctx = a.ctx;
+  p.symm = to_dev(a.symm);
+  p.wait_recv = 1;
+  const int ctas = a.num_ctas > 0 ? a.num_ctas : 64;
+  ep_dispatch_kernel<<<ctas, kEpThreads, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_count(const int32_t* ids, int64_t n, int E, int32_t* counts, cudaStream_t s) {
+  cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int32_t) * E, s);
+  if (e != cudaSuccess) return e;
+  if (n > 0) ep_count_kernel<<<grid_1d(n, 256, 296), 256, 0, s>>>(ids, n, E, counts);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_layout(const int32_t* counts_all, int32_t* base, int epr, int W, int E, cudaStream_t s) {
+  ep_layout_kernel<<<W, 32, 0, s>>>(counts_all, base, epr, W, E);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_recv_ids(const int32_t* recv_count, const int32_t* base_self, int32_t* row_expert, int epr, int W,
+                               int max_tokens, int64_t rows, const CtxDev* dispatch_ctx, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  ep_recv_ids_kernel<<<grid_1d(rows, 256, 592), 256, 0, s>>>(recv_count, base_self, row_expert, epr, W, max_tokens, rows,
+                                                             dispatch_ctx);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_gather_rows(const void* recv_x, const float* recv_scale, const int32_t* sorted_ids, const int32_t* meta,
+                                  void* out, int64_t rows_cap, int H, int quant, int64_t rows_per_parity,
+                                  const CtxDev* dispatch_ctx, cudaStream_t s) {
+  if (rows_cap == 0) return cudaSuccess;
+  ep_gather_rows_kernel<<<static_cast<unsigned>(rows_cap), 128, 0, s>>>(reinterpret_cast<const uint8_t*>(recv_x), recv_scale,
+                                                                       sorted_ids, meta, reinterpret_cast<__nv_bfloat16*>(out),
+                                                                       H, quant, rows_per_parity, dispatch_ctx);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_combine(const EpCombineArgs& a, cudaStream_t s) {
+  if (a.H % 8 != 0) return cudaErrorInvalidValue;
+  CombineParams p;
+  p.y = reinterpret_cast<const __nv_bfloat16*>(a.y);
+  p.pos_of = a.pos_of;
+  p.recv_meta = a.recv_meta;
+  p.dctx = a.dispatch_ctx;
+  p.base_self = a.base_self;
+  p.epr = a.E / a.symm.world;
+  p.max_tokens = a.max_tokens;
+  p.recv_rows = a.recv_rows;
+  p.ret = reinterpret_cast<__nv_bfloat16*>(a.ret);
+  p.ret_half = a.ret_half;
+  p.flags = a.flags;
+  p.topk_ids = a.topk_ids;
+  p.topk_w = a.topk_w;
+  p.out = reinterpret_cast<__nv_bfloat16*>(a.out);
+  p.T = a.T; p.H = a.H; p.k = a.k; p.E = a.E;
+  p.ctx = a.ctx;
+  p.symm = to_dev(a.symm);
+  int ctas = a.num_ctas > 0 ? a.num_ctas : 64;
+  if (ctas > 128) ctas = 128;   // every CTA waits on remote flags: the grid must be resident
+  ep_combine_kernel<<<ctas, kEpThreads, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_a2a_single(const void* in, void* out, const int32_t* splits_all, int64_t row_bytes, uint32_t* flags,
+                              CtxDev* ctx, const SymmInfoHost& symm, int parts, cudaStream_t s) {
+  if (row_bytes % 16 != 0) return cudaErrorInvalidValue;
+  A2AParams p;
+  p.in = reinterpret_cast<const char*>(in);
+  p.out = reinterpret_cast<char*>(out);
+  p.splits_all = splits_all;
+  p.row_bytes = row_bytes;
+  p.flags = flags;
+  p.ctx = ctx;
+  p.symm = to_dev(symm);
+  if (parts < 1) parts = 1;
+  a2a_single_kernel<<<symm.world * parts, kEpThreads, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fp8_quant(const void* x, void* q, float* scales, int64_t T, int H, cudaStream_t s) {
+  if (H % kQuantBlock != 0) return cudaErrorInvalidValue;
+  if (T == 0) return cudaSuccess;
+  fp8_quant_kernel<<<grid_1d(T, 8, 592), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<uint8_t*>(q),
+                                                      scales, T, H);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fp8_dequant(const void* q, const float* scales, void* out, int64_t T, int H, cudaStream_t s) {
+  if (H % kQuantBlock != 0) return cudaErrorInvalidValue;
+  if (T == 0) return cudaSuccess;
+  fp8_dequant_kernel<<<grid_1d(T * H / 4, 256, 1184), 256, 0, s>>>(reinterpret_cast<const uint8_t*>(q), scales,
+                                                                  reinterpret_cast<__nv_bfloat16*>(out), T, H);
+  return cudaGetLastError();
+}
+
+}  // namespace tdb

@@ -93,6 +93,7 @@ struct KParams {
   int max_tiles;
   __nv_bfloat16* rs_out;
   int64_t ld_out;
+  const int32_t* tile_expert;   // grouped GEMM: expert (third coordinate of B) of every M tile, < 0 = skip the tile
   CtxDev* ctx;
   SymmInfo symm;
 };
@@ -399,6 +400,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         bool ok = true;
         for (int t = g_idx; t < num_tiles && ok; t += n_gemm) {
           const Tile tl = decode_tile(p, t, BN);
+          const int expert = p.tile_expert ? __ldg(p.tile_expert + tl.mt) : 0;
+          if (expert < 0) continue;
           // all-gather mode: the local shard is read where it is, remote shards from the workspace once they arrived
           const bool local_seg = (p.mode == kGemmAllGather) && tl.seg == p.symm.rank;
           if (p.mode == kGemmAllGather && !local_seg) {
@@ -423,7 +426,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             } else {
               tma_load_3d(sa, &tmap_a, &full_bar[s], kb * kBK, tl.m0, (p.mode == kGemmAllGather) ? buf : 0);
             }
-            tma_load_3d(sb, &tmap_b, &full_bar[s], kb * kBK, tl.n0, 0);
+            tma_load_3d(sb, &tmap_b, &full_bar[s], kb * kBK, tl.n0, expert);
             ++issued;
           }
         }
@@ -442,9 +445,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         uint32_t it = 0;
         int local = 0;
         bool ok = true;
-        for (int t = g_idx; t < num_tiles && ok; t += n_gemm, ++local) {
+        for (int t = g_idx; t < num_tiles && ok; t += n_gemm) {
+          if (p.tile_expert) {
+            const Tile tl = decode_tile(p, t, BN);
+            if (__ldg(p.tile_expert + tl.mt) < 0) continue;
+          }
           const int b = local & 1;
           const uint32_t aph = (local >> 1) & 1;
+          ++local;
           if (!mbar_wait(&tmem_empty[b], aph ^ 1, abort_flag, kMbarTimeoutNs)) {
             ok = false;
             report(p.symm, kTimeoutMbarrier, kKernelGemm, 20, -1, b, (int)aph, t);
@@ -484,10 +492,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t chunk_ctr = 0;   // staging buffers alternate over all chunks of all tiles
       int local = 0;
       bool ok = true;
-      for (int t = g_idx; t < num_tiles && ok; t += n_gemm, ++local) {
+      for (int t = g_idx; t < num_tiles && ok; t += n_gemm) {
         const Tile tl = decode_tile(p, t, BN);
+        if (p.tile_expert && __ldg(p.tile_expert + tl.mt) < 0) continue;
         const int b = local & 1;
         const uint32_t aph = (local >> 1) & 1;
+        ++local;
         if (!mbar_wait(&tmem_full[b], aph, abort_flag, kMbarTimeoutNs)) {
           ok = false;
           if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemm, 30, -1, b, (int)aph, t);
@@ -666,6 +676,7 @@ cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
   p.max_tiles = a.max_tiles;
   p.rs_out = reinterpret_cast<__nv_bfloat16*>(a.rs_out);
   p.ld_out = a.ld_out;
+  p.tile_expert = a.tile_expert;
   p.ctx = a.ctx;
   static_assert(sizeof(SymmInfo) == sizeof(SymmInfoHost), "SymmInfo mirrors must match");
   memcpy(&p.symm, &a.symm, sizeof(SymmInfo));

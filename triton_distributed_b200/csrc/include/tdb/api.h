@@ -82,6 +82,7 @@ struct GemmArgs {
   int max_tiles;
   void* rs_out;          // [seg_rows, N] bf16
   int64_t ld_out;
+  const int32_t* tile_expert;  // grouped GEMM (plain mode): expert of each 128-row tile (B is [experts][N][K]), <0 skips
   CtxDev* ctx;           // device memory
   SymmInfoHost symm;
   int use_multimem;      // all-gather push through the multicast mapping

@@ -1,0 +1,61 @@
+// Host API of the expert-parallel all-to-all kernels (ep_a2a.cu).
+#pragma once
+#include "api.h"
+
+namespace tdb {
+
+struct EpDispatchArgs {
+  const void* x;              // bf16 [T, H] local tokens
+  const int32_t* topk_ids;    // [T, k] global expert ids; outside [0, E) = dropped
+  int T, H, k, E;
+  int quant;                  // 1: rows travel as fp8 e4m3 + one fp32 scale per 128 elements
+  int max_tokens;             // per-rank token capacity of the context
+  void* recv_x;               // heap [2][rows_per_parity][row bytes]
+  float* recv_scale;          // heap [2][rows_per_parity][H/128]
+  int32_t* recv_meta;         // heap [2][rows_per_parity]
+  int32_t* recv_count;        // heap [2][E/W][W]
+  uint32_t* flags;            // heap [W]
+  uint64_t rows_per_parity;
+  const int32_t* base;        // [W][E/W][W] packed layout offsets, or null for the fixed-stride layout
+  int32_t* cursor;            // local [E], zero on entry (the kernel leaves it zero)
+  int32_t* sent_row;          // local [T*k]
+  int num_ctas;
+  CtxDev* ctx;
+  SymmInfoHost symm;
+};
+cudaError_t launch_ep_dispatch(const EpDispatchArgs& a, cudaStream_t s);
+cudaError_t launch_ep_count(const int32_t* ids, int64_t n, int E, int32_t* counts, cudaStream_t s);
+cudaError_t launch_ep_layout(const int32_t* counts_all, int32_t* base, int epr, int W, int E, cudaStream_t s);
+cudaError_t launch_ep_recv_ids(const int32_t* recv_count, const int32_t* base_self, int32_t* row_expert, int epr, int W,
+                               int max_tokens, int64_t rows, const CtxDev* dispatch_ctx, cudaStream_t s);
+cudaError_t launch_ep_gather_rows(const void* recv_x, const float* recv_scale, const int32_t* sorted_ids, const int32_t* meta,
+                                  void* out, int64_t rows_cap, int H, int quant, int64_t rows_per_parity,
+                                  const CtxDev* dispatch_ctx, cudaStream_t s);
+
+struct EpCombineArgs {
+  const void* y;              // bf16 [sorted rows, H]
+  const int32_t* pos_of;      // [recv rows]
+  const int32_t* recv_meta;   // heap [2][recv rows]
+  const CtxDev* dispatch_ctx;
+  const int32_t* base_self;   // [E/W * W] packed layout, or null
+  int max_tokens;
+  int64_t recv_rows;
+  void* ret;                  // heap [2][max_tokens*k][H] bf16
+  uint64_t ret_half;
+  uint32_t* flags;            // heap [W]
+  const int32_t* topk_ids;
+  const float* topk_w;        // may be null
+  void* out;                  // bf16 [T, H]
+  int T, H, k, E;
+  int num_ctas;
+  CtxDev* ctx;
+  SymmInfoHost symm;
+};
+cudaError_t launch_ep_combine(const EpCombineArgs& a, cudaStream_t s);
+
+cudaError_t launch_a2a_single(const void* in, void* out, const int32_t* splits_all, int64_t row_bytes, uint32_t* flags,
+                              CtxDev* ctx, const SymmInfoHost& symm, int parts, cudaStream_t s);
+cudaError_t launch_fp8_quant(const void* x, void* q, float* scales, int64_t T, int H, cudaStream_t s);
+cudaError_t launch_fp8_dequant(const void* q, const float* scales, void* out, int64_t T, int H, cudaStream_t s);
+
+}  // namespace tdb

@@ -18,3 +18,10 @@ from .attention import (flash_attn_varlen, gqa_fwd_batch_decode, gqa_fwd_batch_d
                         dense_block_table, decode_workspace, pick_kv_splits)
 from .gemm_ar import (GemmARContext, LLGemmARContext, create_gemm_ar_context, create_ll_gemm_ar_context,  # noqa: F401
                       gemm_allreduce_op, low_latency_gemm_allreduce_op, skinny_gemm, gemm_ar_reference)
+from .moe import (topk_router, sort_topk_ids_align_block_size, calc_gather_scatter_index, group_gemm_sorted,  # noqa: F401
+                  gather_sorted, reduce_topk, unsort, MoESort, create_ag_group_gemm_context, ag_group_gemm,
+                  create_moe_rs_context, create_moe_ar_context, run_moe_reduce_rs, run_moe_reduce_ar,
+                  topk_router_reference, group_gemm_reference, moe_reduce_reference)
+from .ep_a2a import (AllToAllContext, EpRecv, create_all_to_all_context, ep_dispatch, ep_combine, fast_all_to_all,  # noqa: F401
+                     all_to_all_post_process, fp8_quant, fp8_dequant)
+from .all_to_all import (AllToAllSingle2DContext, create_all_to_all_single_2d_context, all_to_all_single_2d)  # noqa: F401

@@ -2,4 +2,6 @@
 (the reference's ``triton_dist.layers.nvidia``)."""
 from .tp_mlp import TP_MLP  # noqa: F401
 from .tp_attn import TP_Attn  # noqa: F401
+from .tp_moe import TP_MoE  # noqa: F401
+from .ep_layer import EPAll2AllLayer, EP_MoE  # noqa: F401
 from .sp_flash_decode import SpGQAFlashDecodeAttention  # noqa: F401
