@@ -229,11 +229,13 @@ void abs_sum(const at::Tensor& x, at::Tensor& out) {
 void bind_attn(py::module_& m);
 void bind_moe(py::module_& m);
 void bind_ep(py::module_& m);
+void bind_mega(py::module_& m);
 
 void bind_more(py::module_& m) {
   bind_attn(m);
   bind_moe(m);
   bind_ep(m);
+  bind_mega(m);
   m.def("all_reduce", &all_reduce);
   m.def("barrier_all", &barrier_all);
   m.def("all_gather", &all_gather);
