@@ -352,14 +352,29 @@ cudaError_t launch_t(const SkinnyGemmArgs& a, const KP& p, int grid, cudaStream_
 
 int skinny_gemm_mpad(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : M <= 256 ? 256 : -1; }
 
-int skinny_gemm_pick_splits(int N, int K, int num_sms) {
+int skinny_gemm_pick_splits(int N, int K, int num_sms, int M) {
+  // A work item is (128 columns, one K split); items run in rounds of `num_sms`.  Pick the split count that
+  // minimises rounds x (time of one item), keeping at least 6 k-blocks per item so that the
+  // pipeline fill does not dominate; the fp32 accumulation traffic of the splits (M x N x 8 bytes per split against
+  // N x K x 2 bytes of weights) is charged too.
   const int tiles = (N + kTN - 1) / kTN;
   const int kb = (K + kBK - 1) / kBK;
-  int s = num_sms / tiles;
-  if (s < 1) s = 1;
-  if (s > kb / 4) s = kb / 4 > 0 ? kb / 4 : 1;   // at least 4 k-blocks per split
-  if (s > 16) s = 16;
-  return s;
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 16; ++s) {
+    if (s > 1 && kb / s < 6) break;
+    const int items = tiles * s;
+    const int rounds = (items + num_sms - 1) / num_sms;
+    // time of one item in k-block units: its share of K, a fixed fill / drain / hand-over cost, and the atomics of
+    // a split accumulation (M x 128 fp32 per item)
+    const double item = (kb + s - 1) / s + 6.0 + (s > 1 ? M / 16.0 : 0.0);
+    const double cost = rounds * item;
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
 }
 
 cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream) {

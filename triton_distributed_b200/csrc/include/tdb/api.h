@@ -115,6 +115,6 @@ struct SkinnyGemmArgs {
 };
 cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream);
 int skinny_gemm_mpad(int M);
-int skinny_gemm_pick_splits(int N, int K, int num_sms);
+int skinny_gemm_pick_splits(int N, int K, int num_sms, int M);
 
 }  // namespace tdb

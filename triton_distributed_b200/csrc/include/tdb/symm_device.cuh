@@ -116,16 +116,15 @@ TDB_DEVICE bool wait_until(const SymmInfo& s, const uint32_t* flag, uint32_t exp
   while (true) {
     v = ld_acquire_sys(flag);
     if (cmp_ok(v, expected, cmp)) return true;
-    if ((++it & 63u) == 0u) {
-      if (abort_requested(s)) {
-        report(s, kAborted, kernel, where, peer, index, (int)expected, (int)v);
-        return false;
-      }
-      if (globaltimer_ns() - t0 > s.timeout_ns) {
-        report(s, kTimeoutFlag, kernel, where, peer, index, (int)expected, (int)v);
-        return false;
-      }
-      nanosleep(20);
+    ++it;
+    if ((it & 255u) == 0u && globaltimer_ns() - t0 > s.timeout_ns) {
+      report(s, kTimeoutFlag, kernel, where, peer, index, (int)expected, (int)v);
+      return false;
+    }
+    // the abort word lives in pinned host memory: a read crosses PCIe, so look at it rarely
+    if ((it & 4095u) == 0u && abort_requested(s)) {
+      report(s, kAborted, kernel, where, peer, index, (int)expected, (int)v);
+      return false;
     }
   }
 }
@@ -227,7 +226,7 @@ TDB_DEVICE bool grid_barrier(const SymmInfo& s, uint32_t* word, int kernel, int 
     const uint64_t t0 = globaltimer_ns();
     uint32_t it = 0;
     while ((((old ^ ld_acquire_gpu(word)) & 0x80000000u) == 0)) {
-      if ((++it & 63u) == 0u) {
+      if ((++it & 1023u) == 0u) {
         if (abort_requested(s) || globaltimer_ns() - t0 > s.timeout_ns) {
           report(s, kTimeoutBarrier, kernel, where, -1, blockIdx.x, 0, (int)ld_volatile(word));
           ok = false;

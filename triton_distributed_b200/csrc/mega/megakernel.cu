@@ -107,11 +107,15 @@ TDB_DEVICE void task_rmsnorm(const MegaOp& op, int row, float* red) {
 
 TDB_DEVICE float silu_f(float x) { return x / (1.f + __expf(-x)); }
 
-TDB_DEVICE void task_silu_mul(const MegaOp& op, int row) {
+TDB_DEVICE void task_silu_mul(const MegaOp& op, int row, int chunk) {
   const int I = op.i[0];
+  const int nchunks = op.i[2];
   const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(op.p[0]) + static_cast<int64_t>(row) * op.i[1];
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.p[1]) + static_cast<int64_t>(row) * I;
-  for (int i = threadIdx.x; i < (I >> 3); i += kThreads) {
+  const int nv = I >> 3;
+  const int per = (nv + nchunks - 1) / nchunks;
+  const int v0 = chunk * per, v1 = min(nv, v0 + per);
+  for (int i = v0 + threadIdx.x; i < v1; i += kThreads) {
     const uint4 g = reinterpret_cast<const uint4*>(in)[i], u = reinterpret_cast<const uint4*>(in + I)[i];
     const float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z), g3 = unpack_bf16x2(g.w);
     const float2 u0 = unpack_bf16x2(u.x), u1 = unpack_bf16x2(u.y), u2 = unpack_bf16x2(u.z), u3 = unpack_bf16x2(u.w);
@@ -202,13 +206,15 @@ TDB_DEVICE attn::DecodeParams attn_params(const MegaOp& op, int batch) {
   return d;
 }
 
-TDB_DEVICE void task_attn_combine(const MegaOp& op, int b, int batch) {
+TDB_DEVICE void task_attn_combine(const MegaOp& op, int b, int h0, int batch) {
   const int Hq = op.i[0], D = op.i[2], splits = op.i[3];
+  const int hper = op.i[5];   // heads per combine task
   const float* part_out = reinterpret_cast<const float*>(op.p[1]);
   const float* part_lse = part_out + static_cast<int64_t>(batch) * Hq * splits * D;
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.p[6]);
-  for (int idx = threadIdx.x; idx < Hq * D; idx += kThreads) {
-    const int h = idx / D, d = idx - h * D;
+  const int hbeg = h0 * hper, hend = min(Hq, hbeg + hper);
+  for (int idx = threadIdx.x; idx < (hend - hbeg) * D; idx += kThreads) {
+    const int h = hbeg + idx / D, d = idx % D;
     const int64_t bh = static_cast<int64_t>(b) * Hq + h;
     float v;
     attn::merge_partials(part_out + bh * splits * D, part_lse + bh * splits, splits, D, d, &v);
@@ -272,7 +278,8 @@ __global__ void __launch_bounds__(kThreads, 1) mega_kernel(const KP p) {
       const uint64_t t0 = globaltimer_ns();
       uint32_t spins = 0;
       while (static_cast<int32_t>(v) < tk.dep_need) {
-        if ((++spins & 63u) == 0u && (abort_requested(p.symm) || globaltimer_ns() - t0 > p.symm.timeout_ns)) {
+        // the abort word lives in host memory: look at it (and at the clock) rarely, a read over PCIe is slow
+        if ((++spins & 4095u) == 0u && (abort_requested(p.symm) || globaltimer_ns() - t0 > p.symm.timeout_ns)) {
           report(p.symm, kTimeoutFlag, kKernelMega, 1, tk.type, ti, tk.dep_need, (int)v);
           ok = false;
           break;
@@ -293,7 +300,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_kernel(const KP p) {
         task_rmsnorm(op, tk.a0, red);
         break;
       case kTaskSiluMul:
-        task_silu_mul(op, tk.a0);
+        task_silu_mul(op, tk.a0, tk.a1);
         break;
       case kTaskRopeKv:
         task_rope_kv(op, tk.a0);
@@ -310,7 +317,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_kernel(const KP p) {
         fence_proxy_async_smem();
         break;
       case kTaskAttnCombine:
-        task_attn_combine(op, tk.a0, p.batch);
+        task_attn_combine(op, tk.a0, tk.a1, p.batch);
         break;
       case kTaskLinear: {
         // op.i: 0 N, 1 K, 2 splits, 3 tmap_w, 4 tmap_x, 5 ld_out, 6 all_reduce, 7 tiles_n, 8 max_tiles(flags stride)

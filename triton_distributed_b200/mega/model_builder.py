@@ -115,7 +115,7 @@ class ModelBuilder:
         N, K = weight.shape
         tiles = (N + 127) // 128
         if splits <= 0:
-            splits = int(self.lib.skinny_gemm_pick_splits(N, K, self.num_sms))
+            splits = int(self.lib.skinny_gemm_pick_splits(N, K, self.num_sms, self.batch))
         ar = bool(all_reduce and self.world_size > 1)
         self._max_n = max(self._max_n, N)
         self._max_tiles = max(self._max_tiles, tiles)
@@ -163,21 +163,25 @@ class ModelBuilder:
         group = num_q_heads // num_kv_heads
         chunks = (group + 15) // 16
         if splits <= 0:
-            splits = pick_kv_splits(self.batch, num_kv_heads, chunks, max_len, self.num_sms)
+            # tasks of one SM run one after the other, so there is no point in more split tasks than SMs
+            blocks = max(1, (max_len + 63) // 64)
+            splits = max(1, min(blocks, 64, self.num_sms // max(1, self.batch * num_kv_heads * chunks)))
         ws = torch.empty(self.batch * num_q_heads * splits * (head_dim + 1), dtype=torch.float32, device=self.device)
         bt = torch.arange(self.batch, dtype=torch.int32, device=self.device).contiguous()
         scale = scale if scale is not None else head_dim ** -0.5
         op = self.sched.add_op([self._ptr(q), self._ptr(ws), self._ptr(k_cache), self._ptr(v_cache), self._ptr(kv_lens),
-                                self._ptr(bt), self._ptr(out)], [num_q_heads, num_kv_heads, head_dim, splits, max_len], [scale])
+                                self._ptr(bt), self._ptr(out)], [num_q_heads, num_kv_heads, head_dim, splits, max_len, 1],
+                               [scale])
         s1 = self.sched.add_stage(T_ATTN_SPLIT, op, self.batch, splits, num_kv_heads * chunks, self._dep(q, k_cache, v_cache))
-        s2 = self.sched.add_stage(T_ATTN_COMBINE, op, self.batch, 1, 1, s1)
+        s2 = self.sched.add_stage(T_ATTN_COMBINE, op, self.batch, num_q_heads, 1, s1)   # one task per (sequence, head)
         self._wrote(s2, out)
         return s2
 
     def make_silu_mul_up(self, x: torch.Tensor, out: torch.Tensor) -> int:
         I = x.shape[-1] // 2
-        op = self.sched.add_op([self._ptr(x), self._ptr(out)], [I, x.stride(0)], [])
-        st = self.sched.add_stage(T_SILU_MUL, op, self.batch, 1, 1, self._dep(x))
+        nchunks = max(1, min(16, self.num_sms // max(1, self.batch), I // 2048))
+        op = self.sched.add_op([self._ptr(x), self._ptr(out)], [I, x.stride(0), nchunks], [])
+        st = self.sched.add_stage(T_SILU_MUL, op, self.batch, nchunks, 1, self._dep(x))
         self._wrote(st, out)
         return st
 
