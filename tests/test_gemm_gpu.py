@@ -34,6 +34,13 @@ def test_gemm_block_n(block_n):
     _check(512, 768, 512, block_n=block_n)
 
 
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 512), (384, 512, 256), (1000, 520, 264),
+                                   (4096, 4096, 512), (8192, 2048, 1024)])
+def test_gemm_cta_pair(shape):
+    # 256 x 256 tiles over two SMs (cta_group::2); 384 and 1000 rows leave the second CTA of a pair without rows
+    _check(*shape, block_n=512)
+
+
 def test_gemm_many_tiles_per_cta():
     # more tiles than CTAs: exercises the smem ring and both TMEM accumulator buffers across tiles
     _check(4096, 4096, 512)

@@ -101,6 +101,20 @@ int pick_block_n(int64_t N, int block_n) {
   return N <= 128 ? 128 : 256;
 }
 
+// Kernel form for a GEMM whose row segments have `rows` rows: block_n 128 / 256 force the single-CTA kernel, 512 the
+// CTA-pair kernel (256 x 256 tiles over two SMs), 0 picks the pair kernel when the problem is large enough for it and
+// the output can go through TMA stores.  TDB200_GEMM_PAIR=0 keeps the automatic choice on the single-CTA kernel.
+bool pick_cta_pair(int64_t rows, int64_t N, int block_n, bool tma_store_ok) {
+  if (!tma_store_ok) return false;
+  if (block_n == 512) return true;
+  if (block_n != 0) return false;
+  static const bool enabled = [] {
+    const char* e = std::getenv("TDB200_GEMM_PAIR");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  return enabled && rows >= 256 && N >= 256;
+}
+
 int sm_count() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
 
 // C[M,N] = A[M,K] @ B[N,K]^T   (bf16)
@@ -121,14 +135,18 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int bloc
   g.M = M; g.N = N; g.K = K;
   g.c = c.data_ptr();
   g.ldc = c.stride(0);
-  g.block_n = pick_block_n(N, block_n);
+  const bool tma_store_ok = c.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15u) == 0;
+  g.cta_pair = pick_cta_pair(M, N, block_n, tma_store_ok) ? 1 : 0;
+  g.block_n = g.cta_pair ? 256 : pick_block_n(N, block_n);
   g.tmap_a = make_tmap3(a.data_ptr(), tdb::kBF16, 1, M, K, a.stride(0) * 2, a.stride(0) * 2 * M, 128, 64);
-  g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, g.block_n, 64);
-  if (c.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15u) == 0) {
+  g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N,
+                        g.cta_pair ? 128 : g.block_n, 64);
+  if (tma_store_ok) {
     g.tmap_c = make_tmap3(c.data_ptr(), tdb::kBF16, 1, M, N, c.stride(0) * 2, c.stride(0) * 2 * M, 128, 64);
     g.use_tma_store = 1;
   }
-  const int tiles = ((M + 127) / 128) * ((N + g.block_n - 1) / g.block_n);
+  const int tile_m = g.cta_pair ? 256 : 128;
+  const int tiles = ((M + tile_m - 1) / tile_m) * ((N + g.block_n - 1) / g.block_n) * (g.cta_pair ? 2 : 1);
   g.num_ctas = std::min<int>(num_ctas > 0 ? num_ctas : sm_count(), tiles);
   g.symm.world = 1;
   g.symm.timeout_ns = 2000000000ull;
@@ -156,11 +174,14 @@ void ag_gemm_bf16(SymmHeap& h, const at::Tensor& a_local, const at::Tensor& b, a
   g.M = M; g.N = N; g.K = K;
   g.c = c.data_ptr();
   g.ldc = c.stride(0);
-  g.block_n = pick_block_n(N, block_n);
+  const bool tma_store_ok = c.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15u) == 0;
+  g.cta_pair = (pick_cta_pair(m, N, block_n, tma_store_ok) && n_comm % 2 == 0) ? 1 : 0;
+  g.block_n = g.cta_pair ? 256 : pick_block_n(N, block_n);
   g.tmap_a = make_tmap3(ws.data_ptr(), tdb::kBF16, 2, M, K, K * 2, buf_elems * 2, 128, 64);
   g.tmap_a_local = make_tmap3(a_local.data_ptr(), tdb::kBF16, 1, m, K, K * 2, static_cast<uint64_t>(m) * K * 2, 128, 64);
-  g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, g.block_n, 64);
-  if (c.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15u) == 0) {
+  g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N,
+                        g.cta_pair ? 128 : g.block_n, 64);
+  if (tma_store_ok) {
     g.tmap_c = make_tmap3(c.data_ptr(), tdb::kBF16, W, m, N, c.stride(0) * 2, c.stride(0) * 2 * m, 128, 64);
     g.use_tma_store = 1;
   }
@@ -197,9 +218,11 @@ void gemm_rs_bf16(SymmHeap& h, const at::Tensor& a, const at::Tensor& b, at::Ten
   std::memset(&g, 0, sizeof(g));
   g.mode = tdb::kGemmReduceScatter;
   g.M = M; g.N = N; g.K = K;
-  g.block_n = pick_block_n(N, block_n);
+  g.cta_pair = pick_cta_pair(m, N, block_n, true) ? 1 : 0;
+  g.block_n = g.cta_pair ? 256 : pick_block_n(N, block_n);
   g.tmap_a = make_tmap3(a.data_ptr(), tdb::kBF16, 1, M, K, a.stride(0) * 2, a.stride(0) * 2 * M, 128, 64);
-  g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, g.block_n, 64);
+  g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N,
+                        g.cta_pair ? 128 : g.block_n, 64);
   g.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
   g.seg_rows = m;
   g.max_seg_rows = max_seg_rows;

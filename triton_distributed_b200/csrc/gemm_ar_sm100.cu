@@ -244,11 +244,19 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         ld_dst = p.N;
       }
       if (n_ok) {
-        for (int m = 0; m < p.M; ++m) {
-          float* a = p.acc + static_cast<int64_t>(m) * p.N + n;
-          const float v = __ldcg(a);
-          *a = 0.f;
-          dst[static_cast<int64_t>(m) * ld_dst + n] = __float2bfloat16(v);
+        // batches of 8 independent loads: one L2 round trip per batch instead of one per row
+        for (int m0 = 0; m0 < p.M; m0 += 8) {
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            v[j] = (m0 + j < p.M) ? __ldcg(p.acc + static_cast<int64_t>(m0 + j) * p.N + n) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (m0 + j < p.M) {
+              p.acc[static_cast<int64_t>(m0 + j) * p.N + n] = 0.f;
+              dst[static_cast<int64_t>(m0 + j) * ld_dst + n] = __float2bfloat16(v[j]);
+            }
+          }
         }
       }
       if (p.mode == 0) continue;

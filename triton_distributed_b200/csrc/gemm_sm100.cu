@@ -639,18 +639,309 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 }
 
-template <int BN>
-cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
-  using L = SmemLayout<BN>;
-  static_assert(kPushSlots * kPushPiece + kPushSlots * 8 <= L::kTotal, "push ring must fit the GEMM's shared memory");
-  const int smem = L::kTotal + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
+
+// ---------------------------------------------------------------------------
+// CTA-pair form of the same kernel (cta_group::2).  Two CTAs of a cluster, on the two SMs of one TPC, share one
+// 256 x 256 output tile: CTA r of the pair loads rows [128 r, 128 r + 128) of the A tile and of the B tile, CTA 0
+// issues tcgen05.mma.cta_group::2 (M = 256) which reads both CTAs' shared memory and writes 128 accumulator rows
+// into each CTA's TMEM, and each CTA runs the epilogue of its own 128 rows.  Per output element this halves the
+// B-operand traffic into shared memory and the shared-memory read bandwidth the tensor core needs, which is what
+// limits the single-CTA 128 x 256 form.  Barrier protocol:
+//   full[s]       in CTA 0, count 1 (+ 64 KB of transactions): both CTAs' TMA loads credit it (cta_group::2 loads)
+//   empty[s]      in each CTA, count 1: CTA 0 commits to both after the MMAs that read stage s
+//   tmem_full[b]  in each CTA, count 1: CTA 0 commits to both after a tile's last MMA
+//   tmem_empty[b] in CTA 0, count 256: the 2 x 128 epilogue threads arrive (remote arrive from CTA 1)
+// The fused modes work on 128-row units exactly as in the single-CTA kernel (all-gather flags per 128-row chunk,
+// reduce-scatter flags per 128 x 256 tile), so the comm CTAs, the workspaces and the owner-side reduction are shared.
+// ---------------------------------------------------------------------------
+struct PairLayout {
+  static constexpr int kStages = 6;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = 128 * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kEpiOffset = kStages * kStageBytes;
+  static constexpr int kBarOffset = kEpiOffset + 2 * kEpiBytes;
+  static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 16;
+};
+constexpr int kPairBN = 256;
+
+// tile order of the pair kernel: like decode_tile, with M tiles of 256 rows; r.mt is the pair-row index
+__device__ __forceinline__ Tile decode_tile_pair(const KParams& p, int t, int tiles_m_pair) {
+  Tile r;
+  const int per_seg = tiles_m_pair * p.tiles_n;
+  const int si = t / per_seg;
+  const int rem = t - si * per_seg;
+  r.seg = (p.seg_first + si) % p.num_seg;
+  const int group_sz = kGroupM * p.tiles_n;
+  const int g = rem / group_sz;
+  const int first_m = g * kGroupM;
+  const int gm = min(tiles_m_pair - first_m, kGroupM);
+  const int in_g = rem - g * group_sz;
+  r.mt = first_m + in_g % gm;
+  r.nt = in_g / gm;
+  r.m0 = r.seg * p.seg_rows + r.mt * 2 * kBM;
+  r.n0 = r.nt * kPairBN;
+  r.m_end = min(p.M, (r.seg + 1) * p.seg_rows);
+  return r;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ PeerMaps peer_maps,
+                 const __grid_constant__ CUtensorMap tmap_a_local, const KParams p) {
+  using L = PairLayout;
+  constexpr int kStages = L::kStages;
+  constexpr int BN = kPairBN;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cr = cluster_ctarank();
+  const uint32_t epoch = (p.ctx != nullptr) ? ld_volatile(&p.ctx->epoch) : 1u;
+  const int buf = epoch & 1;
+
+  // n_comm is even, so both CTAs of a pair take the same role
+  const bool is_comm = (p.mode == kGemmAllGather) && (static_cast<int>(blockIdx.x) < p.n_comm);
+  if (is_comm) {
+    if (p.use_mc) {
+      ag_push_multimem(p, epoch);
+    } else {
+      ag_push_bulk(p, epoch, smem);
+    }
+  } else {
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < kStages; ++i) {
+        mbar_init(&full_bar[i], 1);
+        mbar_init(&empty_bar[i], 1);
+      }
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&tmem_full[i], 1);
+        mbar_init(&tmem_empty[i], 256);
+      }
+      *abort_flag = 0;
+      fence_mbar_init();
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      if (p.mode == kGemmAllGather) tma_prefetch_desc(&tmap_a_local);
+      if (p.mode != kGemmReduceScatter) tma_prefetch_desc(&tmap_c);
+    }
+    if (warp == 1) {
+      // collective over the pair: the same warp of both CTAs allocates all 512 columns in both TMEMs
+      tmem_alloc_pair(tmem_base_smem, 2 * BN);
+      tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    const int n_pairs = (gridDim.x - p.n_comm) / 2;
+    const int pair_idx = (blockIdx.x - p.n_comm) / 2;
+    const int tiles_m_pair = (p.tiles_m_seg + 1) / 2;
+    const int num_tiles = p.num_seg * tiles_m_pair * p.tiles_n;
+    const int num_kb = (p.K + kBK - 1) / kBK;
+
+    if (warp == 0) {
+      // ------------------------------------------------------------ TMA producer (both CTAs, own operand halves)
+      if (lane == 0) {
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = pair_idx; t < num_tiles && ok; t += n_pairs) {
+          const Tile tl = decode_tile_pair(p, t, tiles_m_pair);
+          const int mt = 2 * tl.mt + static_cast<int>(cr);     // this CTA's 128-row chunk of the segment
+          const bool valid_m = mt < p.tiles_m_seg;
+          const bool local_seg = (p.mode == kGemmAllGather) && tl.seg == p.symm.rank;
+          if (p.mode == kGemmAllGather && !local_seg && valid_m) {
+            const uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * p.symm.world + tl.seg) * p.max_chunks + mt;
+            ok = wait_until(p.symm, flag, epoch, kCmpGe, kKernelAgGemm, 1, tl.seg, mt);
+            if (!ok) break;
+            fence_proxy_async();
+          }
+          for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1;
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kMbarTimeoutNs)) {
+              ok = false;
+              report(p.symm, kTimeoutMbarrier, kKernelGemm, 110, -1, s, (int)ph, t);
+              break;
+            }
+            uint8_t* sa = smem + s * L::kStageBytes;
+            uint8_t* sb = sa + L::kABytes;
+            const uint32_t full0 = mapa_u32(smem_u32(&full_bar[s]), 0);
+            if (cr == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * L::kStageBytes);
+            if (local_seg) {
+              tma_load_3d_pair(sa, &tmap_a_local, full0, kb * kBK, mt * kBM, 0);
+            } else {
+              tma_load_3d_pair(sa, &tmap_a, full0, kb * kBK, tl.seg * p.seg_rows + mt * kBM,
+                               (p.mode == kGemmAllGather) ? buf : 0);
+            }
+            tma_load_3d_pair(sb, &tmap_b, full0, kb * kBK, tl.n0 + static_cast<int>(cr) * 128, 0);
+          }
+        }
+        if (!ok) {
+          *abort_flag = 1;
+          // loads already issued land within microseconds; give them time before the CTA may leave
+          const uint64_t t0 = globaltimer_ns();
+          while (globaltimer_ns() - t0 < 2000000ull) nanosleep(1000);
+        }
+      }
+    } else if (warp == 1) {
+      // ------------------------------------------------------------ MMA issuer (CTA 0 of the pair only)
+      if (lane == 0 && cr == 0) {
+        constexpr uint32_t idesc = make_idesc(1u, 2 * kBM, BN);
+        uint32_t it = 0;
+        int local = 0;
+        bool ok = true;
+        for (int t = pair_idx; t < num_tiles && ok; t += n_pairs) {
+          const int b = local & 1;
+          const uint32_t aph = (local >> 1) & 1;
+          ++local;
+          if (!mbar_wait(&tmem_empty[b], aph ^ 1, abort_flag, kMbarTimeoutNs)) {
+            ok = false;
+            report(p.symm, kTimeoutMbarrier, kKernelGemm, 120, -1, b, (int)aph, t);
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + b * BN;
+          for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1;
+            if (!mbar_wait(&full_bar[s], ph, abort_flag, kMbarTimeoutNs)) {
+              ok = false;
+              report(p.symm, kTimeoutMbarrier, kKernelGemm, 121, -1, s, (int)ph, t);
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
+            const uint64_t adesc = make_smem_desc_sw128(sa);
+            const uint64_t bdesc = make_smem_desc_sw128(sa + L::kABytes);
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k)
+              umma_f16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            const uint32_t e = smem_u32(&empty_bar[s]);
+            umma_commit_pair(mapa_u32(e, 0));
+            umma_commit_pair(mapa_u32(e, 1));
+          }
+          if (ok) {
+            const uint32_t f = smem_u32(&tmem_full[b]);
+            umma_commit_pair(mapa_u32(f, 0));
+            umma_commit_pair(mapa_u32(f, 1));
+          }
+        }
+        if (!ok) *abort_flag = 1;
+      }
+    } else {
+      // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+      const int q = warp & 3;
+      const bool leader = (warp == 2 && lane == 0);
+      uint8_t* stage_base = smem + L::kEpiOffset;
+      const int row_in_tile = q * 32 + lane;
+      uint32_t chunk_ctr = 0;
+      int local = 0;
+      bool ok = true;
+      for (int t = pair_idx; t < num_tiles && ok; t += n_pairs) {
+        const Tile tl = decode_tile_pair(p, t, tiles_m_pair);
+        const int mt = 2 * tl.mt + static_cast<int>(cr);
+        const bool valid_m = mt < p.tiles_m_seg;
+        const int b = local & 1;
+        const uint32_t aph = (local >> 1) & 1;
+        ++local;
+        if (!mbar_wait(&tmem_full[b], aph, abort_flag, kMbarTimeoutNs)) {
+          ok = false;
+          if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemm, 130, -1, b, (int)aph, t);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t t_acc = tmem_base + b * BN + (static_cast<uint32_t>(q * 32) << 16);
+        const CUtensorMap* cmap = (p.mode == kGemmReduceScatter) ? &peer_maps.m[tl.seg] : &tmap_c;
+        const int c2 = (p.mode == kGemmReduceScatter) ? (buf * p.symm.world + p.symm.rank) : tl.seg;
+#pragma unroll 1
+        for (int c = 0; c < BN / kEpiCols; ++c, ++chunk_ctr) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_acc + c * kEpiCols, r0);
+          tmem_ld_32x32(t_acc + c * kEpiCols + 32, r1);
+          tmem_ld_wait();
+          if (c == BN / kEpiCols - 1) {
+            tc_fence_before_sync();
+            mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[b]), 0));
+          }
+          uint8_t* stg = stage_base + (chunk_ctr & 1) * kEpiBytes;
+          if (leader) bulk_wait_read<1>();
+          epi_bar();
+          uint8_t* srow = stg + row_in_tile * 128;
+          const int sw = row_in_tile & 7;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+            *reinterpret_cast<uint4*>(srow + ((j ^ sw) << 4)) = o;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+            *reinterpret_cast<uint4*>(srow + (((j + 4) ^ sw) << 4)) = o;
+          }
+          fence_proxy_async_smem();
+          epi_bar();
+          if (leader && valid_m && tl.n0 + c * kEpiCols < p.N) {
+            tma_store_3d(cmap, stg, tl.n0 + c * kEpiCols, mt * kBM, c2);
+            bulk_commit();
+          }
+        }
+        if (p.mode == kGemmReduceScatter && leader && valid_m) {
+          bulk_wait<0>();
+          fence_proxy_async();
+          fence_acq_rel_sys();
+          uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.max_tiles +
+                           mt * p.tiles_n + tl.nt;
+          st_release_sys(symm_at(p.symm, flag, tl.seg), epoch);
+        }
+      }
+      if (!ok) *abort_flag = 1;
+      if (leader) bulk_wait<0>();
+    }
+
+    // ------------------------------------------------------------ teardown
+    // neither CTA may leave (or free TMEM) while its partner can still read its shared memory or signal its barriers
+    tc_fence_before_sync();
+    cluster_sync_all();
+    if (warp == 1) {
+      tc_fence_after_sync();
+      tmem_dealloc_pair(tmem_base, 2 * BN);
+    }
+    if (p.mode == kGemmReduceScatter && *abort_flag == 0) rs_reduce(p, epoch, BN);
   }
-  KParams p;
+
+  if (p.ctx != nullptr) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const uint32_t prev = atomicAdd(&p.ctx->done, 1u);
+      if (prev == gridDim.x - 1) {
+        p.ctx->done = 0;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(&p.ctx->epoch) = epoch + 1;
+      }
+    }
+  }
+}
+
+// Fills the kernel parameters shared by both kernel forms; BN is the tile width.
+cudaError_t fill_params(const GemmArgs& a, int BN, KParams& p) {
   p.mode = a.mode;
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.c = reinterpret_cast<__nv_bfloat16*>(a.c);
@@ -684,7 +975,23 @@ cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
   if (a.mode == kGemmReduceScatter && p.tiles_m_seg * p.tiles_n > a.max_tiles) return cudaErrorInvalidValue;
   if (a.mode == kGemmAllGather && (a.n_comm_ctas < 1 || a.n_comm_ctas >= a.num_ctas)) return cudaErrorInvalidValue;
   if (a.K % 8 != 0) return cudaErrorInvalidValue;
+  return cudaSuccess;
+}
 
+template <int BN>
+cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  static_assert(kPushSlots * kPushPiece + kPushSlots * 8 <= L::kTotal, "push ring must fit the GEMM's shared memory");
+  const int smem = L::kTotal + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  KParams p;
+  cudaError_t e = fill_params(a, BN, p);
+  if (e != cudaSuccess) return e;
   CUtensorMap ta, tb, tc, tl;
   memcpy(&tl, a.tmap_a_local.bytes, sizeof(CUtensorMap));
   memcpy(&ta, a.tmap_a.bytes, sizeof(CUtensorMap));
@@ -696,6 +1003,37 @@ cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// CTA-pair form: needs the TMA-store epilogue, no grouped mode, an even grid and an even number of comm CTAs;
+// the B tensor map must have a 128-row box.
+cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
+  using L = PairLayout;
+  static_assert(kPushSlots * kPushPiece + kPushSlots * 8 <= L::kTotal, "push ring must fit the GEMM's shared memory");
+  static_assert(L::kTotal + 1024 <= 227 * 1024, "pair kernel exceeds the shared memory of an SM");
+  const int smem = L::kTotal + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  if (!a.use_tma_store || a.tile_expert != nullptr) return cudaErrorInvalidValue;
+  KParams p;
+  cudaError_t e = fill_params(a, kPairBN, p);
+  if (e != cudaSuccess) return e;
+  if ((p.n_comm & 1) != 0) return cudaErrorInvalidValue;
+  int grid = a.num_ctas & ~1;
+  if (grid - p.n_comm < 2) return cudaErrorInvalidValue;
+  CUtensorMap ta, tb, tc, tl;
+  memcpy(&tl, a.tmap_a_local.bytes, sizeof(CUtensorMap));
+  memcpy(&ta, a.tmap_a.bytes, sizeof(CUtensorMap));
+  memcpy(&tb, a.tmap_b.bytes, sizeof(CUtensorMap));
+  memcpy(&tc, a.tmap_c.bytes, sizeof(CUtensorMap));
+  PeerMaps pm;
+  memcpy(&pm, a.tmap_peer_c, sizeof(PeerMaps));
+  gemm_pair_kernel<<<grid, kThreads, smem, stream>>>(ta, tb, tc, pm, tl, p);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 int gemm_smem_bytes(int block_n) {
@@ -703,6 +1041,7 @@ int gemm_smem_bytes(int block_n) {
 }
 
 cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
+  if (a.cta_pair) return launch_pair(a, stream);
   if (a.block_n == 256) return launch_impl<256>(a, stream);
   if (a.block_n == 128) return launch_impl<128>(a, stream);
   return cudaErrorInvalidValue;

@@ -68,6 +68,7 @@ struct GemmArgs {
   TensorMap tmap_peer_c[kMaxRanksHost];
   int use_tma_store;
   int block_n;      // 128 or 256
+  int cta_pair;     // 1: CTA-pair kernel (256 x 256 tiles over two SMs); tmap_b then has a 128-row box
   int num_ctas;     // grid size (<= SM count)
   // fused modes
   int seg_rows;     // rows per rank segment (M = world * seg_rows)

@@ -425,11 +425,18 @@ __global__ void __launch_bounds__(kThreads, 1) mega_kernel(const KP p) {
               __nv_bfloat16* dst = ar ? (p.use_mc ? partial : partial + static_cast<int64_t>(rank) * p.batch * N) : out;
               const int64_t ld_dst = ar ? N : ld_out;
               if (n_ok) {
-                for (int m = 0; m < p.batch; ++m) {
-                  float* a = p.acc + static_cast<int64_t>(m) * N + n;
-                  const float v = __ldcg(a);
-                  *a = 0.f;
-                  dst[static_cast<int64_t>(m) * ld_dst + n] = __float2bfloat16(v);
+                for (int m0 = 0; m0 < p.batch; m0 += 8) {
+                  float v[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    v[j] = (m0 + j < p.batch) ? __ldcg(p.acc + static_cast<int64_t>(m0 + j) * N + n) : 0.f;
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    if (m0 + j < p.batch) {
+                      p.acc[static_cast<int64_t>(m0 + j) * N + n] = 0.f;
+                      dst[static_cast<int64_t>(m0 + j) * ld_dst + n] = __float2bfloat16(v[j]);
+                    }
+                  }
                 }
               }
               final_tile = true;

@@ -20,6 +20,7 @@ import torch
 
 from .. import _native
 from ..runtime import Runtime, get_runtime
+from .gemm import use_cta_pair
 from .common import new_ctx_dev, ref_all_gather, sm_count
 
 BLOCK_M = 128
@@ -34,6 +35,7 @@ class AllGatherGEMMTensorParallelContext:
     K: int
     dtype: torch.dtype
     BLOCK_N: int = 256
+    kernel_form: str = "auto"   # "auto" | "single" (128 x BLOCK_N tiles) | "pair" (256 x 256 tiles over two SMs)
     n_comm_ctas: int = 0       # 0 = automatic
     num_ctas: int = 0
     use_multimem: bool = False
@@ -94,12 +96,20 @@ def create_ag_gemm_context(tensor_A: Optional[torch.Tensor] = None, tensor_B: Op
     return ctx
 
 
-def pick_comm_ctas(rows_per_rank: int, n_local: int, world: int, block_n: int, n_sms: int) -> int:
+def pick_comm_ctas(rows_per_rank: int, n_local: int, world: int, block_n: int, n_sms: int, pair: bool = False) -> int:
     """Comm CTAs of the fused launch: at least enough push bandwidth for the remote shards to stay ahead of the GEMM
     (about 45 GB/s per bulk-TMA CTA; a segment of the GEMM consumes its shard in 1/world of the GEMM time), and every
-    SM that the tile count leaves idle in the last wave anyway."""
-    tiles = world * ((rows_per_rank + BLOCK_M - 1) // BLOCK_M) * ((n_local + block_n - 1) // block_n)
+    SM that the tile count leaves idle in the last wave anyway.  With the CTA-pair kernel the work units are 256 x 256
+    tiles on SM pairs and the count is even."""
     n_min = 4 if world <= 2 else 8
+    if pair:
+        tiles = world * ((rows_per_rank + 2 * BLOCK_M - 1) // (2 * BLOCK_M)) * ((n_local + 255) // 256)
+        units = (n_sms - n_min) // 2
+        waves = max(1, -(-tiles // units))
+        n_gemm = 2 * -(-tiles // waves)
+        n = max(n_min, min(32, n_sms - n_gemm))
+        return int(n - (n & 1))
+    tiles = world * ((rows_per_rank + BLOCK_M - 1) // BLOCK_M) * ((n_local + block_n - 1) // block_n)
     waves = max(1, -(-tiles // (n_sms - n_min)))
     n_gemm = -(-tiles // waves)
     return int(max(n_min, min(32, n_sms - n_gemm)))
@@ -142,9 +152,12 @@ def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelCo
     if out is None:
         out = torch.empty((m * W, N), dtype=a.dtype, device=a.device)
     n_sms = ctx.num_ctas or sm_count(a.device)
-    n_comm = ctx.n_comm_ctas or pick_comm_ctas(m, N, W, ctx.BLOCK_N, n_sms)
+    pair = use_cta_pair(ctx.kernel_form, m, N, out)
+    n_comm = ctx.n_comm_ctas or pick_comm_ctas(m, N, W, ctx.BLOCK_N, n_sms, pair)
     n_comm = max(1, min(n_comm, n_sms - 1))
+    if pair and n_comm % 2:
+        n_comm += 1
     lib.ag_gemm_bf16(rt.heap, a, b, out, ctx.workspace, ctx.flags, ctx.ctx_dev, ctx.max_seg_rows, ctx.max_chunks,
-                     n_comm, ctx.BLOCK_N, n_sms, bool(ctx.use_multimem and rt.has_multicast), rt.config.wait_timeout_s)
+                     n_comm, 512 if pair else ctx.BLOCK_N, n_sms, bool(ctx.use_multimem and rt.has_multicast), rt.config.wait_timeout_s)
     ctx.calls += 1
     return out

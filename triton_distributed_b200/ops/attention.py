@@ -86,11 +86,12 @@ def flash_attn_varlen(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 
 
 def pick_kv_splits(batch: int, num_kv_heads: int, head_chunks: int, max_kv_len: int, num_sms: int = 148) -> int:
-    """Number of KV splits: about four CTAs per SM in total (decode attention is latency-bound until many loads are in
-    flight), never more splits than 64-token blocks, at most 64."""
+    """Number of KV splits: as many as still fit one wave of the grid (three CTAs of the split-KV kernel are resident
+    per SM; a second, partly filled wave costs more than the extra parallelism brings), never more splits than
+    64-token blocks, at most 64."""
     blocks = max(1, (max_kv_len + 63) // 64)
     ctas = max(1, batch * num_kv_heads * head_chunks)
-    want = max(1, (4 * num_sms + ctas - 1) // ctas)
+    want = max(1, (3 * num_sms) // ctas)
     return int(max(1, min(want, blocks, 64)))
 
 

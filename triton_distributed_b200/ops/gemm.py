@@ -16,6 +16,20 @@ from .. import _native
 SKINNY_M = 128   # up to this many rows the weight-streaming kernel wins
 
 
+def use_cta_pair(kernel_form: str, rows: int, n: int, out: Optional[torch.Tensor] = None) -> bool:
+    """Whether a GEMM with ``rows`` rows per segment and ``n`` columns runs the CTA-pair kernel (256 x 256 tiles over
+    two SMs): ``kernel_form`` "pair" / "single" force it, "auto" takes it for problems of at least one pair tile unless
+    ``TDB200_GEMM_PAIR=0``.  The pair kernel stores through TMA, so the output rows must be 16-byte aligned."""
+    import os
+    if out is not None and (out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0):
+        return False
+    if kernel_form == "pair":
+        return True
+    if kernel_form == "single":
+        return False
+    return os.environ.get("TDB200_GEMM_PAIR", "1") != "0" and rows >= 256 and n >= 256
+
+
 def gemm_reference(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """fp32 reference: A @ B^T."""
     return (a.float() @ b.float().t()).to(a.dtype)

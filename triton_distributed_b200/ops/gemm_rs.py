@@ -18,6 +18,7 @@ import torch
 
 from .. import _native
 from ..runtime import Runtime, get_runtime
+from .gemm import use_cta_pair
 from .common import new_ctx_dev, ref_reduce_scatter, sm_count
 
 BLOCK_M = 128
@@ -32,6 +33,7 @@ class GEMMReduceScatterTensorParallelContext:
     N: int
     output_dtype: torch.dtype
     BLOCK_N: int = 256
+    kernel_form: str = "auto"   # "auto" | "single" (128 x BLOCK_N tiles) | "pair" (256 x 256 tiles over two SMs)
     num_ctas: int = 0
     slots: Optional[torch.Tensor] = None   # heap [2][W][max_M/W][N]
     flags: Optional[torch.Tensor] = None   # heap [2][W][max_tiles]
@@ -106,7 +108,8 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParall
         raise ValueError("gemm_rs: M must be divisible by the world size")
     if out is None:
         out = torch.empty((M // W, N), dtype=a.dtype, device=a.device)
+    pair = use_cta_pair(ctx.kernel_form, M // W, N, out)
     lib.gemm_rs_bf16(rt.heap, a, b, out, ctx.slots, ctx.flags, ctx.ctx_dev, ctx.max_seg_rows, ctx.max_tiles,
-                     ctx.BLOCK_N, ctx.num_ctas or sm_count(a.device), rt.config.wait_timeout_s)
+                     512 if pair else ctx.BLOCK_N, ctx.num_ctas or sm_count(a.device), rt.config.wait_timeout_s)
     ctx.calls += 1
     return out
