@@ -50,6 +50,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--n-comm", default="8")
     ap.add_argument("--multimem", type=int, default=0)
+    ap.add_argument("--only", default="", help="comma list of op names to run (default: all)")
     args = ap.parse_args()
     tdb.initialize_distributed(seed=0)
     rt = tdb.get_runtime()
@@ -67,6 +68,11 @@ def main():
     w1t, w2t = w1.t(), w2.t()
     flops = 2.0 * M * K * n
     link_bytes = (W - 1) / W * M * K * 2
+
+    only = set(v for v in args.only.split(",") if v)
+
+    def want(name):
+        return not only or name in only
 
     def emit(name, ms, extra=None):
         if rt.rank == 0:
@@ -91,21 +97,29 @@ def main():
         else:
             torch.matmul(h, w2t, out=o)
 
-    emit("torch_ag_gemm", timed(t_ag_gemm, args.iters, args.warmup, fl, rt))
-    emit("torch_gemm_rs", timed(t_gemm_rs, args.iters, args.warmup, fl, rt))
-    emit("torch_gemm_only_ag_shape", timed(lambda: torch.matmul(full, w1t, out=h), args.iters, args.warmup, fl, rt))
-    emit("own_gemm_only_ag_shape", timed(lambda: ops.gemm(full, w1, out=h), args.iters, args.warmup, fl, rt))
-    emit("own_gemm_only_rs_shape", timed(lambda: ops.gemm(h, w2, out=part), args.iters, args.warmup, fl, rt))
-    for nc in [int(v) for v in args.n_comm.split(",")]:
+    full.normal_()
+    h.normal_()
+    if want("torch_ag_gemm"):
+        emit("torch_ag_gemm", timed(t_ag_gemm, args.iters, args.warmup, fl, rt))
+    if want("torch_gemm_rs"):
+        emit("torch_gemm_rs", timed(t_gemm_rs, args.iters, args.warmup, fl, rt))
+    if want("torch_gemm_only_ag_shape"):
+        emit("torch_gemm_only_ag_shape", timed(lambda: torch.matmul(full, w1t, out=h), args.iters, args.warmup, fl, rt))
+    if want("own_gemm_only_ag_shape"):
+        emit("own_gemm_only_ag_shape", timed(lambda: ops.gemm(full, w1, out=h), args.iters, args.warmup, fl, rt))
+    if want("own_gemm_only_rs_shape"):
+        emit("own_gemm_only_rs_shape", timed(lambda: ops.gemm(h, w2, out=part), args.iters, args.warmup, fl, rt))
+    for nc in ([int(v) for v in args.n_comm.split(",")] if want("own_ag_gemm") else []):
         ag_ctx = ops.create_ag_gemm_context(max_M=M, K=K, dtype=torch.bfloat16, n_comm_ctas=nc,
                                             use_multimem=bool(args.multimem))
         emit("own_ag_gemm", timed(lambda: ops.ag_gemm(a, w1, ag_ctx, out=h), args.iters, args.warmup, fl, rt),
              {"n_comm": nc, "multimem": args.multimem})
         rt.check_status()
         ag_ctx.finalize()
-    rs_ctx = ops.create_gemm_rs_context(max_M=M, N=K)
-    emit("own_gemm_rs", timed(lambda: ops.gemm_rs(h, w2, rs_ctx, out=o), args.iters, args.warmup, fl, rt))
-    rt.check_status()
+    if want("own_gemm_rs"):
+        rs_ctx = ops.create_gemm_rs_context(max_M=M, N=K)
+        emit("own_gemm_rs", timed(lambda: ops.gemm_rs(h, w2, rs_ctx, out=o), args.iters, args.warmup, fl, rt))
+        rt.check_status()
     tdb.finalize_distributed()
 
 

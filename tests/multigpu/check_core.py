@@ -135,7 +135,9 @@ def check_fused_gemms(rt, quick):
     for (m, N, K) in shapes:   # m = rows per rank
         for use_mc in ([True, False] if rt.has_multicast else [False]):
             ctx = ops.create_ag_gemm_context(max_M=m * W, K=K, dtype=torch.bfloat16, use_multimem=use_mc)
-            for it in range(3):
+            for it in range(5):
+                # iterations 3 and 4 repeat on the single-CTA kernel where the automatic choice is the CTA-pair kernel
+                ctx.kernel_form = "auto" if it < 3 else "single"
                 a = (torch.randn(m, K, device="cuda") * (0.5 + 0.1 * rt.rank)).to(torch.bfloat16)
                 b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
                 strag = (it % W, 0.02) if it == 1 else None
@@ -150,7 +152,8 @@ def check_fused_gemms(rt, quick):
             ctx.finalize()
     for (m, N, K) in shapes:   # m = rows per rank of the output
         ctx = ops.create_gemm_rs_context(max_M=m * W, N=N)
-        for it in range(3):
+        for it in range(5):
+            ctx.kernel_form = "auto" if it < 3 else "single"
             a = (torch.randn(m * W, K, device="cuda") * 0.1 * (rt.rank + 1)).to(torch.bfloat16)
             b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
             out = ops.gemm_rs(a, b, ctx)

@@ -218,7 +218,10 @@ void gemm_rs_bf16(SymmHeap& h, const at::Tensor& a, const at::Tensor& b, at::Ten
   std::memset(&g, 0, sizeof(g));
   g.mode = tdb::kGemmReduceScatter;
   g.M = M; g.N = N; g.K = K;
-  g.cta_pair = pick_cta_pair(m, N, block_n, true) ? 1 : 0;
+  const bool out_tma_ok = out.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15u) == 0;
+  g.cta_pair = pick_cta_pair(m, N, block_n, out_tma_ok) ? 1 : 0;
+  if (g.cta_pair)
+    g.tmap_out = make_tmap3(out.data_ptr(), tdb::kBF16, 1, m, N, out.stride(0) * 2, out.stride(0) * 2 * m, 128, 64);
   g.block_n = g.cta_pair ? 256 : pick_block_n(N, block_n);
   g.tmap_a = make_tmap3(a.data_ptr(), tdb::kBF16, 1, M, K, a.stride(0) * 2, a.stride(0) * 2 * M, 128, 64);
   g.tmap_b = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N,

@@ -688,7 +688,8 @@ __device__ __forceinline__ Tile decode_tile_pair(const KParams& p, int t, int ti
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ PeerMaps peer_maps,
-                 const __grid_constant__ CUtensorMap tmap_a_local, const KParams p) {
+                 const __grid_constant__ CUtensorMap tmap_a_local, const __grid_constant__ CUtensorMap tmap_out,
+                 const KParams p) {
   using L = PairLayout;
   constexpr int kStages = L::kStages;
   constexpr int BN = kPairBN;
@@ -860,8 +861,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         tc_fence_after_sync();
         const uint32_t t_acc = tmem_base + b * BN + (static_cast<uint32_t>(q * 32) << 16);
-        const CUtensorMap* cmap = (p.mode == kGemmReduceScatter) ? &peer_maps.m[tl.seg] : &tmap_c;
-        const int c2 = (p.mode == kGemmReduceScatter) ? (buf * p.symm.world + p.symm.rank) : tl.seg;
+        // reduce-scatter: tiles of this rank's own segment (computed last) are summed with the partials the other
+        // ranks have already delivered, straight from the fp32 accumulators, and go to the output; no separate
+        // reduction pass remains
+        const bool own_seg = (p.mode == kGemmReduceScatter) && tl.seg == p.symm.rank;
+        const CUtensorMap* cmap = own_seg ? &tmap_out : (p.mode == kGemmReduceScatter) ? &peer_maps.m[tl.seg] : &tmap_c;
+        const int c2 = own_seg ? 0 : (p.mode == kGemmReduceScatter) ? (buf * p.symm.world + p.symm.rank) : tl.seg;
+        if (own_seg && valid_m) {
+          const int et = threadIdx.x - 64;
+          bool wok = true;
+          if (et < p.symm.world && et != p.symm.rank) {
+            const uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + et) * p.max_tiles +
+                                   mt * p.tiles_n + tl.nt;
+            wok = wait_until(p.symm, flag, epoch, kCmpGe, kKernelGemmRs, 3, et, mt * p.tiles_n + tl.nt);
+          }
+          if (!wok) *abort_flag = 1;
+          epi_bar();
+          if (*abort_flag != 0) {
+            ok = false;
+            break;
+          }
+        }
+        const int seg_row = mt * kBM + row_in_tile;
+        const bool row_ok = valid_m && seg_row < p.seg_rows;
 #pragma unroll 1
         for (int c = 0; c < BN / kEpiCols; ++c, ++chunk_ctr) {
           uint32_t r0[32], r1[32];
@@ -871,6 +893,32 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (c == BN / kEpiCols - 1) {
             tc_fence_before_sync();
             mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[b]), 0));
+          }
+          if (own_seg && row_ok) {
+            const int col0 = tl.n0 + c * kEpiCols;
+            for (int s = 0; s < p.symm.world; ++s) {
+              if (s == p.symm.rank) continue;
+              const __nv_bfloat16* src = p.rs_slots + (static_cast<uint64_t>(buf) * p.symm.world + s) * p.rs_slot_elems +
+                                         static_cast<uint64_t>(seg_row) * p.N + col0;
+              uint4 u[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                u[j] = (col0 + 8 * j + 8 <= p.N) ? ld_relaxed_sys_v4(src + 8 * j) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                uint32_t* r = (j < 4) ? &r0[8 * j] : &r1[8 * (j - 4)];
+                const float2 f0 = unpack_bf16x2(u[j].x), f1 = unpack_bf16x2(u[j].y), f2 = unpack_bf16x2(u[j].z),
+                             f3 = unpack_bf16x2(u[j].w);
+                r[0] = __float_as_uint(__uint_as_float(r[0]) + f0.x);
+                r[1] = __float_as_uint(__uint_as_float(r[1]) + f0.y);
+                r[2] = __float_as_uint(__uint_as_float(r[2]) + f1.x);
+                r[3] = __float_as_uint(__uint_as_float(r[3]) + f1.y);
+                r[4] = __float_as_uint(__uint_as_float(r[4]) + f2.x);
+                r[5] = __float_as_uint(__uint_as_float(r[5]) + f2.y);
+                r[6] = __float_as_uint(__uint_as_float(r[6]) + f3.x);
+                r[7] = __float_as_uint(__uint_as_float(r[7]) + f3.y);
+              }
+            }
           }
           uint8_t* stg = stage_base + (chunk_ctr & 1) * kEpiBytes;
           if (leader) bulk_wait_read<1>();
@@ -902,7 +950,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             bulk_commit();
           }
         }
-        if (p.mode == kGemmReduceScatter && leader && valid_m) {
+        if (p.mode == kGemmReduceScatter && !own_seg && leader && valid_m) {
           bulk_wait<0>();
           fence_proxy_async();
           fence_acq_rel_sys();
@@ -923,7 +971,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after_sync();
       tmem_dealloc_pair(tmem_base, 2 * BN);
     }
-    if (p.mode == kGemmReduceScatter && *abort_flag == 0) rs_reduce(p, epoch, BN);
   }
 
   if (p.ctx != nullptr) {
@@ -1030,7 +1077,9 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   memcpy(&tc, a.tmap_c.bytes, sizeof(CUtensorMap));
   PeerMaps pm;
   memcpy(&pm, a.tmap_peer_c, sizeof(PeerMaps));
-  gemm_pair_kernel<<<grid, kThreads, smem, stream>>>(ta, tb, tc, pm, tl, p);
+  CUtensorMap to;
+  memcpy(&to, a.tmap_out.bytes, sizeof(CUtensorMap));
+  gemm_pair_kernel<<<grid, kThreads, smem, stream>>>(ta, tb, tc, pm, tl, to, p);
   return cudaGetLastError();
 }
 
