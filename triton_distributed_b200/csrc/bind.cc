@@ -272,9 +272,9 @@ void skinny_gemm_bf16(const at::Tensor& x, const at::Tensor& w, at::Tensor& out,
   a.tmap_x = m;
   a.out = out.data_ptr();
   a.ld_out = out.stride(0);
-  a.splits = splits > 0 ? splits : tdb::skinny_gemm_pick_splits(N, K, sm_count(), M);
+  a.splits = splits > 0 ? splits : 0;
   a.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
-  if (a.splits > 1) {
+  {
     TORCH_CHECK(acc.scalar_type() == at::kFloat && acc.numel() >= M * N, "skinny_gemm: accumulation buffer too small");
     TORCH_CHECK(counters.scalar_type() == at::kInt && counters.numel() >= (N + 127) / 128, "skinny_gemm: counters too small");
     a.acc = acc.data_ptr<float>();
@@ -313,7 +313,7 @@ void gemm_ar_bf16(SymmHeap& h, const at::Tensor& x, const at::Tensor& w, at::Ten
   a.tmap_x = m;
   a.out = out.data_ptr();
   a.ld_out = out.stride(0);
-  a.splits = splits > 0 ? splits : tdb::skinny_gemm_pick_splits(N, K, sm_count(), M);
+  a.splits = splits > 0 ? splits : 0;
   a.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
   a.acc = acc.data_ptr<float>();
   a.counters = reinterpret_cast<uint32_t*>(counters.data_ptr());

@@ -4,11 +4,13 @@
 //
 // The problem is swapped so that the weight rows fill the 128-row dimension of tcgen05.mma: the A operand is a
 // 128 x 64 weight tile, the B operand the M_pad x 64 activation tile, and the accumulator in TMEM is
-// [128 lanes = output columns] x [M_pad columns = tokens].  A work item is (128 output columns, one K split); the
-// persistent grid streams the weights exactly once through a deep TMA ring, which is what bounds decode GEMMs.
-// Split-K partials are added with red.global.add.f32 into an accumulation buffer; the CTA that arrives last on a
-// column tile converts it, clears the buffer again (self-cleaning, CUDA-graph safe) and, in all-reduce mode, runs
-// the cross-rank sum for that tile right away:
+// [128 lanes = output columns] x [M_pad columns = tokens].  The work is the flattened list of (column tile, k-block)
+// units; every CTA takes one contiguous, equally long range of it ("stream-K"), so all SMs stream the same number of
+// weight bytes whatever the tile count is, and the weights are read exactly once through a deep TMA ring, which is
+// what bounds decode GEMMs.  A range covers pieces of one to three tiles.  A piece that spans a tile's whole K is
+// stored directly; other pieces are added with red.global.add.f32 into an accumulation buffer, and the CTA that
+// arrives last on a column tile converts it, clears the buffer again (self-cleaning, CUDA-graph safe) and, in
+// all-reduce mode, runs the cross-rank sum for that tile right away:
 //     NVLS:  store the bf16 partial tile to the heap, flag all ranks, wait for all ranks' flags of this tile,
 //            multimem.ld_reduce the tile (summed inside the switch) -> out
 //     push:  store the partial tile into slot [rank] on every peer, flag, wait, sum the W slots -> out
@@ -18,6 +20,8 @@
 // (per-tile flags, consumer CTAs reduce with multimem.ld_reduce, double-buffered phases :74-92), layer wrapper
 // layers/nvidia/gemm_allreduce_layer.py:32-116.
 #include <cuda.h>
+
+#include <cstdlib>
 
 #include "tdb/api.h"
 #include "tdb/symm_device.cuh"
@@ -46,7 +50,8 @@ struct Layout {
 
 struct KP {
   int M, N, K;
-  int tiles_n, splits, kb_total;
+  int tiles_n, kb_total;
+  int per_cta;               // (tile, k-block) units per CTA
   __nv_bfloat16* out;        // [M, N]
   int64_t ld_out;
   float* acc;                // [M_cap, N] fp32 split-K accumulation (all zero between calls)
@@ -63,6 +68,29 @@ struct KP {
 };
 
 TDB_DEVICE void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// The pieces of this CTA's unit range, in order: (column tile, [kb0, kb1)).
+struct PieceIter {
+  int u, u1, kb_total;
+  int nt, kb0, kb1;
+  TDB_DEVICE PieceIter(const KP& p) : kb_total(p.kb_total) {
+    const int total = p.tiles_n * p.kb_total;
+    u = min(total, static_cast<int>(blockIdx.x) * p.per_cta);
+    u1 = min(total, u + p.per_cta);
+  }
+  TDB_DEVICE bool next() {
+    if (u >= u1) return false;
+    nt = u / kb_total;
+    kb0 = u - nt * kb_total;
+    kb1 = min(kb_total, kb0 + (u1 - u));
+    u += kb1 - kb0;
+    return true;
+  }
+};
+// number of CTAs whose ranges touch tile nt
+TDB_DEVICE int pieces_of_tile(const KP& p, int nt) {
+  return ((nt + 1) * p.kb_total - 1) / p.per_cta - (nt * p.kb_total) / p.per_cta + 1;
+}
 
 template <int MPAD>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -106,22 +134,18 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_smem;
 
-  const int items = p.tiles_n * p.splits;
-  const int kb_per = (p.kb_total + p.splits - 1) / p.splits;
-
   if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0, issued = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
-        const int nt = w / p.splits, sp = w - nt * p.splits;
-        const int kb0 = sp * kb_per, kb1 = min(p.kb_total, kb0 + kb_per);
+      for (PieceIter pc(p); ok && pc.next();) {
+        const int nt = pc.nt, kb0 = pc.kb0, kb1 = pc.kb1;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kMbarTimeoutNs)) {
             ok = false;
-            report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 10, -1, s, (int)ph, w);
+            report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 10, -1, s, (int)ph, nt);
             break;
           }
           uint8_t* sw = smem + s * L::kStageBytes;
@@ -143,14 +167,13 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       uint32_t it = 0;
       int local = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++local) {
-        const int nt = w / p.splits, sp = w - nt * p.splits;
-        const int kb0 = sp * kb_per, kb1 = min(p.kb_total, kb0 + kb_per);
+      for (PieceIter pc(p); ok && pc.next(); ++local) {
+        const int kb0 = pc.kb0, kb1 = pc.kb1;
         const int b = local & 1;
         const uint32_t aph = (local >> 1) & 1;
         if (!mbar_wait(&tmem_empty[b], aph ^ 1, abort_flag, kMbarTimeoutNs)) {
           ok = false;
-          report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 20, -1, b, (int)aph, w);
+          report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 20, -1, b, (int)aph, pc.nt);
           break;
         }
         tc_fence_after_sync();
@@ -160,7 +183,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, kMbarTimeoutNs)) {
             ok = false;
-            report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 21, -1, s, (int)ph, w);
+            report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 21, -1, s, (int)ph, pc.nt);
             break;
           }
           tc_fence_after_sync();
@@ -172,7 +195,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             umma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           umma_commit(&empty_bar[s]);
         }
-        // an empty K range (more splits than k-blocks) still has to release the epilogue: commit with no MMAs
         if (ok) umma_commit(&tmem_full[b]);
       }
       if (!ok) *abort_flag = 1;
@@ -183,21 +205,21 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const int W = p.symm.world, rank = p.symm.rank;
     int local = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++local) {
-      const int nt = w / p.splits, sp = w - nt * p.splits;
-      const int kb0 = sp * kb_per, kb1 = min(p.kb_total, kb0 + kb_per);
+    for (PieceIter pc(p); ok && pc.next(); ++local) {
+      const int nt = pc.nt;
       const int b = local & 1;
       const uint32_t aph = (local >> 1) & 1;
       if (!mbar_wait(&tmem_full[b], aph, abort_flag, kMbarTimeoutNs)) {
         ok = false;
-        if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 30, -1, b, (int)aph, w);
+        if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 30, -1, b, (int)aph, nt);
         break;
       }
       tc_fence_after_sync();
       const int n = nt * kTN + q * 32 + lane;   // this thread's output column
       const bool n_ok = n < p.N;
-      const bool direct = (p.splits == 1 && p.mode == 0);
-      const bool has_k = kb1 > kb0;
+      const int pieces = pieces_of_tile(p, nt);
+      const bool direct = (pieces == 1 && p.mode == 0);
+      constexpr bool has_k = true;
 #pragma unroll 1
       for (int c = 0; c < MPAD / 16; ++c) {
         uint32_t r[16];
@@ -224,7 +246,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       epi_bar();
       if (leader) {
         const uint32_t prev = atomicAdd(p.counters + nt, 1u);
-        *is_last = (prev == static_cast<uint32_t>(p.splits) - 1) ? 1 : 0;
+        *is_last = (prev == static_cast<uint32_t>(pieces) - 1) ? 1 : 0;
         if (*is_last) p.counters[nt] = 0;
       }
       epi_bar();
@@ -244,14 +266,15 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         ld_dst = p.N;
       }
       if (n_ok) {
-        // batches of 8 independent loads: one L2 round trip per batch instead of one per row
-        for (int m0 = 0; m0 < p.M; m0 += 8) {
-          float v[8];
+        // batches of independent loads: one L2 round trip per batch instead of one per row
+        constexpr int kBatch = MPAD < 32 ? MPAD : 32;
+        for (int m0 = 0; m0 < p.M; m0 += kBatch) {
+          float v[kBatch];
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
+          for (int j = 0; j < kBatch; ++j)
             v[j] = (m0 + j < p.M) ? __ldcg(p.acc + static_cast<int64_t>(m0 + j) * p.N + n) : 0.f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < kBatch; ++j) {
             if (m0 + j < p.M) {
               p.acc[static_cast<int64_t>(m0 + j) * p.N + n] = 0.f;
               dst[static_cast<int64_t>(m0 + j) * ld_dst + n] = __float2bfloat16(v[j]);
@@ -391,9 +414,20 @@ cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream) {
   KP p;
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.tiles_n = (a.N + kTN - 1) / kTN;
-  p.splits = a.splits < 1 ? 1 : a.splits;
   p.kb_total = (a.K + kBK - 1) / kBK;
-  if (p.splits > p.kb_total) p.splits = p.kb_total;
+  // stream-K partition: equal unit ranges over the CTAs.  splits == 0 keeps at least `min_units` k-blocks per CTA
+  // (a shorter range does not pay for the pipeline fill and the split accumulation); splits >= 1 asks for about that
+  // many pieces per tile.
+  const int total_units = p.tiles_n * p.kb_total;
+  const int num_ctas = a.num_ctas < 1 ? 1 : a.num_ctas;
+  const int even = (total_units + num_ctas - 1) / num_ctas;
+  static const int min_units = [] {
+    const char* e = std::getenv("TDB200_SKINNY_MIN_UNITS");
+    const int v = e ? std::atoi(e) : 8;
+    return v < 1 ? 1 : v;
+  }();
+  const int want = a.splits >= 1 ? (p.kb_total + a.splits - 1) / a.splits : min_units;
+  p.per_cta = even > want ? even : want;
   p.out = reinterpret_cast<__nv_bfloat16*>(a.out);
   p.ld_out = a.ld_out;
   p.acc = a.acc;
@@ -408,11 +442,10 @@ cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream) {
   p.ctx = a.ctx;
   static_assert(sizeof(SymmInfo) == sizeof(SymmInfoHost), "SymmInfo mirrors must match");
   memcpy(&p.symm, &a.symm, sizeof(SymmInfo));
-  if ((p.splits > 1 || p.mode == 1) && (a.acc == nullptr || a.counters == nullptr)) return cudaErrorInvalidValue;
+  if ((p.per_cta < p.kb_total || p.per_cta % p.kb_total != 0 || p.mode == 1) && (a.acc == nullptr || a.counters == nullptr))
+    return cudaErrorInvalidValue;
   if (p.mode == 1 && (p.tiles_n > a.max_tiles || a.M > a.m_cap || a.ctx == nullptr)) return cudaErrorInvalidValue;
-  const int items = p.tiles_n * p.splits;
-  int grid = a.num_ctas < items ? a.num_ctas : items;
-  if (grid < 1) grid = 1;
+  const int grid = (total_units + p.per_cta - 1) / p.per_cta;
   switch (skinny_gemm_mpad(a.M)) {
     case 16: return launch_t<16>(a, p, grid, stream);
     case 32: return launch_t<32>(a, p, grid, stream);

@@ -102,9 +102,9 @@ struct SkinnyGemmArgs {
   TensorMap tmap_x;        // X [M, K], box [M_pad x 64], 128-byte swizzle
   void* out;               // bf16 [M, ld_out]
   int64_t ld_out;
-  int splits;              // K splits (>= 1)
+  int splits;              // 0: automatic stream-K partition; >= 1: about this many pieces per column tile
   int num_ctas;
-  float* acc;              // fp32 [m_cap, N], all zero between calls (needed when splits > 1 or all_reduce)
+  float* acc;              // fp32 [m_cap, N], all zero between calls
   uint32_t* counters;      // [ceil(N/128)], zero between calls
   int all_reduce;
   int use_multimem;
