@@ -70,8 +70,16 @@ def main():
 
             t_own, t_ref = timeit(own), timeit(ref)
             ideal = N * K * 2 / (hbm * 1e3)
-            print(json.dumps({"op": name, "B": B, "N": N, "K": K, "own_us": round(t_own, 2), "torch_us": round(t_ref, 2),
-                              "hbm_ideal_us": round(ideal, 2), "own_frac_of_hbm": round(ideal / t_own, 3)}), flush=True)
+            rec = {"op": name, "B": B, "N": N, "K": K, "skinny_us": round(t_own, 2), "torch_us": round(t_ref, 2),
+                   "hbm_ideal_us": round(ideal, 2), "skinny_frac_of_hbm": round(ideal / t_own, 3)}
+            if ops.gemv_supported(B, K):
+                def gemv():
+                    i[0] = (i[0] + 1) % ncopy
+                    ops.gemv_fused(x, ws[i[0]], out=out)
+
+                t_gemv = timeit(gemv)
+                rec.update({"gemv_us": round(t_gemv, 2), "gemv_frac_of_hbm": round(ideal / t_gemv, 3)})
+            print(json.dumps(rec), flush=True)
             del ws
         # attention
         L = args.ctx

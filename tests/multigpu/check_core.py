@@ -188,6 +188,32 @@ def check_gemm_ar(rt):
     log(rt, "OK gemm_allreduce")
 
 
+def check_gemv_ar(rt):
+    """Fused decode GEMV: RMSNorm / SiLU*up prologue, all-reduce + in-place residual epilogue, both reduce paths."""
+    for (N, K) in [(5120, 3200), (5120, 1024), (264, 520)]:
+        for use_mc in ([True, False] if rt.has_multicast else [False]):
+            ctx = ops.create_gemv_ar_context(N, use_multimem=use_mc)
+            for M in (1, 3, 8):
+                for it, mode in enumerate(("plain", "silu", "norm", "plain")):
+                    torch.manual_seed(1000 * M + it)   # same residual stream on every rank
+                    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+                    torch.manual_seed(77 + rt.rank + 10 * it)
+                    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+                    x = torch.randn(M, 2 * K if mode == "silu" else K, device="cuda", dtype=torch.bfloat16)
+                    kw = {"silu_mul": True} if mode == "silu" else {}
+                    if mode == "norm":
+                        kw["norm_weight"] = (1.0 + 0.1 * torch.randn(K, device="cuda")).to(torch.bfloat16)
+                    ref = ops.gemv_reference(x, w, residual=res, group=rt.group, all_reduce=True, **kw).float()
+                    buf = res.clone()
+                    ops.gemv_fused(x, w, out=buf, residual=buf, ar_ctx=ctx, **kw)
+                    torch.cuda.synchronize()
+                    rt.check_status()
+                    err = (buf.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+                    assert err < 3e-2, f"gemv_ar {mode} M={M} N={N} K={K} mc={use_mc}: rel err {err}"
+            ctx.finalize()
+    log(rt, "OK gemv_allreduce")
+
+
 def check_dist_decode(rt):
     from triton_distributed_b200.parallel import SpGQAFlashDecodeAttention
 
@@ -243,7 +269,8 @@ def main():
     t0 = time.time()
     checks = {"primitives": lambda: check_primitives(rt), "allreduce": lambda: check_allreduce(rt, args.quick),
               "rs_ag": lambda: check_rs_ag(rt), "fused": lambda: check_fused_gemms(rt, args.quick),
-              "gemm_ar": lambda: check_gemm_ar(rt), "dist_decode": lambda: check_dist_decode(rt)}
+              "gemm_ar": lambda: check_gemm_ar(rt), "gemv_ar": lambda: check_gemv_ar(rt),
+              "dist_decode": lambda: check_dist_decode(rt)}
     for name, fn in checks.items():
         if args.only and name not in args.only.split(","):
             continue

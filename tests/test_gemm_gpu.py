@@ -72,3 +72,38 @@ def test_skinny_gemm_split_k(shape):
         torch.cuda.synchronize()
         err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
         assert err < 2e-2, f"skinny {shape} splits={splits}: rel err {err}"
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("mode", ["plain", "norm", "silu", "norm_residual"])
+def test_gemv_fused(M, mode):
+    # decode GEMV with fused RMSNorm / SiLU*up prologue and residual epilogue against the fp32 reference
+    from triton_distributed_b200 import ops
+
+    torch.manual_seed(M)
+    for (N, K) in [(1280, 5120), (5120, 1024), (6400, 5120), (5120, 3200), (136, 64), (1003, 264)]:
+        w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+        kw = {}
+        if mode == "silu":
+            x = torch.randn(M, 2 * K, device="cuda", dtype=torch.bfloat16)
+            kw["silu_mul"] = True
+        else:
+            x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        if mode.startswith("norm"):
+            kw["norm_weight"] = (1.0 + 0.1 * torch.randn(K, device="cuda")).to(torch.bfloat16)
+            kw["eps"] = 1e-6
+        res = None
+        if mode == "norm_residual":
+            res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+        ref = ops.gemv_reference(x, w, residual=res, **kw).float()
+        out = ops.gemv_fused(x, w, residual=res, **kw)
+        torch.cuda.synchronize()
+        err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+        assert err < 2e-2, f"gemv {mode} M={M} N={N} K={K}: rel err {err}"
+        if res is not None:
+            # in place: out aliases the residual
+            buf = res.clone()
+            ops.gemv_fused(x, w, out=buf, residual=buf, **kw)
+            torch.cuda.synchronize()
+            err = (buf.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+            assert err < 2e-2, f"gemv in-place {mode} M={M} N={N} K={K}: rel err {err}"

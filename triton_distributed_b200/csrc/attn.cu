@@ -124,6 +124,8 @@ __global__ void decode_combine_kernel(const float* part_out, const float* part_l
                                       float* out_f32, int splits, int D) {
   const int64_t bh = blockIdx.x;
   const int d = threadIdx.x;
+  // a successor launched programmatically (the output projection's GEMV) may begin fetching its weights now
+  pdl_launch_dependents();
   float v;
   const float lse = merge_partials(part_out + bh * splits * D, part_lse + bh * splits, splits, D, d, &v);
   if (out) out[bh * D + d] = __float2bfloat16(v);

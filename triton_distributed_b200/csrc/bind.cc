@@ -8,6 +8,7 @@
 #include <torch/extension.h>
 
 #include "tdb/api.h"
+#include "tdb/gemv.h"
 #include "tdb/symm_heap.h"
 
 namespace py = pybind11;
@@ -328,6 +329,71 @@ void gemm_ar_bf16(SymmHeap& h, const at::Tensor& x, const at::Tensor& w, at::Ten
   check_cuda(tdb::launch_skinny_gemm(a, cur_stream()), "launch_skinny_gemm(all-reduce)");
 }
 
+// Decode GEMV (M <= 8) with the fused prologue / epilogue.  `heap` is null without all-reduce.
+void fill_gemv(tdb::GemvArgs& a, const at::Tensor& x, const at::Tensor& w, at::Tensor& out,
+               const c10::optional<at::Tensor>& norm_w, double eps, bool silu_mul,
+               const c10::optional<at::Tensor>& residual, int num_ctas) {
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16,
+              "gemv: bf16 expected");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1,
+              "gemv: 2-D tensors with contiguous rows expected");
+  const int64_t M = x.size(0), K = w.size(1), N = w.size(0);
+  TORCH_CHECK(x.size(1) == (silu_mul ? 2 * K : K), "gemv: x has ", x.size(1), " columns, expected ", silu_mul ? 2 * K : K);
+  TORCH_CHECK(out.size(0) == M && out.size(1) == N, "gemv: output shape mismatch");
+  TORCH_CHECK(M >= 1 && M <= 8, "gemv: 1 <= M <= 8");
+  TORCH_CHECK(K <= tdb::gemv_max_k(M), "gemv: K too large for the shared-memory staging of ", M, " rows");
+  std::memset(&a, 0, sizeof(a));
+  a.M = M; a.N = N; a.K = K;
+  a.x = x.data_ptr(); a.ldx = x.stride(0);
+  a.w = w.data_ptr(); a.ldw = w.stride(0);
+  a.out = out.data_ptr(); a.ld_out = out.stride(0);
+  if (norm_w.has_value()) {
+    TORCH_CHECK(norm_w->scalar_type() == at::kBFloat16 && norm_w->numel() == K && norm_w->is_contiguous(), "gemv: norm weight [K] bf16");
+    a.norm_w = norm_w->data_ptr();
+  }
+  a.eps = static_cast<float>(eps);
+  a.silu_mul = silu_mul ? 1 : 0;
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->size(0) == M &&
+                    residual->size(1) == N && residual->stride(1) == 1, "gemv: residual [M, N] bf16");
+    a.residual = residual->data_ptr();
+    a.ld_res = residual->stride(0);
+  }
+  a.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
+  a.symm.world = 1;
+  a.symm.timeout_ns = 2000000000ull;
+}
+
+void gemv_bf16(const at::Tensor& x, const at::Tensor& w, at::Tensor& out, const c10::optional<at::Tensor>& norm_w,
+               double eps, bool silu_mul, const c10::optional<at::Tensor>& residual, int num_ctas) {
+  c10::cuda::CUDAGuard guard(x.device());
+  tdb::GemvArgs a;
+  fill_gemv(a, x, w, out, norm_w, eps, silu_mul, residual, num_ctas);
+  check_cuda(tdb::launch_gemv(a, cur_stream()), "launch_gemv");
+}
+
+void gemv_ar_bf16(SymmHeap& h, const at::Tensor& x, const at::Tensor& w, at::Tensor& out,
+                  const c10::optional<at::Tensor>& norm_w, double eps, bool silu_mul,
+                  const c10::optional<at::Tensor>& residual, at::Tensor& partial, at::Tensor& flags, at::Tensor& ctx,
+                  int64_t m_cap, int64_t max_ctas, int num_ctas, bool use_multimem, double timeout_s) {
+  c10::cuda::CUDAGuard guard(x.device());
+  tdb::GemvArgs a;
+  fill_gemv(a, x, w, out, norm_w, eps, silu_mul, residual, num_ctas);
+  const int W = h.world();
+  const bool mc = use_multimem && h.has_multicast();
+  TORCH_CHECK(static_cast<uint64_t>(partial.numel()) >= 2ull * (mc ? 1 : W) * m_cap * a.N, "gemv_ar: partial buffer too small");
+  TORCH_CHECK(flags.numel() >= static_cast<int64_t>(W) * max_ctas, "gemv_ar: flag buffer too small");
+  a.all_reduce = 1;
+  a.use_multimem = mc ? 1 : 0;
+  a.partial = partial.data_ptr();
+  a.flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
+  a.max_ctas = max_ctas;
+  a.m_cap = m_cap;
+  a.ctx = reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr());
+  a.symm = h.info(static_cast<uint64_t>(timeout_s * 1e9));
+  check_cuda(tdb::launch_gemv(a, cur_stream()), "launch_gemv(all-reduce)");
+}
+
 }  // namespace
 
 void bind_more(py::module_& m);  // bind_ops.inc-style split kept in this file for build simplicity
@@ -385,5 +451,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("skinny_gemm_bf16", &skinny_gemm_bf16);
   m.def("gemm_ar_bf16", &gemm_ar_bf16);
   m.def("skinny_gemm_pick_splits", &tdb::skinny_gemm_pick_splits);
+  m.def("gemv_bf16", &gemv_bf16, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("norm_w") = py::none(),
+        py::arg("eps") = 1e-6, py::arg("silu_mul") = false, py::arg("residual") = py::none(), py::arg("num_ctas") = 0);
+  m.def("gemv_ar_bf16", &gemv_ar_bf16);
+  m.def("gemv_max_k", &tdb::gemv_max_k);
   bind_more(m);
 }

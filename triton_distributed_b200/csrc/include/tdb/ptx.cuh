@@ -206,6 +206,14 @@ TDB_DEVICE void umma_commit(uint64_t* bar) {
 }
 
 // ----------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while its
+// predecessor in the stream still runs; pdl_wait() blocks until the predecessor has completed and its writes are
+// visible (a no-op for a normal launch), pdl_launch_dependents() lets the successor start launching now.
+// ----------------------------------------------------------------------------
+TDB_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+TDB_DEVICE void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------
 // CTA pairs (cta_group::2): two CTAs of a cluster on adjacent SMs run one MMA of 256 rows.  CTA 0 of the pair issues
 // the MMAs; each CTA supplies its own 128 rows of A and its half of the B tile from its own shared memory and holds
 // its 128 accumulator rows in its own TMEM.  Barriers that the other CTA must reach are addressed in the

@@ -40,6 +40,7 @@ enum KernelId : int32_t {
   kKernelMoeReduce = 15,
   kKernelP2P = 16,
   kKernelPrimitive = 17,
+  kKernelGemv = 18,
 };
 
 // One record; the first writer wins (code is set with atomicCAS from kOk).

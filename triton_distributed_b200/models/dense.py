@@ -47,6 +47,20 @@ class DenseLLMLayer:
         return m.reshape(shape), residual
 
 
+    def fwd_fused_decode(self, stream: torch.Tensor, position_ids, kv_cache, gemv_ctx):
+        """Decode step for up to eight tokens with four fused GEMV launches plus attention: ``stream`` [M, H] holds
+        the residual stream and is updated in place (norms in the GEMV prologues, all-reduce and residual add in
+        their epilogues, SiLU*up in the down projection's prologue)."""
+        a, m = self.attn, self.mlp
+        bsz = stream.shape[0]
+        qkv = ops.gemv_fused(stream, a.wqkv, norm_weight=self.input_norm_w, eps=self.eps)
+        o = a._attend(qkv, position_ids, kv_cache, self.layer_idx, bsz, 1)
+        ops.gemv_fused(o, a.wo, out=stream, residual=stream, ar_ctx=gemv_ctx)
+        gu = ops.gemv_fused(stream, m.gate_up_proj, norm_weight=self.post_norm_w, eps=self.eps)
+        ops.gemv_fused(gu, m.down_proj, out=stream, silu_mul=True, residual=stream, ar_ctx=gemv_ctx)
+        return stream
+
+
 class DenseLLM:
     def __init__(self, model_config: ModelConfig, group=None):
         self.rt = get_runtime()
@@ -149,6 +163,16 @@ class DenseLLM:
         l0.attn._init_gemm_ar_ctx(max_M)
         l0.mlp.gemm_ar_ctx = l0.attn.gemm_ar_ctx   # same N = hidden for both row-parallel projections
         self._share_ctx(("gemm_ar_ctx",), l0.attn, l0.mlp)
+        # decode steps of up to eight tokens take the fused GEMV path; one scratch set serves every layer
+        self.gemv_ctx = ops.create_gemv_ar_context(self.arch.hidden_size)
+
+    def _fused_decode_ok(self, B: int, S: int) -> bool:
+        a = self.arch
+        return (self.mode in ("triton_dist_gemm_ar", "gemm_ar") and S == 1 and getattr(self, "gemv_ctx", None) is not None
+                and self.embed_tokens.is_cuda and self.embed_tokens.dtype == torch.bfloat16
+                and ops.gemv_supported(B, a.hidden_size)
+                and ops.gemv_supported(B, a.intermediate_size // self.world_size)
+                and ops.gemv_supported(B, a.num_attention_heads * a.head_dim // self.world_size))
 
     def init_ctx_for(self, mode: str, max_M: int):
         if mode == "torch":
@@ -173,6 +197,13 @@ class DenseLLM:
             bl = B // self.world_size
             ids = input_ids[self.rank * bl:(self.rank + 1) * bl]
         hidden = ops.embedding(ids, self.embed_tokens)
+        if self._fused_decode_ok(B, S):
+            stream = hidden.reshape(B, -1)
+            for l in self.layers:
+                l.fwd_fused_decode(stream, position_ids, kv_cache, self.gemv_ctx)
+            if wo_lm_head:
+                return ops.rmsnorm(stream, self.final_norm_w, self.arch.rms_norm_eps)
+            return ops.gemv_fused(stream, self.lm_head, norm_weight=self.final_norm_w, eps=self.arch.rms_norm_eps).float()
         residual = None
         for l in self.layers:
             hidden, residual = l.fwd(hidden, residual, position_ids, kv_cache)
@@ -187,6 +218,9 @@ class DenseLLM:
         return ops.gemm(x, self.lm_head).float()
 
     def finalize(self):
+        if getattr(self, "gemv_ctx", None) is not None:
+            self.gemv_ctx.finalize()
+            self.gemv_ctx = None
         l0 = self.layers[0]
         l0.attn.finalize()
         l0.mlp.ar_ctx = None if l0.mlp.ar_ctx is l0.attn.ar_ctx else l0.mlp.ar_ctx

@@ -38,7 +38,7 @@ STATUS_CODES = {0: "ok", 1: "timeout waiting for a flag", 2: "timeout waiting fo
 KERNEL_NAMES = {0: "none", 1: "gemm", 2: "ag_gemm", 3: "gemm_rs", 4: "gemm_ar", 5: "all_reduce", 6: "all_gather",
                 7: "reduce_scatter", 8: "barrier", 9: "all_to_all", 10: "ep_dispatch", 11: "ep_combine",
                 12: "flash_decode", 13: "megakernel", 14: "group_gemm", 15: "moe_reduce", 16: "p2p",
-                17: "primitive"}
+                17: "primitive", 18: "gemv"}
 
 
 class CommTimeoutError(RuntimeError):
