@@ -18,6 +18,7 @@
 //   python/triton_dist/kernels/nvidia/flash_decode.py:130-239 (split-KV), :308-482 (combines), :587-760 (fused)
 //   python/triton_dist/layers/nvidia/sp_flash_decode_layer.py:83-185 (partials -> LL all-gather -> LSE merge)
 //   mega_triton_kernel/kernels/flash_attn.py:33-372 and kernels/nvidia/sp_ag_attention_intra_node.py:256-425 (prefill)
+#include "tdb/launch.cuh"
 #include "tdb/attn.h"
 #include "tdb/attn_device.cuh"
 #include "tdb/symm_device.cuh"
@@ -114,10 +115,83 @@ __global__ void __launch_bounds__(kAttnThreads) flash_fwd_kernel(const PrefillPa
 // Decode, split-KV.  q [B, Hq, D].  grid = (splits, Hkv * head_chunks, B).  Partials: out [B, Hq, splits, D] fp32,
 // lse [B, Hq, splits].
 // ---------------------------------------------------------------------------
-template <int D>
+template <int D, int S>
 __global__ void __launch_bounds__(kAttnThreads) decode_splitkv_kernel(const DecodeParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
-  decode_splitkv_body<D>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem, [] { __syncthreads(); });
+  pdl_wait();   // q and the cache rows of the new token come from the previous kernel
+  auto sync = [] { __syncthreads(); };
+  decode_splitkv_body<D, decltype(sync), S>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem, sync);
+  if (p.fuse_counters == nullptr) return;
+  // ---- fused combine: the last CTA to arrive for this (sequence, KV head, head chunk) merges the splits
+  __shared__ int s_last;
+  pdl_launch_dependents();
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* ctr = p.fuse_counters + blockIdx.z * gridDim.y + blockIdx.y;
+    const uint32_t prev = atomicAdd(ctr, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) *ctr = 0;   // every arrival of this call has been counted: leave the counter clean for the next one
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // Merge: the partials come from other CTAs, so they are read at L2.  First the LSEs of all heads of the chunk
+  // go to shared memory and become weights, then every thread sums four output dims of one head over the splits
+  // with several independent 16-byte loads in flight.
+  const int b = blockIdx.z;
+  const int hkv = blockIdx.y / p.head_chunks, hc = blockIdx.y - hkv * p.head_chunks;
+  const int h_begin = hkv * p.group + hc * 16;
+  const int nheads = min(p.group - hc * 16, 16);
+  float* s_w = reinterpret_cast<float*>(smem);          // [nheads][splits] weights
+  float* s_inv = s_w + 16 * p.splits;                   // [nheads] 1 / total
+  for (int i = threadIdx.x; i < nheads * p.splits; i += kAttnThreads) {
+    const int h = i / p.splits, sp = i - h * p.splits;
+    s_w[i] = __ldcg(p.part_lse + (static_cast<int64_t>(b) * p.Hq + h_begin + h) * p.splits + sp);
+  }
+  __syncthreads();
+  if (threadIdx.x < nheads) {
+    float* w = s_w + threadIdx.x * p.splits;
+    float mx = -INFINITY;
+    for (int i = 0; i < p.splits; ++i) mx = fmaxf(mx, w[i]);
+    float tot = 0.f;
+    for (int i = 0; i < p.splits; ++i) {
+      const float e = (mx == -INFINITY) ? 0.f : __expf(w[i] - mx);
+      w[i] = e;
+      tot += e;
+    }
+    s_inv[threadIdx.x] = tot > 0.f ? 1.f / tot : 0.f;
+  }
+  __syncthreads();
+  constexpr int kVecPerHead = D / 4;                     // float4 per head row
+  constexpr int kHeadsPerPass = kAttnThreads / kVecPerHead;
+  const int dv = threadIdx.x % kVecPerHead, sub = threadIdx.x / kVecPerHead;
+  for (int h = sub; h < nheads; h += kHeadsPerPass) {
+    const int64_t bh = static_cast<int64_t>(b) * p.Hq + h_begin + h;
+    const float4* po = reinterpret_cast<const float4*>(p.part_out + bh * p.splits * D) + dv;
+    const float* w = s_w + h * p.splits;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int i = 0;
+    for (; i + 8 <= p.splits; i += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __ldcg(po + static_cast<int64_t>(i + j) * kVecPerHead);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc.x += w[i + j] * v[j].x; acc.y += w[i + j] * v[j].y;
+        acc.z += w[i + j] * v[j].z; acc.w += w[i + j] * v[j].w;
+      }
+    }
+    for (; i < p.splits; ++i) {
+      const float4 v = __ldcg(po + static_cast<int64_t>(i) * kVecPerHead);
+      acc.x += w[i] * v.x; acc.y += w[i] * v.y; acc.z += w[i] * v.z; acc.w += w[i] * v.w;
+    }
+    const float inv = s_inv[h];
+    uint2 o;
+    o.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+    o.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(p.fuse_out + bh * D + dv * 4) = o;
+  }
 }
 
 __global__ void decode_combine_kernel(const float* part_out, const float* part_lse, __nv_bfloat16* out, float* out_lse,
@@ -300,19 +374,26 @@ cudaError_t launch_decode_splitkv(const DecodeArgs& a, cudaStream_t stream) {
   p.splits = a.splits;
   p.scale = a.scale;
   p.softcap = a.softcap;
+  p.fuse_counters = (a.fuse_counters != nullptr && a.fuse_out != nullptr) ? a.fuse_counters : nullptr;
+  p.fuse_out = reinterpret_cast<__nv_bfloat16*>(a.fuse_out);
   dim3 grid(a.splits, a.kv.num_kv_heads * p.head_chunks, a.batch);
+  // A grid of at most one CTA per SM is latency-bound: four stages (three blocks in flight per CTA) instead of two.
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const bool deep = static_cast<int64_t>(grid.x) * grid.y * grid.z <= sms;
+  auto launch = [&](auto kernel, int smem, bool* set) -> cudaError_t {
+    cudaError_t e = ensure_smem(kernel, smem, set);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(kernel, grid, dim3(kAttnThreads), static_cast<size_t>(smem), stream, p);
+  };
+  static bool set128_2 = false, set128_4 = false, set64_2 = false, set64_4 = false;
   if (a.head_dim == 128) {
-    static bool set = false;
-    cudaError_t e = ensure_smem(decode_splitkv_kernel<128>, Tiles<128>::kSmem, &set);
-    if (e != cudaSuccess) return e;
-    decode_splitkv_kernel<128><<<grid, kAttnThreads, Tiles<128>::kSmem, stream>>>(p);
-  } else {
-    static bool set = false;
-    cudaError_t e = ensure_smem(decode_splitkv_kernel<64>, Tiles<64>::kSmem, &set);
-    if (e != cudaSuccess) return e;
-    decode_splitkv_kernel<64><<<grid, kAttnThreads, Tiles<64>::kSmem, stream>>>(p);
+    return deep ? launch(decode_splitkv_kernel<128, 4>, 2 * Tiles<128>::kSmem, &set128_4)
+                : launch(decode_splitkv_kernel<128, 2>, Tiles<128>::kSmem, &set128_2);
   }
-  return cudaGetLastError();
+  return deep ? launch(decode_splitkv_kernel<64, 4>, 2 * Tiles<64>::kSmem, &set64_4)
+              : launch(decode_splitkv_kernel<64, 2>, Tiles<64>::kSmem, &set64_2);
 }
 
 cudaError_t launch_decode_combine(const DecodeArgs& a, void* out_bf16, float* out_lse, float* out_f32,

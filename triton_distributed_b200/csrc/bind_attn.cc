@@ -99,9 +99,21 @@ tdb::DecodeArgs decode_args(const at::Tensor& q, const at::Tensor& k_cache, cons
 // Split-KV decode + local combine.  Any of out / out_lse / out_f32 may be None.
 void decode_attn(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, const at::Tensor& block_table,
                  const at::Tensor& kv_lens, at::Tensor& workspace, int64_t splits, double scale, double softcap,
-                 c10::optional<at::Tensor> out, c10::optional<at::Tensor> out_lse, c10::optional<at::Tensor> out_f32) {
+                 c10::optional<at::Tensor> out, c10::optional<at::Tensor> out_lse, c10::optional<at::Tensor> out_f32,
+                 c10::optional<at::Tensor> counters) {
   c10::cuda::CUDAGuard guard(q.device());
   tdb::DecodeArgs a = decode_args(q, k_cache, v_cache, block_table, kv_lens, workspace, splits, scale, softcap);
+  if (counters.has_value() && out.has_value() && !out_lse.has_value() && !out_f32.has_value()) {
+    // one launch: the last split CTA of every (sequence, KV head) merges the partials
+    const int64_t group = a.num_q_heads / k_cache.size(2);
+    const int64_t need = static_cast<int64_t>(a.batch) * k_cache.size(2) * ((group + 15) / 16);
+    TORCH_CHECK(counters->scalar_type() == at::kInt && counters->numel() >= need, "decode_attn: counters too small");
+    TORCH_CHECK(out->scalar_type() == at::kBFloat16 && out->is_contiguous(), "decode_attn: out must be contiguous bf16");
+    a.fuse_counters = reinterpret_cast<uint32_t*>(counters->data_ptr());
+    a.fuse_out = out->data_ptr();
+    check_cuda(tdb::launch_decode_splitkv(a, cur_stream()), "launch_decode_splitkv(fused combine)");
+    return;
+  }
   check_cuda(tdb::launch_decode_splitkv(a, cur_stream()), "launch_decode_splitkv");
   check_cuda(tdb::launch_decode_combine(a, out.has_value() ? out->data_ptr() : nullptr,
                                         out_lse.has_value() ? out_lse->data_ptr<float>() : nullptr,

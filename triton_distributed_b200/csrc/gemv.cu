@@ -21,6 +21,7 @@
 #include <cstdlib>
 
 #include "tdb/gemv.h"
+#include "tdb/launch.cuh"
 #include "tdb/symm_device.cuh"
 
 namespace tdb {
@@ -318,23 +319,8 @@ cudaError_t launch_t(const GemvParams& p, int grid, size_t smem, cudaStream_t st
     if (e != cudaSuccess) return e;
     set = true;
   }
-  // programmatic dependent launch: the kernel may start while its predecessor in the stream drains; everything it
-  // reads from that predecessor comes after pdl_wait() (TDB200_PDL=0 launches normally)
-  static const bool pdl = [] {
-    const char* e = std::getenv("TDB200_PDL");
-    return e == nullptr || std::atoi(e) != 0;
-  }();
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kGemvThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, gemv_kernel<M>, p);
+  // everything the kernel reads from its predecessor comes after pdl_wait()
+  return launch_pdl(gemv_kernel<M>, dim3(grid), dim3(kGemvThreads), smem, stream, p);
 }
 
 }  // namespace

@@ -2,6 +2,7 @@
 // and a CUDA stream, never allocate, and return a cudaError_t (0 = success).
 // The torch binding (bind.cc) and the C entry points are thin wrappers.
 #pragma once
+#include <cstdlib>
 #include <cuda_runtime.h>
 #include <stdint.h>
 

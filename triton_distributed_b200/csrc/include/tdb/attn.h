@@ -37,6 +37,10 @@ struct DecodeArgs {
   AttnKV kv;
   int batch, num_q_heads, head_dim, splits;
   float scale, softcap;
+  // Optional fused combine: with both set, the CTA that finishes last for a (sequence, KV head) merges the split
+  // partials of its query heads into fuse_out (bf16 [batch, Hq, D]) and no combine launch is needed.
+  uint32_t* fuse_counters = nullptr;   // [batch * Hkv * head_chunks], zero between calls (the kernel leaves them zero)
+  void* fuse_out = nullptr;
 };
 int decode_workspace_floats(int batch, int num_q_heads, int head_dim, int splits);
 cudaError_t launch_decode_splitkv(const DecodeArgs& a, cudaStream_t stream);

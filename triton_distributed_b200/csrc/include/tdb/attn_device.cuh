@@ -201,11 +201,14 @@ struct DecodeParams {
   PagedKV kv;
   int Hq, group, head_chunks, splits;
   float scale, softcap;
+  uint32_t* fuse_counters = nullptr;    // fused combine (see DecodeArgs); null = partials only
+  __nv_bfloat16* fuse_out = nullptr;
 };
 
 // Body of the split-KV decode step for one (split, kv head x head chunk, sequence).  Executed by 128 threads
 // (threadIdx.x < 128); `sync` is a barrier over exactly those threads.
-template <int D, typename Sync>
+// S = shared-memory stages of (K, V) blocks: S - 1 blocks are in flight while one is computed.
+template <int D, typename Sync, int S = 2>
 TDB_DEVICE void decode_splitkv_body(const DecodeParams& p, int split, int yidx, int b, uint8_t* smem, Sync sync) {
   using T = Tiles<D>;
   const int hkv = yidx / p.head_chunks, hc = yidx - hkv * p.head_chunks;
@@ -225,21 +228,25 @@ TDB_DEVICE void decode_splitkv_body(const DecodeParams& p, int split, int yidx, 
   w.load_q(h_lo < p.group ? qb + static_cast<int64_t>(head0 + h_lo) * D : nullptr,
            h_hi < p.group ? qb + static_cast<int64_t>(head0 + h_hi) * D : nullptr);
   const int nblk = blk1 - blk0;
-  if (nblk > 0) {
-    load_kv_block<D>(p.kv, b, hkv, blk0 * kBlockN, kv_len, smem, smem + T::kTileBytes);
+  // one commit group per block, empty when there is no block left, so that "all but the newest S - 1 groups are
+  // complete" always means "block i has landed"
+#pragma unroll
+  for (int j = 0; j < S - 1; ++j) {
+    if (j < nblk) {
+      uint8_t* nK = smem + j * 2 * T::kTileBytes;
+      load_kv_block<D>(p.kv, b, hkv, (blk0 + j) * kBlockN, kv_len, nK, nK + T::kTileBytes);
+    }
     cp_async_commit();
   }
   for (int i = 0; i < nblk; ++i) {
-    uint8_t* sK = smem + (i & 1) * 2 * T::kTileBytes;
+    uint8_t* sK = smem + (i % S) * 2 * T::kTileBytes;
     uint8_t* sV = sK + T::kTileBytes;
-    if (i + 1 < nblk) {
-      uint8_t* nK = smem + ((i + 1) & 1) * 2 * T::kTileBytes;
-      load_kv_block<D>(p.kv, b, hkv, (blk0 + i + 1) * kBlockN, kv_len, nK, nK + T::kTileBytes);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    if (i + S - 1 < nblk) {
+      uint8_t* nK = smem + ((i + S - 1) % S) * 2 * T::kTileBytes;
+      load_kv_block<D>(p.kv, b, hkv, (blk0 + i + S - 1) * kBlockN, kv_len, nK, nK + T::kTileBytes);
     }
+    cp_async_commit();
+    cp_async_wait<S - 1>();
     sync();
     // each warp takes 16 of the block's 64 tokens
     w.template step<2>(sK, sV, (blk0 + i) * kBlockN, warp * 16, kv_len, kv_len, p.scale, p.softcap);

@@ -1,0 +1,31 @@
+// Kernel launch helpers shared by the .cu files.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+
+namespace tdb {
+
+// Launch with the programmatic-dependent-launch attribute: the kernel may be scheduled while its predecessor in the
+// stream drains, and must execute griddepcontrol.wait (pdl_wait) before touching anything the predecessor writes.
+// TDB200_PDL=0 turns the attribute off (the kernels' waits are then no-ops).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  static const bool pdl = [] {
+    const char* e = std::getenv("TDB200_PDL");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+}  // namespace tdb

@@ -8,6 +8,7 @@
 //   layers/nvidia/tp_attn.py:61-67,173 (flashinfer rmsnorm / rope calls these replace)
 //   models/utils.py:86 (sample_token arg-max path)
 // All kernels use 16-byte accesses and fp32 math; one pass over the data.
+#include "tdb/launch.cuh"
 #include "tdb/ops.h"
 #include "tdb/ptx.cuh"
 
@@ -127,6 +128,8 @@ __global__ void qk_norm_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, co
                                        __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int T,
                                        int Hq, int Hkv, int D, int64_t ld_qkv, float eps, float log2_theta,
                                        int64_t cache_slot_stride) {
+  pdl_wait();                 // qkv comes from the previous kernel
+  pdl_launch_dependents();
   const int warps_per_block = blockDim.x >> 5;
   const int64_t wid = static_cast<int64_t>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -303,12 +306,11 @@ cudaError_t launch_qk_norm_rope_kv(const void* qkv, const void* qw, const void* 
   if (T == 0) return cudaSuccess;
   const int64_t warps = static_cast<int64_t>(T) * (Hq + 2 * Hkv);
   const int wpb = 8;
-  qk_norm_rope_kv_kernel<<<static_cast<unsigned>((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(
-      reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const __nv_bfloat16*>(qw),
-      reinterpret_cast<const __nv_bfloat16*>(kw), positions, slots, reinterpret_cast<__nv_bfloat16*>(q_out),
-      reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, D, ld_qkv, eps,
-      log2f(rope_theta), cache_slot_stride);
-  return cudaGetLastError();
+  return launch_pdl(qk_norm_rope_kv_kernel, dim3(static_cast<unsigned>((warps + wpb - 1) / wpb)), dim3(wpb * 32), 0, s,
+                    reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const __nv_bfloat16*>(qw),
+                    reinterpret_cast<const __nv_bfloat16*>(kw), positions, slots, reinterpret_cast<__nv_bfloat16*>(q_out),
+                    reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, D,
+                    ld_qkv, eps, log2f(rope_theta), cache_slot_stride);
 }
 
 cudaError_t launch_embedding(const int64_t* ids, const void* table, void* out, int64_t T, int H, int64_t vocab,

@@ -66,6 +66,8 @@ PRESETS = {
                                      num_experts_per_tok=8, moe_intermediate_size=768),
     "Qwen/Qwen3-235B-A22B": ArchConfig("Qwen/Qwen3-235B-A22B", 4096, 12288, 94, 64, 4, 128, 151936, num_experts=128,
                                        num_experts_per_tok=8, moe_intermediate_size=1536),
+    # what one rank of Qwen3-32B holds under TP=8, as a single-GPU model: lets one GPU profile the per-rank kernels
+    "Qwen/Qwen3-32B-tp8-shard": ArchConfig("Qwen/Qwen3-32B-tp8-shard", 5120, 3200, 64, 8, 1, 128, 18992),
     # small shapes for tests and the smoke check
     "tiny-dense": ArchConfig("tiny-dense", 256, 512, 2, 8, 2, 64, 1024),
     "tiny-moe": ArchConfig("tiny-moe", 256, 512, 2, 8, 2, 64, 1024, num_experts=8, num_experts_per_tok=2,

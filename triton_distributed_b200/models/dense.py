@@ -197,6 +197,13 @@ class DenseLLM:
             bl = B // self.world_size
             ids = input_ids[self.rank * bl:(self.rank + 1) * bl]
         hidden = ops.embedding(ids, self.embed_tokens)
+        kv_cache.begin_step(position_ids, B, S)   # cache rows and kv lengths are the same for every layer
+        try:
+            return self._layers_and_head(hidden, ids, position_ids, kv_cache, B, S, sharded, wo_lm_head)
+        finally:
+            kv_cache.end_step()
+
+    def _layers_and_head(self, hidden, ids, position_ids, kv_cache, B, S, sharded, wo_lm_head):
         if self._fused_decode_ok(B, S):
             stream = hidden.reshape(B, -1)
             for l in self.layers:

@@ -45,6 +45,21 @@ class KV_Cache:
             self._ws = decode_workspace(self.batch_size, num_q_heads, head_dim, self.kv_splits, self.kv_offset.device)
         return self._ws
 
+    # -- per-step values shared by all layers (computed once instead of once per layer) ----------------------
+    def begin_step(self, position_ids: torch.Tensor, bsz: int, q_len: int):
+        self._step = (self.slots_for(position_ids, bsz, q_len), self.kv_lens_after(q_len, bsz), bsz, q_len)
+
+    def end_step(self):
+        self._step = None
+
+    def step_values(self, position_ids: torch.Tensor, bsz: int, q_len: int):
+        """(cache rows of the new tokens, kv lengths after the step): the values of ``begin_step`` when a step is
+        open for the same shape, else computed here."""
+        st = getattr(self, "_step", None)
+        if st is not None and st[2] == bsz and st[3] == q_len:
+            return st[0], st[1]
+        return self.slots_for(position_ids, bsz, q_len), self.kv_lens_after(q_len, bsz)
+
     # -- bookkeeping ------------------------------------------------------------------------------------------
     def inc_offset(self, n: int = 1):
         self.kv_offset += n
@@ -90,6 +105,9 @@ class PagedKVCache:
     decode_workspace = KV_Cache.decode_workspace
     inc_offset = KV_Cache.inc_offset
     clear = KV_Cache.clear
+    begin_step = KV_Cache.begin_step
+    end_step = KV_Cache.end_step
+    step_values = KV_Cache.step_values
 
     def rand_fill(self, length: int):
         self.k_cache.normal_()

@@ -85,18 +85,37 @@ def flash_attn_varlen(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                                return_lse)
 
 
-def pick_kv_splits(batch: int, num_kv_heads: int, head_chunks: int, max_kv_len: int, num_sms: int = 148) -> int:
-    """Number of KV splits: as many as still fit one wave of the grid (three CTAs of the split-KV kernel are resident
-    per SM; a second, partly filled wave costs more than the extra parallelism brings), never more splits than
-    64-token blocks, at most 64."""
+def pick_kv_splits(batch: int, num_kv_heads: int, head_dim_chunks: int, max_kv_len: int, num_sms: int = 148) -> int:
+    """Number of KV splits.  A CTA walks its 64-token blocks one after the other (about a microsecond each) and the
+    merge of the partials grows with the number of splits (about a tenth of that per split), so a small problem takes
+    about sqrt(8 x blocks) splits; a large batch is limited to what still fits one wave of the grid (three CTAs of
+    the split-KV kernel are resident per SM; a second, partly filled wave costs more than the extra parallelism
+    brings).  At most 64."""
     blocks = max(1, (max_kv_len + 63) // 64)
-    ctas = max(1, batch * num_kv_heads * head_chunks)
-    want = max(1, (3 * num_sms) // ctas)
-    return int(max(1, min(want, blocks, 64)))
+    ctas = max(1, batch * num_kv_heads * head_dim_chunks)
+    one_wave = max(1, (3 * num_sms) // ctas)
+    want = max(1, math.ceil(math.sqrt(8.0 * blocks)))
+    return int(max(1, min(want, one_wave, blocks, 64)))
+
+
+FUSED_COMBINE_MAX_SPLITS = 32   # up to here the last split CTA merges the partials itself; beyond, a combine launch
 
 
 def decode_workspace(batch: int, num_q_heads: int, head_dim: int, splits: int, device) -> torch.Tensor:
     return torch.empty(batch * num_q_heads * splits * (head_dim + 1), dtype=torch.float32, device=device)
+
+
+_COUNTERS = {}
+
+
+def _decode_counters(device, n: int) -> torch.Tensor:
+    """Zeroed arrival counters of the fused split-KV combine, one buffer per device (the kernel leaves them zero)."""
+    key = (device.type, device.index)
+    buf = _COUNTERS.get(key)
+    if buf is None or buf.numel() < n:
+        buf = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+        _COUNTERS[key] = buf
+    return buf
 
 
 def gqa_fwd_batch_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -117,8 +136,11 @@ def gqa_fwd_batch_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
             workspace = decode_workspace(B, Hq, D, splits, q.device)
         out = output_combine if output_combine is not None else torch.empty_like(q)
         lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if return_lse else None
+        # without the LSE the last split CTA of every (sequence, KV head) merges the partials: one launch
+        counters = None if (return_lse or splits > FUSED_COMBINE_MAX_SPLITS) else \
+            _decode_counters(q.device, B * Hkv * ((group + 15) // 16))
         lib.decode_attn(q.contiguous(), k_cache, v_cache, block_table, kv_lens, workspace, int(splits), float(scale),
-                        float(soft_cap), out, lse, None)
+                        float(soft_cap), out, lse, None, counters)
         return (out, lse) if return_lse else out
     cu = torch.arange(B + 1, dtype=torch.int32, device=q.device)
     res = attention_reference(q, k_cache, v_cache, block_table, cu, kv_lens, None, False, scale, soft_cap, return_lse)

@@ -67,7 +67,7 @@ class SpGQAFlashDecodeAttention:
         out = torch.empty_like(q)
         if self.num_ranks == 1:
             lib.decode_attn(q.contiguous(), k_cache, v_cache, block_table, local_lens, self.workspace, splits,
-                            float(self.scale), float(self.soft_cap), out, None, None)
+                            float(self.scale), float(self.soft_cap), out, None, None, None)
             return out
         lib.dist_decode_attn(self.rt.heap, q.contiguous(), k_cache, v_cache, block_table, local_lens, self.workspace,
                              splits, float(self.scale), float(self.soft_cap), out, self.staging, self.ctx_dev,

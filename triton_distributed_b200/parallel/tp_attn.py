@@ -88,11 +88,10 @@ class TP_Attn:
     def _attend(self, qkv: torch.Tensor, position_ids: torch.Tensor, kv_cache, layer_idx: int, bsz: int, q_len: int):
         """qkv [bsz*q_len, (Hq+2Hkv)*D] -> attention output [bsz*q_len, Hq*D]; writes K/V into the cache."""
         k_cache, v_cache = kv_cache.layer(layer_idx)
-        slots = kv_cache.slots_for(position_ids, bsz, q_len)
+        slots, kv_lens = kv_cache.step_values(position_ids, bsz, q_len)
         pos = position_ids.reshape(-1).to(torch.int64)
         q = ops.qk_norm_rope_kv(qkv, self.q_norm_w, self.k_norm_w, pos, slots, k_cache, v_cache, self.q_heads,
                                 self.kv_heads, self.head_dim, self.eps, self.rope_theta)
-        kv_lens = kv_cache.kv_lens_after(q_len, bsz)
         if q_len == 1:
             out = ops.gqa_fwd_batch_decode(q, k_cache, v_cache, kv_cache.decode_workspace(self.q_heads, self.head_dim),
                                            None, kv_lens, kv_cache.block_table, scale=self.scale,
