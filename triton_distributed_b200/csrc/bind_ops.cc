@@ -5,6 +5,7 @@
 
 #include "tdb/api.h"
 #include "tdb/coll.h"
+#include "tdb/gdn.h"
 #include "tdb/ops.h"
 #include "tdb/symm_heap.h"
 
@@ -223,6 +224,42 @@ void abs_sum(const at::Tensor& x, at::Tensor& out) {
   check_cuda(tdb::launch_abs_sum(x.data_ptr(), x.numel(), out.data_ptr<float>(), cur_stream()), "launch_abs_sum");
 }
 
+// Gated delta rule forward (variable length).  q, k [T, H, 128]; v [T, H, V]; g fp32 [T, H]; beta [T, H];
+// cu_seqlens int32 [N + 1] on the device.  Returns (o [T, H, V] bf16, final_state fp32 [N, H, K, V] or an empty tensor).
+std::tuple<at::Tensor, at::Tensor> gdn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& g,
+                                           const at::Tensor& beta, double scale, const c10::optional<at::Tensor>& h0,
+                                           bool output_final_state, const at::Tensor& cu_seqlens) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
+                  v.scalar_type() == at::kBFloat16 && beta.scalar_type() == at::kBFloat16 && g.scalar_type() == at::kFloat,
+              "gdn_fwd: q, k, v, beta bf16 and g fp32 expected");
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && g.is_contiguous() &&
+                  beta.is_contiguous(), "gdn_fwd: contiguous [T, H, *] tensors expected");
+  TORCH_CHECK(cu_seqlens.scalar_type() == at::kInt && cu_seqlens.is_cuda() && cu_seqlens.numel() >= 2, "gdn_fwd: cu_seqlens int32 on the device");
+  const int64_t T = q.size(0), H = q.size(1), K = q.size(2), V = v.size(2);
+  TORCH_CHECK(K == 128 && V % 32 == 0, "gdn_fwd: K = 128 and V a multiple of 32");
+  TORCH_CHECK(k.size(0) == T && v.size(0) == T && g.numel() == T * H && beta.numel() == T * H, "gdn_fwd: shape mismatch");
+  const int64_t N = cu_seqlens.numel() - 1;
+  c10::cuda::CUDAGuard guard(q.device());
+  at::Tensor o = at::empty({T, H, V}, q.options());
+  at::Tensor ht = output_final_state ? at::empty({N, H, K, V}, q.options().dtype(at::kFloat)) : at::empty({0}, q.options().dtype(at::kFloat));
+  tdb::GdnArgs a;
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
+  a.g = g.data_ptr<float>();
+  a.beta = beta.data_ptr();
+  a.o = o.data_ptr();
+  a.initial_state = nullptr;
+  if (h0.has_value()) {
+    TORCH_CHECK(h0->scalar_type() == at::kFloat && h0->is_contiguous() && h0->numel() == N * H * K * V, "gdn_fwd: initial_state fp32 [N, H, K, V]");
+    a.initial_state = h0->data_ptr<float>();
+  }
+  a.final_state = output_final_state ? ht.data_ptr<float>() : nullptr;
+  a.cu_seqlens = cu_seqlens.data_ptr<int32_t>();
+  a.num_seqs = N; a.H = H; a.K = K; a.V = V;
+  a.scale = static_cast<float>(scale);
+  if (T > 0) check_cuda(tdb::launch_gdn_fwd(a, cur_stream()), "launch_gdn_fwd");
+  return {o, ht};
+}
+
 }  // namespace
 
 
@@ -250,4 +287,5 @@ void bind_more(py::module_& m) {
   m.def("embedding", &embedding);
   m.def("argmax", &argmax);
   m.def("abs_sum", &abs_sum);
+  m.def("gdn_fwd", &gdn_fwd);
 }

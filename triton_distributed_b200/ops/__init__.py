@@ -27,3 +27,6 @@ from .moe import (topk_router, sort_topk_ids_align_block_size, calc_gather_scatt
 from .ep_a2a import (AllToAllContext, EpRecv, create_all_to_all_context, ep_dispatch, ep_combine, fast_all_to_all,  # noqa: F401
                      all_to_all_post_process, fp8_quant, fp8_dequant)
 from .all_to_all import (AllToAllSingle2DContext, create_all_to_all_single_2d_context, all_to_all_single_2d)  # noqa: F401
+
+from .gdn import (chunk_gated_delta_rule_fwd, gated_delta_rule_chunked, gated_delta_rule_recurrent,  # noqa: F401,E402
+                  prepare_chunk_indices, prepare_lens)
