@@ -1,0 +1,68 @@
+"""Tooling that needs no GPU: the contextual autotuner, the intra-kernel profiler's host side, topology probes and
+the roofline helpers."""
+import json
+import time
+
+import torch
+
+from triton_distributed_b200.tools import autotuner, profiler
+from triton_distributed_b200.utils import roofline, topology
+
+
+def test_contextual_autotune_picks_the_fastest_config_and_caches(tmp_path):
+    calls = []
+
+    @autotuner.contextual_autotune(configs=autotuner.config_space(delay_ms=[4, 0, 2]), key=lambda n: f"n={n}",
+                                   n_repeat=2, n_warmup=1, log_dir=str(tmp_path))
+    def work(n):
+        cfg = autotuner.current_config({"delay_ms": 0})
+        calls.append(cfg["delay_ms"])
+        time.sleep(cfg["delay_ms"] / 1e3)
+        return n * 2
+
+    assert work(21) == 42
+    tuned = len(calls)
+    assert tuned == 3 * 3 + 1 and calls[-1] == 0          # (warm-up + 2 repeats) per candidate, then the winner
+    assert work(21) == 42 and len(calls) == tuned + 1      # cached: one more call only
+    assert work(5) == 10 and len(calls) > tuned + 2        # another key tunes again
+    log = (tmp_path / "rank-0.log").read_text()
+    assert 'best {"delay_ms": 0}' in log
+    assert autotuner.current_config({"x": 1}) == {"x": 1}  # outside of a tuned call the default comes back
+
+
+def _record(block, group, task, start, sm, t_ns):
+    tag = (block << 16) | (group << 12) | (task << 1) | int(start)
+    return ((tag << 32) | (t_ns & 0xFFFFFFFF), (sm << 32) | (t_ns >> 32))
+
+
+def test_profiler_decode_trace_and_sm_activity(tmp_path):
+    buf = profiler.create_buffer(8, device="cpu")
+    recs = [_record(3, 1, 7, True, 12, 1000), _record(3, 1, 7, False, 12, 1600),
+            _record(4, 0, 9, True, 13, 1200), _record(4, 0, 9, False, 13, 2000)]
+    buf[0] = len(recs)
+    for i, (w0, w1) in enumerate(recs):
+        buf[2 + 2 * i] = w0 - (1 << 64) if w0 >= (1 << 63) else w0
+        buf[3 + 2 * i] = w1 - (1 << 64) if w1 >= (1 << 63) else w1
+    dec = profiler.decode(buf)
+    assert [(r["block"], r["group"], r["task"], r["start"], r["sm"], r["t_ns"]) for r in dec] == \
+        [(3, 1, 7, True, 12, 1000), (3, 1, 7, False, 12, 1600), (4, 0, 9, True, 13, 1200), (4, 0, 9, False, 13, 2000)]
+    trace = profiler.to_chrome_trace(dec, {7: "linear", 9: "attn"}, path=str(tmp_path / "t.json"))
+    names = sorted(e["name"] for e in trace["traceEvents"])
+    assert names == ["attn", "linear"] and json.load(open(tmp_path / "t.json"))["traceEvents"]
+    act = profiler.sm_activity(dec)
+    assert abs(act[12] - 0.6) < 1e-9 and abs(act[13] - 0.8) < 1e-9
+
+
+def test_topology_probes_answer_without_a_gpu():
+    d = topology.describe()
+    assert isinstance(d, dict) and d["gpus"] == topology.device_count()
+    assert topology.device_count() >= 0
+    assert isinstance(topology.has_fullmesh_nvlink(2), bool)
+
+
+def test_roofline_arithmetic():
+    peaks = {"hbm_gbs": 6500.0, "bf16_tflops": 1600.0, "source": "test"}
+    r = roofline.gemm_roofline(8192, 8192, 8192, 1.0, peaks=peaks)
+    assert abs(r["tflops"] - 2 * 8192 ** 3 / 1e9) < 1e-6 and 0 < r["frac_of_roofline"] < 1
+    f = roofline.fused_roofline(2 * 8192 * 8192 * 3584.0, 117e6, 0.5, peaks=peaks)
+    assert f["roofline_ms"] >= max(f["compute_ms"], f["link_ms"]) - 1e-9
