@@ -193,7 +193,7 @@ def check_gemv_ar(rt):
     for (N, K) in [(5120, 3200), (5120, 1024), (264, 520)]:
         for use_mc in ([True, False] if rt.has_multicast else [False]):
             ctx = ops.create_gemv_ar_context(N, use_multimem=use_mc)
-            for M in (1, 3, 8):
+            for M in (1, 3, 8, 16):
                 for it, mode in enumerate(("plain", "silu", "norm", "plain")):
                     torch.manual_seed(1000 * M + it)   # same residual stream on every rank
                     res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)

@@ -74,7 +74,7 @@ def test_skinny_gemm_split_k(shape):
         assert err < 2e-2, f"skinny {shape} splits={splits}: rel err {err}"
 
 
-@pytest.mark.parametrize("M", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 8, 12, 16])
 @pytest.mark.parametrize("mode", ["plain", "norm", "silu", "norm_residual"])
 def test_gemv_fused(M, mode):
     # decode GEMV with fused RMSNorm / SiLU*up prologue and residual epilogue against the fp32 reference

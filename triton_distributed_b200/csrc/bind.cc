@@ -340,7 +340,7 @@ void fill_gemv(tdb::GemvArgs& a, const at::Tensor& x, const at::Tensor& w, at::T
   const int64_t M = x.size(0), K = w.size(1), N = w.size(0);
   TORCH_CHECK(x.size(1) == (silu_mul ? 2 * K : K), "gemv: x has ", x.size(1), " columns, expected ", silu_mul ? 2 * K : K);
   TORCH_CHECK(out.size(0) == M && out.size(1) == N, "gemv: output shape mismatch");
-  TORCH_CHECK(M >= 1 && M <= 8, "gemv: 1 <= M <= 8");
+  TORCH_CHECK(M >= 1 && M <= 16, "gemv: 1 <= M <= 16");
   TORCH_CHECK(K <= tdb::gemv_max_k(M), "gemv: K too large for the shared-memory staging of ", M, " rows");
   std::memset(&a, 0, sizeof(a));
   a.M = M; a.N = N; a.K = K;

@@ -1,4 +1,4 @@
-// Decode GEMV for one to eight tokens:  out[M, N] = f(x)[M, K] * W[N, K]^T  (+ all-reduce) (+ residual).
+// Decode GEMV for one to sixteen tokens:  out[M, N] = f(x)[M, K] * W[N, K]^T  (+ all-reduce) (+ residual).
 //
 // With so few tokens a linear layer is a pure weight stream: the tensor cores have nothing to amortise and the cost
 // of a decode step is the HBM time of the weights plus whatever each launch adds around it.  This kernel therefore
@@ -89,19 +89,18 @@ TDB_DEVICE void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t
 // in flight (kJ per lane, double buffered).  Slices of K are summed through shared memory at the end.
 constexpr int kJ = 8;
 
-template <int MP>   // tokens rounded up to 1, 2, 4 or 8
+template <int MP>   // tokens rounded up to 1, 2, 4, 8 or 16 (two 8-token MMA tiles)
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams p) {
   extern __shared__ uint4 smem4[];
   __shared__ float s_part[kGemvWarps][MP];
-  __shared__ float s_rstd[8];
+  __shared__ float s_rstd[16];
+  constexpr int NT = (MP + 7) / 8;          // 8-token tiles of the MMA's N dimension
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const uint32_t epoch = (p.ctx != nullptr) ? ld_volatile(&p.ctx->epoch) : 1u;
-  const int par = epoch & 1;
   const int kv = p.K >> 3;                       // 16-byte vectors per row
   const int xs_stride = kv + 4;                  // in vectors: rows 64 bytes apart modulo 128 (bank-conflict free)
   uint4* xs = smem4;                             // staged activations f(x): [MP][xs_stride]
-  float* red = reinterpret_cast<float*>(smem4 + MP * xs_stride);   // [slots][64] partial accumulators
+  float* red = reinterpret_cast<float*>(smem4 + MP * xs_stride);   // [slots][8 rows][8 NT tokens] partial accumulators
   const int r0 = blockIdx.x * p.rows_per_cta;
   const int r1 = min(p.N, r0 + p.rows_per_cta);
   const int groups = (r1 - r0 + 7) >> 3;         // groups this CTA really has (the last CTA may have fewer)
@@ -131,41 +130,51 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
   if (active) issue(wa, grp, st0);
   pdl_wait();
   pdl_launch_dependents();
+  // the call epoch is advanced by the last CTA of the previous call: read it only after the dependency wait
+  const uint32_t epoch = (p.ctx != nullptr) ? ld_volatile(&p.ctx->epoch) : 1u;
+  const int par = epoch & 1;
 
-  // ---- prologue: stage f(x) in shared memory
+  // ---- prologue: stage f(x) in shared memory; a thread takes one 16-byte column slice of every token, so the loads
+  // of all tokens are in flight together and the staging time does not grow with the token count
   float ss[MP];
 #pragma unroll
   for (int m = 0; m < MP; ++m) ss[m] = 0.f;
+  constexpr int MB = MP < 4 ? MP : 4;      // tokens whose loads are in flight together (register budget)
+  for (int c = tid; c < kv; c += kGemvThreads) {
+    float gn[8];
+    if (p.norm_w != nullptr) unpack8(ld_nc_v4(p.norm_w + c * 8), gn);
 #pragma unroll
-  for (int m = 0; m < MP; ++m) {
-    if (m >= p.M) {
-      for (int c = tid; c < kv; c += kGemvThreads) xs[m * xs_stride + c] = make_uint4(0u, 0u, 0u, 0u);
-      continue;
-    }
-    const __nv_bfloat16* xr = p.x + static_cast<int64_t>(m) * p.ldx;
-    for (int c = tid; c < kv; c += kGemvThreads) {
-      uint4 v = ld_v4(xr + c * 8);
-      if (p.silu_mul) {
-        const uint4 u = ld_v4(xr + p.K + c * 8);
-        float gg[8], h[8];
-        unpack8(v, gg);
-        unpack8(u, h);
+    for (int m0 = 0; m0 < MP; m0 += MB) {
+      uint4 v[MB], u[MB];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) gg[j] = gg[j] / (1.f + __expf(-gg[j])) * h[j];
-        v = pack8(gg);
-      } else if (p.norm_w != nullptr) {
-        const uint4 gw = ld_nc_v4(p.norm_w + c * 8);
-        float a[8], gn[8];
-        unpack8(v, a);
-        unpack8(gw, gn);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          ss[m] += a[j] * a[j];
-          a[j] *= gn[j];
-        }
-        v = pack8(a);
+      for (int i = 0; i < MB; ++i) {
+        const int m = m0 + i;
+        v[i] = (m < p.M) ? ld_v4(p.x + static_cast<int64_t>(m) * p.ldx + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+        if (p.silu_mul)
+          u[i] = (m < p.M) ? ld_v4(p.x + static_cast<int64_t>(m) * p.ldx + p.K + c * 8) : make_uint4(0u, 0u, 0u, 0u);
       }
-      xs[m * xs_stride + c] = v;
+#pragma unroll
+      for (int i = 0; i < MB; ++i) {
+        const int m = m0 + i;
+        if (p.silu_mul) {
+          float gg[8], h[8];
+          unpack8(v[i], gg);
+          unpack8(u[i], h);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) gg[j] = gg[j] / (1.f + __expf(-gg[j])) * h[j];
+          v[i] = pack8(gg);
+        } else if (p.norm_w != nullptr) {
+          float a[8];
+          unpack8(v[i], a);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            ss[m] += a[j] * a[j];
+            a[j] *= gn[j];
+          }
+          v[i] = pack8(a);
+        }
+        xs[m * xs_stride + c] = v[i];
+      }
     }
   }
   if (p.norm_w != nullptr) {
@@ -180,27 +189,32 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
       for (int wi = 0; wi < kGemvWarps; ++wi) tt += s_part[wi][tid];
       s_rstd[tid] = rsqrtf(tt / static_cast<float>(p.K) + p.eps);
     }
-  } else if (tid < 8) {
+  } else if (tid < 16) {
     s_rstd[tid] = 1.f;
   }
   __syncthreads();
 
   // ---- main loop
-  const uint4* xrow = xs + (g < MP ? g : 0) * xs_stride;
-  const bool tok_ok = g < MP;
-  auto consume = [&](const uint4 (&src)[kJ], int step, float (&c)[4]) {
+  auto consume = [&](const uint4 (&src)[kJ], int step, float (&c)[NT][4]) {
 #pragma unroll
     for (int j = 0; j < kJ; ++j) {
       const int cv = (step + j) * 4 + t;
-      uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-      if (tok_ok && step + j < st1 && cv < kv) xv = xrow[cv];
-      mma_bf16_16816(c, src[j].x, 0u, src[j].y, 0u, xv.x, xv.y);
-      mma_bf16_16816(c, src[j].z, 0u, src[j].w, 0u, xv.z, xv.w);
+      const bool in_range = step + j < st1 && cv < kv;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int tok = nt * 8 + g;               // token whose activations this lane feeds as the B fragment
+        uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+        if (tok < MP && in_range) xv = xs[tok * xs_stride + cv];
+        mma_bf16_16816(c[nt], src[j].x, 0u, src[j].y, 0u, xv.x, xv.y);
+        mma_bf16_16816(c[nt], src[j].z, 0u, src[j].w, 0u, xv.z, xv.w);
+      }
     }
   };
   if (active) {
     for (; grp < groups; grp += kGemvWarps) {
-      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      float c[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
       int st = st0;
       while (st < st1) {
         // wa holds steps [st, st + kJ); fetch the next batch into wb before consuming wa, and vice versa
@@ -214,8 +228,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
       }
       // accumulator: c[0], c[1] = (row g, tokens 2t, 2t + 1); rows 8..15 of the tile are the zero half
       const int slot = grp * slices + slice;
-      red[slot * 64 + g * 8 + 2 * t] = c[0];
-      red[slot * 64 + g * 8 + 2 * t + 1] = c[1];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        red[(slot * 8 + g) * (8 * NT) + nt * 8 + 2 * t] = c[nt][0];
+        red[(slot * 8 + g) * (8 * NT) + nt * 8 + 2 * t + 1] = c[nt][1];
+      }
       const int nxt = grp + kGemvWarps;
       if (slices == 1 && nxt < groups) issue(wa, nxt, st0);
       if (slices != 1) break;
@@ -233,7 +250,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const GemvParams 
     if (row >= r1) continue;
     const int gi = rr >> 3, gr = rr & 7;
     float v = 0.f;
-    for (int sl = 0; sl < slices; ++sl) v += red[(gi * slices + sl) * 64 + gr * 8 + m];
+    for (int sl = 0; sl < slices; ++sl) v += red[((gi * slices + sl) * 8 + gr) * (8 * NT) + m];
     v *= s_rstd[m];
     if (p.all_reduce) {
       pdst[static_cast<int64_t>(m) * p.N + row] = __float2bfloat16(v);
@@ -326,13 +343,13 @@ cudaError_t launch_t(const GemvParams& p, int grid, size_t smem, cudaStream_t st
 }  // namespace
 
 int gemv_max_k(int M) {
-  const int mp = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
+  const int mp = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16;
   // mp rows of (2 K + 64) bytes next to the partial-sum slots
   return (((kMaxSmem - kRedBytes) / mp - 64) / 2) & ~7;
 }
 
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
-  if (a.M < 1 || a.M > 8 || a.K % 8 != 0 || a.K > gemv_max_k(a.M)) return cudaErrorInvalidValue;
+  if (a.M < 1 || a.M > 16 || a.K % 8 != 0 || a.K > gemv_max_k(a.M)) return cudaErrorInvalidValue;
   if (a.ldw % 8 != 0 || a.ldx % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a.w) | reinterpret_cast<uintptr_t>(a.x)) & 15u) return cudaErrorInvalidValue;
   if (a.norm_w != nullptr && a.silu_mul) return cudaErrorInvalidValue;
@@ -370,16 +387,17 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t stream) {
   p.rows_per_cta = rows;
   const int grid = (a.N + rows - 1) / rows;
   if (a.all_reduce && grid > a.max_ctas) return cudaErrorInvalidValue;
-  const int mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
+  const int mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : a.M <= 8 ? 8 : 16;
   const int groups = rows / 8;
   const int slots = groups >= kGemvWarps ? groups : groups * (kGemvWarps / groups);
-  const size_t smem = static_cast<size_t>(mp) * (a.K * 2 + 64) + static_cast<size_t>(slots) * 256;
+  const size_t smem = static_cast<size_t>(mp) * (a.K * 2 + 64) + static_cast<size_t>(slots) * 256 * ((mp + 7) / 8);
   if (smem > static_cast<size_t>(kMaxSmem)) return cudaErrorInvalidValue;
   switch (mp) {
     case 1: return launch_t<1>(p, grid, smem, stream);
     case 2: return launch_t<2>(p, grid, smem, stream);
     case 4: return launch_t<4>(p, grid, smem, stream);
-    default: return launch_t<8>(p, grid, smem, stream);
+    case 8: return launch_t<8>(p, grid, smem, stream);
+    default: return launch_t<16>(p, grid, smem, stream);
   }
 }
 

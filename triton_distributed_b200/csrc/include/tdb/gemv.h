@@ -1,4 +1,4 @@
-// Host API of the decode GEMV (gemv.cu): out[M, N] = f(x)[M, K] * W[N, K]^T for M <= 8 tokens, with the element-wise
+// Host API of the decode GEMV (gemv.cu): out[M, N] = f(x)[M, K] * W[N, K]^T for M <= 16 tokens, with the element-wise
 // neighbours of a transformer layer and the tensor-parallel all-reduce folded into the same launch.
 #pragma once
 #include "api.h"

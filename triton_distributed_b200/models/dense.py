@@ -170,7 +170,7 @@ class DenseLLM:
         a = self.arch
         return (self.mode in ("triton_dist_gemm_ar", "gemm_ar") and S == 1 and getattr(self, "gemv_ctx", None) is not None
                 and self.embed_tokens.is_cuda and self.embed_tokens.dtype == torch.bfloat16
-                and ops.gemv_supported(B, a.hidden_size)
+                and B <= ops.GEMV_FAST_M and ops.gemv_supported(B, a.hidden_size)
                 and ops.gemv_supported(B, a.intermediate_size // self.world_size)
                 and ops.gemv_supported(B, a.num_attention_heads * a.head_dim // self.world_size))
 

@@ -17,7 +17,7 @@ from .attention import (flash_attn_varlen, gqa_fwd_batch_decode, gqa_fwd_batch_d
                         gqa_fwd_batch_decode_persistent, attention_reference, merge_attention_partials,
                         dense_block_table, decode_workspace, pick_kv_splits)
 from .gemv import (GemvARContext, create_gemv_ar_context, gemv_fused, gemv_reference, gemv_supported,  # noqa: F401
-                   GEMV_MAX_M)
+                   GEMV_FAST_M, GEMV_MAX_M)
 from .gemm_ar import (GemmARContext, LLGemmARContext, create_gemm_ar_context, create_ll_gemm_ar_context,  # noqa: F401
                       gemm_allreduce_op, low_latency_gemm_allreduce_op, skinny_gemm, gemm_ar_reference)
 from .moe import (topk_router, sort_topk_ids_align_block_size, calc_gather_scatter_index, group_gemm_sorted,  # noqa: F401

@@ -1,4 +1,4 @@
-"""Decode GEMV with its layer neighbours fused in (``gemv_fused``): for up to eight tokens
+"""Decode GEMV with its layer neighbours fused in (``gemv_fused``): for up to sixteen tokens
 
     out = [residual +] [all_reduce(] f(x) @ w^T [)],   f = identity | RMSNorm(x) * norm_weight | SiLU(gate) * up
 
@@ -19,7 +19,8 @@ from .. import _native
 from ..runtime import Runtime, get_runtime
 from .common import new_ctx_dev, sm_count
 
-GEMV_MAX_M = 8
+GEMV_MAX_M = 16    # what the kernel accepts
+GEMV_FAST_M = 8    # up to here it beats the tcgen05 weight-streaming kernel (two MMA tiles of tokens are mma.sync-bound)
 
 
 @dataclass
@@ -86,14 +87,14 @@ def gemv_supported(M: int, K: int) -> bool:
     """Whether ``M`` tokens with ``K`` input features fit the GEMV kernel (token count and shared-memory staging)."""
     if M < 1 or M > GEMV_MAX_M or K % 8 != 0:
         return False
-    mp = 1 if M <= 1 else 2 if M <= 2 else 4 if M <= 4 else 8
+    mp = 1 if M <= 1 else 2 if M <= 2 else 4 if M <= 4 else 8 if M <= 8 else 16
     return K <= (((200 - 8) * 1024 // mp - 64) // 2) // 8 * 8
 
 
 def gemv_fused(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
                norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6, silu_mul: bool = False,
                residual: Optional[torch.Tensor] = None, ar_ctx: Optional[GemvARContext] = None) -> torch.Tensor:
-    """``x`` [M<=8, K] (or [M, 2K] with ``silu_mul``), ``w`` [N, K] -> [M, N].  ``residual`` may be ``out`` itself.
+    """``x`` [M<=16, K] (or [M, 2K] with ``silu_mul``), ``w`` [N, K] -> [M, N].  ``residual`` may be ``out`` itself.
     With ``ar_ctx`` of a multi-rank runtime the per-rank results are summed over the ranks before the residual."""
     M = x.shape[0]
     N, K = w.shape
