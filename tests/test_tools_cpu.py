@@ -66,3 +66,12 @@ def test_roofline_arithmetic():
     assert abs(r["tflops"] - 2 * 8192 ** 3 / 1e9) < 1e-6 and 0 < r["frac_of_roofline"] < 1
     f = roofline.fused_roofline(2 * 8192 * 8192 * 3584.0, 117e6, 0.5, peaks=peaks)
     assert f["roofline_ms"] >= max(f["compute_ms"], f["link_ms"]) - 1e-9
+
+
+def test_speed_of_light_models():
+    assert roofline.get_tensorcore_tflops("fp8", measured=False) == 2 * roofline.get_tensorcore_tflops("bf16", measured=False)
+    t = roofline.estimate_gemm_sol_time_ms(8192, 8192, 8192)
+    assert 0.3 < t < 1.5                                     # 1.1 PFLOP at roughly 1.6 PFLOP/s
+    ag = roofline.estimate_all_gather_time_ms(8192 * 8192 * 2, 8)
+    rs = roofline.estimate_reduce_scatter_time_ms(8192 * 8192 * 2, 8)
+    assert abs(ag - rs) < 1e-9 and 0.1 < ag < 0.3            # 117 MB over about 770 GB/s

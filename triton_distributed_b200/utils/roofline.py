@@ -52,3 +52,44 @@ def fused_roofline(flops_per_rank: float, nvlink_bytes_per_rank: float, ms: floa
     return {"compute_ms": t_compute * 1e3, "link_ms": t_link * 1e3, "roofline_ms": t_roof * 1e3,
             "frac_of_roofline": t_roof * 1e3 / ms, "tflops_per_rank": flops_per_rank / (ms * 1e-3) / 1e12,
             "peaks": peaks["source"]}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Speed-of-light estimates with the reference's function names (gemm_perf_model.py:198-236, comm_perf_model.py:94-116),
+# for a B200 inside one NVSwitch domain.  Dense nominal tensor peaks; measured values where this pool has them.
+# ---------------------------------------------------------------------------------------------------------------------
+NOMINAL_TFLOPS = {"bf16": 2250.0, "fp16": 2250.0, "fp8": 4500.0, "fp4": 9000.0, "tf32": 1100.0}
+
+
+def get_tensorcore_tflops(dtype="bf16", measured: bool = True) -> float:
+    """Dense tensor-core rate of one B200: the measured cuBLAS bf16 burst rate (scaled by the nominal ratio for other
+    types) or the nominal figure."""
+    name = str(dtype).replace("torch.", "")
+    name = {"bfloat16": "bf16", "float16": "fp16", "float8_e4m3fn": "fp8", "float8_e5m2": "fp8", "float32": "tf32"}.get(name, name)
+    nominal = NOMINAL_TFLOPS[name]
+    if not measured:
+        return nominal
+    return load_peaks()["bf16_tflops"] * nominal / NOMINAL_TFLOPS["bf16"]
+
+
+def get_dram_gbps(measured: bool = True) -> float:
+    return load_peaks()["hbm_gbs"] if measured else 7700.0
+
+
+def estimate_gemm_sol_time_ms(M: int, N: int, K: int, dtype="bf16", elem_bytes: int = 2) -> float:
+    """max(compute at the tensor peak, operands + result once over HBM)."""
+    t_c = 2.0 * M * N * K / (get_tensorcore_tflops(dtype) * 1e12)
+    t_m = (M * K + N * K + M * N) * elem_bytes / (get_dram_gbps() * 1e9)
+    return max(t_c, t_m) * 1e3
+
+
+def estimate_all_gather_time_ms(nbytes: int, world_size: int, local_world_size: Optional[int] = None,
+                                intranode_bw: float = NVLINK_GBS_MEASURED, internode_bw: Optional[float] = None) -> float:
+    """Every rank receives (W - 1) / W of ``nbytes`` (the gathered size) through its own NVLink ingress."""
+    return nbytes * (world_size - 1) / world_size / (intranode_bw * 1e9) * 1e3
+
+
+def estimate_reduce_scatter_time_ms(nbytes: int, world_size: int, local_world_size: Optional[int] = None,
+                                    intranode_bw: float = NVLINK_GBS_MEASURED, internode_bw: Optional[float] = None) -> float:
+    """Every rank sends (W - 1) / W of its ``nbytes`` partial result."""
+    return nbytes * (world_size - 1) / world_size / (intranode_bw * 1e9) * 1e3
