@@ -895,28 +895,42 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[b]), 0));
           }
           if (own_seg && row_ok) {
-            const int col0 = tl.n0 + c * kEpiCols;
-            for (int s = 0; s < p.symm.world; ++s) {
-              if (s == p.symm.rank) continue;
-              const __nv_bfloat16* src = p.rs_slots + (static_cast<uint64_t>(buf) * p.symm.world + s) * p.rs_slot_elems +
-                                         static_cast<uint64_t>(seg_row) * p.N + col0;
-              uint4 u[8];
+            // 32 columns at a time: the 64-byte pieces of ALL other ranks' partials are requested together (one
+            // round trip per half chunk instead of one per source), then added to the accumulators
+            const int W = p.symm.world;
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                u[j] = (col0 + 8 * j + 8 <= p.N) ? ld_relaxed_sys_v4(src + 8 * j) : make_uint4(0u, 0u, 0u, 0u);
+            for (int half = 0; half < 2; ++half) {
+              const int col0 = tl.n0 + c * kEpiCols + half * 32;
+              uint4 u[kMaxRanks - 1][4];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                uint32_t* r = (j < 4) ? &r0[8 * j] : &r1[8 * (j - 4)];
-                const float2 f0 = unpack_bf16x2(u[j].x), f1 = unpack_bf16x2(u[j].y), f2 = unpack_bf16x2(u[j].z),
-                             f3 = unpack_bf16x2(u[j].w);
-                r[0] = __float_as_uint(__uint_as_float(r[0]) + f0.x);
-                r[1] = __float_as_uint(__uint_as_float(r[1]) + f0.y);
-                r[2] = __float_as_uint(__uint_as_float(r[2]) + f1.x);
-                r[3] = __float_as_uint(__uint_as_float(r[3]) + f1.y);
-                r[4] = __float_as_uint(__uint_as_float(r[4]) + f2.x);
-                r[5] = __float_as_uint(__uint_as_float(r[5]) + f2.y);
-                r[6] = __float_as_uint(__uint_as_float(r[6]) + f3.x);
-                r[7] = __float_as_uint(__uint_as_float(r[7]) + f3.y);
+              for (int i = 0; i < kMaxRanks - 1; ++i) {
+                if (i < W - 1) {
+                  const int src_rank = (p.symm.rank + 1 + i) % W;
+                  const __nv_bfloat16* src = p.rs_slots + (static_cast<uint64_t>(buf) * W + src_rank) * p.rs_slot_elems +
+                                             static_cast<uint64_t>(seg_row) * p.N + col0;
+#pragma unroll
+                  for (int j = 0; j < 4; ++j)
+                    u[i][j] = (col0 + 8 * j + 8 <= p.N) ? ld_relaxed_sys_v4(src + 8 * j) : make_uint4(0u, 0u, 0u, 0u);
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < kMaxRanks - 1; ++i) {
+                if (i < W - 1) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    uint32_t* r = half ? &r1[8 * j] : &r0[8 * j];
+                    const float2 f0 = unpack_bf16x2(u[i][j].x), f1 = unpack_bf16x2(u[i][j].y),
+                                 f2 = unpack_bf16x2(u[i][j].z), f3 = unpack_bf16x2(u[i][j].w);
+                    r[0] = __float_as_uint(__uint_as_float(r[0]) + f0.x);
+                    r[1] = __float_as_uint(__uint_as_float(r[1]) + f0.y);
+                    r[2] = __float_as_uint(__uint_as_float(r[2]) + f1.x);
+                    r[3] = __float_as_uint(__uint_as_float(r[3]) + f1.y);
+                    r[4] = __float_as_uint(__uint_as_float(r[4]) + f2.x);
+                    r[5] = __float_as_uint(__uint_as_float(r[5]) + f2.y);
+                    r[6] = __float_as_uint(__uint_as_float(r[6]) + f3.x);
+                    r[7] = __float_as_uint(__uint_as_float(r[7]) + f3.y);
+                  }
+                }
               }
             }
           }
