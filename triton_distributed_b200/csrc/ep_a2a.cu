@@ -38,14 +38,24 @@ TDB_DEVICE float fp8_to_float(uint32_t byte) {
 // One warp quantises one bf16 row of H elements (H % 128 == 0) into fp8 + H/128 scales and writes both.
 TDB_DEVICE void warp_quant_row(const __nv_bfloat16* src, uint8_t* dst_q, float* dst_s, int H) {
   const int lane = lane_id();
-  for (int b = 0; b < H / kQuantBlock; ++b) {
-    const uint2 u = *reinterpret_cast<const uint2*>(src + b * kQuantBlock + lane * 4);
-    const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y);
-    float amax = fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y)));
-    amax = fmaxf(warp_max(amax), 1e-10f);
-    const float scale = amax / 448.f;
-    reinterpret_cast<uint32_t*>(dst_q + b * kQuantBlock)[lane] = quant4(f0.x, f0.y, f1.x, f1.y, 1.f / scale);
-    if (lane == 0) dst_s[b] = scale;
+  const int nb = H / kQuantBlock;
+  // eight 128-value blocks per step: their loads are in flight together (a block per iteration would pay one memory
+  // round trip per block, 56 in a row for a 7168-wide token)
+  for (int b0 = 0; b0 < nb; b0 += 8) {
+    uint2 u[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      u[j] = (b0 + j < nb) ? *reinterpret_cast<const uint2*>(src + (b0 + j) * kQuantBlock + lane * 4) : make_uint2(0u, 0u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (b0 + j >= nb) break;
+      const float2 f0 = unpack_bf16x2(u[j].x), f1 = unpack_bf16x2(u[j].y);
+      float amax = fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y)));
+      amax = fmaxf(warp_max(amax), 1e-10f);
+      const float scale = amax / 448.f;
+      reinterpret_cast<uint32_t*>(dst_q + (b0 + j) * kQuantBlock)[lane] = quant4(f0.x, f0.y, f1.x, f1.y, 1.f / scale);
+      if (lane == 0) dst_s[b0 + j] = scale;
+    }
   }
 }
 
@@ -202,28 +212,30 @@ __global__ void ep_gather_rows_kernel(const uint8_t* __restrict__ recv_x_base, c
   const int par = last_parity(dctx);
   const uint8_t* recv_x = recv_x_base + par * rows_per_parity * (quant ? H : 2 * H);
   const float* recv_scale = recv_scale_base + par * rows_per_parity * (H / kQuantBlock);
-  const int64_t r = blockIdx.x;
-  if (r >= meta[0]) return;
-  const int id = sorted_ids[r];
-  __nv_bfloat16* dst = out + r * H;
-  if (id < 0) {
-    for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = make_uint4(0, 0, 0, 0);
-    return;
-  }
-  if (!quant) {
-    const uint4* s = reinterpret_cast<const uint4*>(recv_x + static_cast<int64_t>(id) * H * 2);
-    for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = s[i];
-    return;
-  }
-  const uint8_t* q = recv_x + static_cast<int64_t>(id) * H;
-  const float* sc = recv_scale + static_cast<int64_t>(id) * (H / kQuantBlock);
-  for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
-    const uint32_t w = reinterpret_cast<const uint32_t*>(q)[i];
-    const float s = sc[(i * 4) / kQuantBlock];
-    uint2 o;
-    o.x = pack_bf16x2(fp8_to_float(w & 0xff) * s, fp8_to_float((w >> 8) & 0xff) * s);
-    o.y = pack_bf16x2(fp8_to_float((w >> 16) & 0xff) * s, fp8_to_float(w >> 24) * s);
-    reinterpret_cast<uint2*>(dst)[i] = o;
+  // the grid is sized for the machine, not for the row capacity: most of the capacity is unused in a decode step
+  const int64_t total = meta[0];
+  for (int64_t r = blockIdx.x; r < total; r += gridDim.x) {
+    const int id = sorted_ids[r];
+    __nv_bfloat16* dst = out + r * H;
+    if (id < 0) {
+      for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    if (!quant) {
+      const uint4* s = reinterpret_cast<const uint4*>(recv_x + static_cast<int64_t>(id) * H * 2);
+      for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = s[i];
+      continue;
+    }
+    const uint8_t* q = recv_x + static_cast<int64_t>(id) * H;
+    const float* sc = recv_scale + static_cast<int64_t>(id) * (H / kQuantBlock);
+    for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
+      const uint32_t w = reinterpret_cast<const uint32_t*>(q)[i];
+      const float s = sc[(i * 4) / kQuantBlock];
+      uint2 o;
+      o.x = pack_bf16x2(fp8_to_float(w & 0xff) * s, fp8_to_float((w >> 8) & 0xff) * s);
+      o.y = pack_bf16x2(fp8_to_float((w >> 16) & 0xff) * s, fp8_to_float(w >> 24) * s);
+      reinterpret_cast<uint2*>(dst)[i] = o;
+    }
   }
 }
 
@@ -258,27 +270,52 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const CombinePar
   const int warps = kEpThreads / 32, lane = threadIdx.x & 31;
   __nv_bfloat16* ret = p.ret + par * p.ret_half;
   const int32_t* recv_meta = p.recv_meta + last_parity(p.dctx) * p.recv_rows;
-  // ---- send: one warp per receive row
+  // ---- send.  Receive rows that carry a token are sparse and clustered (the first few slots of every
+  // (expert, source) block), so a fixed row-to-warp mapping leaves most warps idle.  Warps instead pull chunks of 32
+  // consecutive rows from a shared counter, look at the 32 `pos_of` entries with one coalesced load, and copy the
+  // rows that are there one after the other with several 16-byte loads in flight.
   const int blocks = p.epr * W;
-  for (int64_t r = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); r < p.recv_rows;
-       r += static_cast<int64_t>(gridDim.x) * warps) {
-    const int pos = p.pos_of[r];
-    if (pos < 0) continue;
-    int src;
-    if (p.base_self == nullptr) {
-      src = static_cast<int>((r / p.max_tokens) % W);
-    } else {
-      int lo = 0, hi = blocks - 1;
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (p.base_self[mid] <= r) lo = mid; else hi = mid - 1;
+  uint32_t* work = &p.ctx->pad[0];
+  const int nvec = p.H >> 3;
+  while (true) {
+    uint32_t chunk = 0;
+    if (lane == 0) chunk = atomicAdd(work, 1u);
+    chunk = __shfl_sync(0xffffffffu, chunk, 0);
+    const int64_t r_base = static_cast<int64_t>(chunk) * 32;
+    if (r_base >= p.recv_rows) break;
+    const int64_t r_mine = r_base + lane;
+    const int pos_mine = r_mine < p.recv_rows ? p.pos_of[r_mine] : -1;
+    const int pair_mine = pos_mine >= 0 ? recv_meta[r_mine] : 0;
+    uint32_t valid = __ballot_sync(0xffffffffu, pos_mine >= 0);
+    while (valid) {
+      const int l = __ffs(valid) - 1;
+      valid &= valid - 1;
+      const int pos = __shfl_sync(0xffffffffu, pos_mine, l);
+      const int pair = __shfl_sync(0xffffffffu, pair_mine, l);
+      const int64_t r = r_base + l;
+      int src;
+      if (p.base_self == nullptr) {
+        src = static_cast<int>((r / p.max_tokens) % W);
+      } else {
+        int lo = 0, hi = blocks - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (p.base_self[mid] <= r) lo = mid; else hi = mid - 1;
+        }
+        src = lo % W;
       }
-      src = lo % W;
+      const uint4* sp = reinterpret_cast<const uint4*>(p.y + static_cast<int64_t>(pos) * p.H);
+      uint4* d = reinterpret_cast<uint4*>(symm_at(p.symm, ret + static_cast<int64_t>(pair) * p.H, src));
+      int i = lane;
+      for (; i + 96 < nvec; i += 128) {
+        const uint4 v0 = sp[i], v1 = sp[i + 32], v2 = sp[i + 64], v3 = sp[i + 96];
+        st_v4(d + i, v0);
+        st_v4(d + i + 32, v1);
+        st_v4(d + i + 64, v2);
+        st_v4(d + i + 96, v3);
+      }
+      for (; i < nvec; i += 32) st_v4(d + i, sp[i]);
     }
-    const int pair = recv_meta[r];
-    const uint4* s = reinterpret_cast<const uint4*>(p.y + static_cast<int64_t>(pos) * p.H);
-    uint4* d = reinterpret_cast<uint4*>(symm_at(p.symm, ret + static_cast<int64_t>(pair) * p.H, src));
-    for (int i = lane; i < (p.H >> 3); i += 32) st_v4(d + i, s[i]);
   }
   __shared__ int s_last;
   __shared__ int s_ok;
@@ -301,22 +338,42 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const CombinePar
   }
   __syncthreads();
   if (s_ok) {
+    // weighted sum of the k returned rows of every token: the (up to eight) row loads of a step are issued together
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
-      for (int i = threadIdx.x; i < (p.H >> 3); i += kEpThreads) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < p.k; ++j) {
-          const int e = p.topk_ids[t * p.k + j];
-          if (e < 0 || e >= p.E) continue;
-          const float wj = p.topk_w ? p.topk_w[t * p.k + j] : 1.f;
-          const uint4 u = ld_relaxed_sys_v4(ret + (static_cast<int64_t>(t) * p.k + j) * p.H + i * 8);
-          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
-          acc[0] += wj * f0.x; acc[1] += wj * f0.y; acc[2] += wj * f1.x; acc[3] += wj * f1.y;
-          acc[4] += wj * f2.x; acc[5] += wj * f2.y; acc[6] += wj * f3.x; acc[7] += wj * f3.y;
+      for (int j0 = 0; j0 < p.k; j0 += 8) {
+        float wj[8];
+        bool okj[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int jj = j0 + j;
+          const int e = jj < p.k ? p.topk_ids[t * p.k + jj] : -1;
+          okj[j] = e >= 0 && e < p.E;
+          wj[j] = okj[j] ? (p.topk_w ? p.topk_w[t * p.k + jj] : 1.f) : 0.f;
         }
-        uint4 o;
-        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-        reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(t) * p.H)[i] = o;
+        for (int i = threadIdx.x; i < (p.H >> 3); i += kEpThreads) {
+          uint4 u[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            u[j] = okj[j] ? ld_relaxed_sys_v4(ret + (static_cast<int64_t>(t) * p.k + j0 + j) * p.H + i * 8)
+                          : make_uint4(0u, 0u, 0u, 0u);
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          uint4* optr = reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(t) * p.H) + i;
+          if (j0 > 0) {
+            const uint4 prev = *optr;   // more than eight slots: continue from the partial sum of the earlier ones
+            const float2 f0 = unpack_bf16x2(prev.x), f1 = unpack_bf16x2(prev.y), f2 = unpack_bf16x2(prev.z), f3 = unpack_bf16x2(prev.w);
+            acc[0] = f0.x; acc[1] = f0.y; acc[2] = f1.x; acc[3] = f1.y; acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float2 f0 = unpack_bf16x2(u[j].x), f1 = unpack_bf16x2(u[j].y), f2 = unpack_bf16x2(u[j].z), f3 = unpack_bf16x2(u[j].w);
+            acc[0] += wj[j] * f0.x; acc[1] += wj[j] * f0.y; acc[2] += wj[j] * f1.x; acc[3] += wj[j] * f1.y;
+            acc[4] += wj[j] * f2.x; acc[5] += wj[j] * f2.y; acc[6] += wj[j] * f3.x; acc[7] += wj[j] * f3.y;
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+          *optr = o;
+        }
       }
     }
   }
@@ -328,6 +385,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const CombinePar
     if (prev == gridDim.x - 1) {
       p.ctx->done = 0;
       p.ctx->grid_bar = 0;
+      p.ctx->pad[0] = 0;   // work counter of the send phase
       __threadfence();
       *reinterpret_cast<volatile uint32_t*>(&p.ctx->epoch) = epoch + 1;
     }
@@ -478,7 +536,8 @@ cudaError_t launch_ep_gather_rows(const void* recv_x, const float* recv_scale, c
                                   void* out, int64_t rows_cap, int H, int quant, int64_t rows_per_parity,
                                   const CtxDev* dispatch_ctx, cudaStream_t s) {
   if (rows_cap == 0) return cudaSuccess;
-  ep_gather_rows_kernel<<<static_cast<unsigned>(rows_cap), 128, 0, s>>>(reinterpret_cast<const uint8_t*>(recv_x), recv_scale,
+  const unsigned grid = static_cast<unsigned>(rows_cap < 148 * 16 ? rows_cap : 148 * 16);
+  ep_gather_rows_kernel<<<grid, 128, 0, s>>>(reinterpret_cast<const uint8_t*>(recv_x), recv_scale,
                                                                        sorted_ids, meta, reinterpret_cast<__nv_bfloat16*>(out),
                                                                        H, quant, rows_per_parity, dispatch_ctx);
   return cudaGetLastError();
@@ -505,7 +564,7 @@ cudaError_t launch_ep_combine(const EpCombineArgs& a, cudaStream_t s) {
   p.ctx = a.ctx;
   p.symm = to_dev(a.symm);
   int ctas = a.num_ctas > 0 ? a.num_ctas : 64;
-  if (ctas > 128) ctas = 128;   // every CTA waits on remote flags: the grid must be resident
+  if (ctas > 592) ctas = 592;   // every CTA waits on remote flags: the grid must be resident (4 x 148 CTAs of 256 threads are)
   ep_combine_kernel<<<ctas, kEpThreads, 0, s>>>(p);
   return cudaGetLastError();
 }

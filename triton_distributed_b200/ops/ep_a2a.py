@@ -164,6 +164,12 @@ def _cpu_combine(ctx: AllToAllContext, y_sorted, recv: EpRecv, topk_w):
     return out.to(y_sorted.dtype)
 
 
+def _ctas_for_rows(rows: int) -> int:
+    """One warp moves one row at a time and a row is a handful of memory round trips, so the kernels are latency-bound
+    until many warps work: 64 CTAs (512 warps) for a decode step, up to four per SM for prefill-sized batches."""
+    return int(min(592, max(64, rows // 16)))
+
+
 # ------------------------------------------------------------------ public ops
 def ep_dispatch(ctx: AllToAllContext, x: torch.Tensor, topk_ids: torch.Tensor) -> EpRecv:
     """Send every (token, slot) to the rank owning its expert; returns the local expert-sorted receive view."""
@@ -181,8 +187,8 @@ def ep_dispatch(ctx: AllToAllContext, x: torch.Tensor, topk_ids: torch.Tensor) -
         base = ctx.base
         base_self = ctx.base[ctx.rank].reshape(-1)
     lib.ep_dispatch(rt.heap, x.contiguous(), ids, E, ctx.quant, ctx.max_m, ctx.recv_x, ctx.recv_scale, ctx.recv_meta,
-                    ctx.recv_count, ctx.flags, ctx.rows_per_parity, base, ctx.cursor, ctx.sent_row, ctx.dctx, 64,
-                    rt.config.wait_timeout_s)
+                    ctx.recv_count, ctx.flags, ctx.rows_per_parity, base, ctx.cursor, ctx.sent_row, ctx.dctx,
+                    _ctas_for_rows(ids.numel()), rt.config.wait_timeout_s)
     # receive rows -> local expert per row -> sorted, padded layout
     row_expert = torch.empty(ctx.rows_per_parity, dtype=torch.int32, device=x.device)
     lib.ep_recv_ids(ctx.recv_count, base_self, row_expert, epr, W, ctx.max_m, ctx.dctx)
@@ -201,8 +207,8 @@ def ep_combine(ctx: AllToAllContext, y_sorted: torch.Tensor, recv: EpRecv, topk_
     base_self = ctx.base[ctx.rank].reshape(-1) if ctx.layout == "packed" else None
     w = topk_w.float().contiguous() if topk_w is not None else None
     return lib.ep_combine(rt.heap, y_sorted.contiguous(), recv.sort.pos_of, ctx.recv_meta, ctx.dctx, base_self, ctx.max_m,
-                          ctx.rows_per_parity, ctx.ret, ctx.ret_flags, recv.topk_ids, w, ctx.num_tot_experts, ctx.cctx, 64,
-                          rt.config.wait_timeout_s)
+                          ctx.rows_per_parity, ctx.ret, ctx.ret_flags, recv.topk_ids, w, ctx.num_tot_experts, ctx.cctx,
+                          _ctas_for_rows(recv.topk_ids.numel()), rt.config.wait_timeout_s)
 
 
 def fast_all_to_all(ctx: AllToAllContext, send_tensor: torch.Tensor, send_split_cumsum: torch.Tensor,

@@ -49,9 +49,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, b
         if out is None:
             out = torch.empty((a2.shape[0], b.shape[0]), dtype=a.dtype, device=a.device)
         if 0 < a2.shape[0] <= SKINNY_M and block_n == 0 and a2.shape[1] % 8 == 0:
-            # decode-size M: stream the weights once with the swap-AB split-K kernel
+            # decode-size M: stream the weights once - the tensor-core GEMV up to eight rows, the swap-AB stream-K
+            # kernel above
             from .gemm_ar import skinny_gemm
-            skinny_gemm(a2, b, out=out.view(a2.shape[0], b.shape[0]))
+            from .gemv import GEMV_FAST_M, gemv_fused, gemv_supported
+            o2 = out.view(a2.shape[0], b.shape[0])
+            if (a2.shape[0] <= GEMV_FAST_M and gemv_supported(a2.shape[0], a2.shape[1]) and b.stride(0) % 8 == 0
+                    and a2.stride(0) % 8 == 0 and a2.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0):
+                gemv_fused(a2, b, out=o2)
+            else:
+                skinny_gemm(a2, b, out=o2)
         else:
             lib.gemm_bf16(a2, b, out.view(a2.shape[0], b.shape[0]), block_n, num_ctas)
         return out.view(*lead, b.shape[0])
