@@ -564,7 +564,18 @@ cudaError_t launch_ep_combine(const EpCombineArgs& a, cudaStream_t s) {
   p.ctx = a.ctx;
   p.symm = to_dev(a.symm);
   int ctas = a.num_ctas > 0 ? a.num_ctas : 64;
-  if (ctas > 592) ctas = 592;   // every CTA waits on remote flags: the grid must be resident (4 x 148 CTAs of 256 threads are)
+  // every CTA waits on remote flags that the last CTA of each rank raises: the whole grid must be resident at once,
+  // so it is clamped to what the occupancy calculator says fits this device
+  static int resident = 0;
+  if (resident == 0) {
+    int dev = 0, sms = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ep_combine_kernel, kEpThreads, 0) != cudaSuccess || per_sm < 1)
+      per_sm = 1;
+    resident = sms * per_sm;
+  }
+  if (ctas > resident) ctas = resident;
   ep_combine_kernel<<<ctas, kEpThreads, 0, s>>>(p);
   return cudaGetLastError();
 }
