@@ -11,7 +11,9 @@
 //   reduce-scatter  every rank computes a partial C; the epilogue TMA-stores each
 //                   tile straight into the owner rank's slot over NVLink and sets
 //                   a per-tile epoch flag there; after its last tile every CTA
-//                   joins the owner-side reduction of the arrived slots.
+//                   joins the owner-side reduction of the arrived slots (single-CTA
+//                   kernel), or the own segment's epilogue sums the arrived partials
+//                   into its accumulators (CTA-pair kernel).
 //
 // Roles inside a CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer
 // (one elected lane) and TMEM owner, warps 2-5 = epilogue: TMEM -> registers ->

@@ -6,7 +6,9 @@ API of the reference: ``create_gemm_rs_context`` / ``gemm_rs``
 
 GPU path: ``csrc/gemm_sm100.cu`` in reduce-scatter mode - the tcgen05 epilogue stores every partial tile
 straight into the owner rank's slot over NVLink (the reference's ``fuse_scatter``) with a per-tile epoch
-flag; all CTAs then reduce the arrived slots of the local row block.
+flag.  Tiles are visited starting with the next rank's rows, so the own rows come last; in the CTA-pair kernel
+their epilogue adds the partials that have arrived from the other ranks to the fp32 accumulators and writes the
+output, in the single-CTA kernel all CTAs reduce the arrived slots of the local row block after their last tile.
 CPU / reference path: ``matmul`` + ``reduce_scatter_tensor`` (layers/nvidia/tp_mlp.py:254-265).
 """
 from __future__ import annotations
