@@ -78,3 +78,31 @@ def test_fp8_quant_reference_roundtrip():
     assert q.dtype == torch.float8_e4m3fn and s.shape == (5, 2)
     back = fp8_dequant(q, s)
     assert (back.float() - x.float()).abs().max() <= 0.07 * x.float().abs().max()
+
+
+def test_tile_arrival_order_matches_a_python_oracle():
+    # C++ host reference of the AG -> grouped-GEMM tile order against a direct restatement
+    import torch
+
+    from triton_distributed_b200 import ops
+
+    torch.manual_seed(3)
+    W, tpr, k, E, blk = 4, 24, 2, 5, 16
+    ids = torch.randint(0, E, (W * tpr, k))
+    srt = ops.sort_topk_ids_align_block_size(ids, E, blk)
+    for rank in range(W):
+        order, stage = ops.tile_arrival_order(srt, tpr, rank, W, blk)
+        sid = srt.sorted_ids.tolist()
+        tiles = (len(sid) + blk - 1) // blk
+        exp_stage = []
+        for t in range(tiles):
+            d = [((i // k) // tpr - rank) % W for i in sid[t * blk:(t + 1) * blk] if i >= 0]
+            exp_stage.append(max(d) if d else -1)
+        assert stage.tolist() == exp_stage
+        o = order.tolist()
+        assert sorted(o) == list(range(tiles))
+        keys = [W if exp_stage[t] < 0 else exp_stage[t] for t in o]
+        assert keys == sorted(keys), "tiles must be visited by arrival stage"
+        for a, b in zip(o, o[1:]):
+            if exp_stage[a] == exp_stage[b]:
+                assert a < b, "expert order is kept inside a stage"

@@ -3,6 +3,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstring>
+
 #include "tdb/api.h"
 #include "tdb/moe.h"
 
@@ -121,11 +123,24 @@ void group_gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, 
   check_cuda(tdb::launch_gemm(g, cur_stream()), "launch_gemm(grouped)");
 }
 
+// (order, stage) of the tiles of an expert-sorted layout for the AG -> grouped-GEMM overlap (host computation)
+std::vector<at::Tensor> moe_tile_arrival_order(const at::Tensor& sorted_ids, int64_t topk, int64_t tokens_per_rank, int64_t rank,
+                                               int64_t world, int64_t block) {
+  at::Tensor ids = sorted_ids.to(at::kCPU, at::kInt).contiguous();
+  std::vector<int32_t> order, stage;
+  tdb::moe_tile_arrival_order(ids.data_ptr<int32_t>(), ids.numel(), topk, tokens_per_rank, rank, world, block, &order, &stage);
+  at::Tensor o = at::empty({static_cast<int64_t>(order.size())}, at::kInt), st = at::empty({static_cast<int64_t>(stage.size())}, at::kInt);
+  std::memcpy(o.data_ptr(), order.data(), order.size() * sizeof(int32_t));
+  std::memcpy(st.data_ptr(), stage.data(), stage.size() * sizeof(int32_t));
+  return {o, st};
+}
+
 }  // namespace
 
 void bind_moe(py::module_& m) {
   m.def("topk_router", &topk_router);
   m.def("moe_align_sort", &moe_align_sort);
+  m.def("moe_tile_arrival_order", &moe_tile_arrival_order);
   m.def("moe_gather", &moe_gather);
   m.def("moe_topk_reduce", &moe_topk_reduce);
   m.def("moe_unsort", &moe_unsort);

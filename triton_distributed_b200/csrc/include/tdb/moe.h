@@ -1,5 +1,6 @@
 // Host API of the mixture-of-experts support kernels (moe.cu).
 #pragma once
+#include <vector>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -26,5 +27,11 @@ cudaError_t launch_moe_topk_reduce(const void* y, const int32_t* pos_of, const f
                                    int64_t out_ld, cudaStream_t s);
 // out[pair] = y[pos_of[pair]]: sorted layout back to (token, slot) order.
 cudaError_t launch_moe_unsort(const void* y, const int32_t* pos_of, void* out, int64_t rows, int N, cudaStream_t s);
+
+// Host reference (moe_sched.cc): stage at which every `block`-row tile of the expert-sorted layout becomes computable
+// during a ring all-gather (largest ring distance of its rows' source ranks; -1 = padding only) and the tile visiting
+// order by stage.
+void moe_tile_arrival_order(const int32_t* sorted_ids, int64_t n_sorted, int topk, int tokens_per_rank, int rank, int world,
+                            int block, std::vector<int32_t>* order, std::vector<int32_t>* stage);
 
 }  // namespace tdb

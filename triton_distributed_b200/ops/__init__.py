@@ -32,3 +32,4 @@ from .gdn import (chunk_gated_delta_rule_fwd, gated_delta_rule_chunked, gated_de
                   prepare_chunk_indices, prepare_lens)
 from .fp8 import (ag_gemm_fp8, dequantize_act_1x128, dequantize_weight_128x128, gemm_fp8_blockscaled,  # noqa: F401,E402
                   gemm_fp8_blockscaled_reference, quantize_act_1x128, quantize_weight_128x128)
+from .moe import tile_arrival_order  # noqa: F401,E402

@@ -116,6 +116,30 @@ def sort_topk_ids_align_block_size(topk_ids: torch.Tensor, num_experts: int, blo
 calc_gather_scatter_index = sort_topk_ids_align_block_size
 
 
+def tile_arrival_order(srt: MoESort, tokens_per_rank: int, rank: int, world: int, block_size: int = BLOCK_M):
+    """Visiting order of the ``block_size``-row tiles of an expert-sorted layout while the token shards of a ring
+    all-gather arrive: ``(order, stage)`` with ``stage[t]`` the largest ring distance of the source ranks of tile
+    ``t``'s rows (-1: padding only) and ``order`` the tiles by stage, expert order kept inside a stage.  Computed on the
+    host by the C++ reference (``csrc/moe_sched.cc``) when the native library is there, else in Python; the reference's
+    ``threadblock_swizzle_ag_moe`` kernels produce the same order (threadblock_swizzle_ag_moe_triton.py:96-216)."""
+    lib = _native.load(False)
+    if lib is not None:
+        o, st = lib.moe_tile_arrival_order(srt.sorted_ids, int(srt.k), int(tokens_per_rank), int(rank), int(world),
+                                           int(block_size))
+        return o, st
+    ids = srt.sorted_ids.cpu().tolist()
+    tiles = (len(ids) + block_size - 1) // block_size
+    stage = []
+    for t in range(tiles):
+        s = -1
+        for i in ids[t * block_size:(t + 1) * block_size]:
+            if i >= 0:
+                s = max(s, ((i // srt.k) // tokens_per_rank - rank) % world)
+        stage.append(s)
+    order = sorted(range(tiles), key=lambda t: world if stage[t] < 0 else stage[t])
+    return torch.tensor(order, dtype=torch.int32), torch.tensor(stage, dtype=torch.int32)
+
+
 def group_gemm_sorted(a_sorted: torch.Tensor, w: torch.Tensor, srt: MoESort) -> torch.Tensor:
     """Rows sorted by expert [cap, K] x w [E, N, K] -> [cap, N] (rows of skipped tiles are left unwritten)."""
     if _native.use_native(a_sorted, w) and a_sorted.dtype == torch.bfloat16:
