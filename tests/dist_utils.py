@@ -31,8 +31,22 @@ def _worker(rank, world_size, port, fn, args, err_q):
         raise
 
 
+_RENDEZVOUS_ERRORS = ("Address already in use", "EADDRINUSE", "Connection refused", "Connection reset",
+                      "failed to connect", "Broken pipe")
+
+
 def run_cpu_ranks(fn, world_size=2, args=()):
-    """Run ``fn(rank, world_size, *args)`` on ``world_size`` gloo ranks; raises if any rank failed."""
+    """Run ``fn(rank, world_size, *args)`` on ``world_size`` gloo ranks; raises if any rank failed.  A failure of the
+    rendezvous itself (the free port was taken between probing and binding) is retried once on another port."""
+    try:
+        _run_cpu_ranks_once(fn, world_size, args)
+    except AssertionError as e:
+        if not any(m in str(e) for m in _RENDEZVOUS_ERRORS):
+            raise
+        _run_cpu_ranks_once(fn, world_size, args)
+
+
+def _run_cpu_ranks_once(fn, world_size, args):
     ctx = mp.get_context("spawn")
     err_q = ctx.SimpleQueue()
     port = free_port()
