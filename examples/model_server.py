@@ -25,14 +25,31 @@ import triton_distributed_b200 as tdb  # noqa: E402
 from triton_distributed_b200.models import Engine, ModelConfig  # noqa: E402
 
 
+def check_request(engine, req):
+    """Validate a client's request on the host (every rank runs the same check on the broadcast copy, so all ranks
+    agree): returns (ids, gen_len) or raises ValueError.  Nothing a client sends reaches a kernel unchecked."""
+    if not isinstance(req, dict) or "input_ids" not in req:
+        raise ValueError("request needs an 'input_ids' field")
+    try:
+        ids = torch.tensor(req["input_ids"], dtype=torch.int64)
+        gen_len = int(req.get("gen_len", 16))
+    except (TypeError, ValueError, RuntimeError) as e:
+        raise ValueError(f"malformed request: {e}")
+    engine.validate_request(ids, gen_len)
+    return ids, gen_len
+
+
 def handle(engine, req):
-    ids = torch.tensor(req["input_ids"], dtype=torch.int64, device=engine.rt.device)
+    try:
+        ids, gen_len = check_request(engine, req)
+    except ValueError as e:
+        return {"error": str(e)}
     t0 = time.perf_counter()
-    out = engine.serve(ids, int(req.get("gen_len", 16)))
+    out = engine.serve(ids, gen_len)
     if torch.cuda.is_available():
         torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    return {"output_ids": out.tolist(), "ms_per_token": 1e3 * dt / max(1, int(req.get("gen_len", 16)))}
+    return {"output_ids": out.tolist(), "ms_per_token": 1e3 * dt / max(1, gen_len)}
 
 
 def main():

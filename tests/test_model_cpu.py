@@ -93,3 +93,90 @@ def test_safetensors_roundtrip_and_slices():
             assert torch.equal(ld["a"], a) and torch.equal(ld["b"], b)
         except ImportError:
             pass
+
+
+def _run_sampling(rank, world, ckpt, out_dir):
+    """temperature > 0 on two ranks: every rank must return the same ids (same generator seed + broadcast)."""
+    import torch.distributed as dist
+
+    from triton_distributed_b200.models import Engine, ModelConfig
+
+    cfg = ModelConfig(model_name="ckpt", max_length=32, dtype=torch.float32, rank=rank, world_size=world,
+                      checkpoint_dir=ckpt)
+    eng = Engine(cfg, temperature=0.9, top_p=0.95, seed=17)
+    eng.backend = "triton_dist_AR"
+    eng.no_graph = True
+    toks = eng.serve(torch.tensor([[5, 9, 2, 77, 31], [1, 2, 3, 4, 5]]), 6)
+    gathered = [torch.empty_like(toks) for _ in range(world)]
+    dist.all_gather(gathered, toks)
+    for t in gathered:
+        assert torch.equal(t, gathered[0]), (rank, t, gathered[0])
+    # a second request re-uses the engine: the contexts of the first one are kept, not re-created
+    key = eng._ctx_key
+    toks2 = eng.serve(torch.tensor([[7, 7, 7], [8, 8, 8]]), 3)
+    assert eng._ctx_key == key and toks2.shape == (2, 3)
+
+
+def test_sampling_is_identical_on_all_ranks():
+    with tempfile.TemporaryDirectory() as d:
+        _write_checkpoint(d)
+        run_cpu_ranks(_run_sampling, 2, (d, d))
+
+
+def _run_reject(rank, world, ckpt, out_dir):
+    import pytest
+
+    from triton_distributed_b200.models import Engine, ModelConfig
+
+    cfg = ModelConfig(model_name="ckpt", max_length=16, dtype=torch.float32, rank=rank, world_size=world,
+                      checkpoint_dir=ckpt)
+    eng = Engine(cfg)
+    eng.no_graph = True
+    ok = torch.tensor([[1, 2, 3, 4]])
+    with pytest.raises(ValueError, match="max_length"):
+        eng.serve(ok, 13)                                   # 4 + 13 > 16 cache rows per sequence
+    with pytest.raises(ValueError, match="token ids"):
+        eng.serve(torch.tensor([[1, 2, 97]]), 2)            # vocabulary is 97
+    with pytest.raises(ValueError, match="token ids"):
+        eng.serve(torch.tensor([[-1, 2, 3]]), 2)
+    with pytest.raises(ValueError, match="gen_len"):
+        eng.serve(ok, 0)
+    with pytest.raises(ValueError):
+        eng.serve(torch.zeros(0, 4, dtype=torch.int64), 2)
+    assert eng.kv_cache is None                             # nothing was allocated or launched for any of them
+    assert eng.serve(ok, 12).shape == (1, 12)               # exactly full is fine
+
+
+def test_engine_rejects_requests_that_do_not_fit():
+    with tempfile.TemporaryDirectory() as d:
+        _write_checkpoint(d)
+        run_cpu_ranks(_run_reject, 1, (d, d))
+
+
+def test_model_server_checks_requests_on_the_host():
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("model_server", os.path.join(os.path.dirname(__file__), "..", "examples",
+                                                                               "model_server.py"))
+    ms = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ms)
+
+    class FakeEngine:
+        def __init__(self):
+            self.served = 0
+
+        def validate_request(self, ids, gen_len):
+            if ids.shape[1] + gen_len > 8:
+                raise ValueError("prompt + gen_len exceeds max_length")
+
+        def serve(self, ids, gen_len):
+            self.served += 1
+            return ids[:, :1].repeat(1, gen_len)
+
+    e = FakeEngine()
+    assert "error" in ms.handle(e, {"input_ids": [[1, 2, 3]], "gen_len": 100})
+    assert "error" in ms.handle(e, {"gen_len": 1})
+    assert "error" in ms.handle(e, {"input_ids": [[1, 2], [3]], "gen_len": 1})
+    assert "error" in ms.handle(e, {"input_ids": "abc", "gen_len": 1})
+    assert e.served == 0
+    assert ms.handle(e, {"input_ids": [[1, 2, 3]], "gen_len": 2})["output_ids"] == [[1, 1]]

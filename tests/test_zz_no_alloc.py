@@ -4,7 +4,7 @@ Some users of the library run under another component's memory manager (a servin
 framework that owns the device memory, a bare C program with a fixed buffer set) and may not allocate; for them
 the split-KV workspace is a fixed array inside the library.  This test drives that entry point with ctypes,
 exactly as such a caller would, and checks it against the regular entry point (which takes a workspace tensor)
-on two consecutive calls - the second one re-uses the array with the first call's leftovers in it.
+and against an fp32 PyTorch restatement of the attention on consecutive calls - the second one re-uses the array with the first call's leftovers in it.
 
 The file name makes pytest collect it last, so a run that stops at the first failure has already run the rest.
 """
@@ -41,6 +41,21 @@ def _case(B, Hq, Hkv, D, page, lens, seed):
     return q, k, v, bt, kv_lens
 
 
+def _oracle(q, k, v, bt, kv_lens):
+    """Plain fp32 softmax attention over the paged cache, one sequence at a time."""
+    B, Hq, D = q.shape
+    page, Hkv = k.shape[1], k.shape[2]
+    out = torch.empty(B, Hq, D, dtype=torch.float32, device=q.device)
+    for b in range(B):
+        n = int(kv_lens[b])
+        pages = bt[b, :(n + page - 1) // page].long()
+        kk = k[pages].reshape(-1, Hkv, D)[:n].float().repeat_interleave(Hq // Hkv, dim=1)   # [n, Hq, D]
+        vv = v[pages].reshape(-1, Hkv, D)[:n].float().repeat_interleave(Hq // Hkv, dim=1)
+        s = torch.einsum("hd,nhd->hn", q[b].float(), kk) / math.sqrt(D)
+        out[b] = torch.einsum("hn,nhd->hd", torch.softmax(s, dim=-1), vv)
+    return out
+
+
 def _call(lib, q, k, v, bt, kv_lens, splits, out):
     B, Hq, D = q.shape
     return lib.tdb_decode_attn_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), bt.data_ptr(), kv_lens.data_ptr(),
@@ -73,6 +88,8 @@ def test_no_alloc_decode_matches_regular_entry_point_twice():
         ref = gqa_fwd_batch_decode(q, k, v, None, None, kv_lens, bt, kv_split=splits)
         torch.cuda.synchronize()
         torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+        # and against a plain fp32 restatement of the op, so both entry points cannot be wrong together
+        torch.testing.assert_close(out.float(), _oracle(q, k, v, bt, kv_lens), rtol=2e-2, atol=2e-2)
 
 
 def test_no_alloc_rejects_oversized_request():

@@ -1,3 +1,4 @@
+#include <atomic>
 // Attention kernels over a paged KV cache (bf16, GQA, head dim 64 or 128):
 //
 //   flash_fwd_kernel         var-len causal prefill / context-parallel attention: one CTA = 64 query rows of one
@@ -300,11 +301,20 @@ __global__ void dist_combine_kernel(const DistCombineParams p) {
   }
 }
 
+// The opt-in to more than 48 KB of dynamic shared memory is an attribute of the kernel ON ONE DEVICE, so it is
+// remembered per device ordinal (one bit each); the attribute call itself allocates nothing and may be repeated.
+struct SmemOptIn {
+  std::atomic<uint64_t> done{0};
+};
 template <typename K>
-cudaError_t ensure_smem(K kernel, int bytes, bool* flag) {
-  if (*flag) return cudaSuccess;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) *flag = true;
+cudaError_t ensure_smem(K kernel, int bytes, SmemOptIn* st) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const uint64_t bit = 1ull << (dev & 63);
+  if (st->done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) st->done.fetch_or(bit, std::memory_order_release);
   return e;
 }
 
@@ -341,12 +351,12 @@ cudaError_t launch_flash_fwd(const FlashFwdArgs& a, cudaStream_t stream) {
   if (a.batch == 0 || a.max_q_len == 0) return cudaSuccess;
   dim3 grid((a.max_q_len + 63) / 64, a.num_q_heads, a.batch);
   if (a.head_dim == 128) {
-    static bool set = false;
+    static SmemOptIn set;
     cudaError_t e = ensure_smem(flash_fwd_kernel<128>, Tiles<128>::kSmem, &set);
     if (e != cudaSuccess) return e;
     flash_fwd_kernel<128><<<grid, kAttnThreads, Tiles<128>::kSmem, stream>>>(p);
   } else {
-    static bool set = false;
+    static SmemOptIn set;
     cudaError_t e = ensure_smem(flash_fwd_kernel<64>, Tiles<64>::kSmem, &set);
     if (e != cudaSuccess) return e;
     flash_fwd_kernel<64><<<grid, kAttnThreads, Tiles<64>::kSmem, stream>>>(p);
@@ -382,12 +392,12 @@ cudaError_t launch_decode_splitkv(const DecodeArgs& a, cudaStream_t stream) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const bool deep = static_cast<int64_t>(grid.x) * grid.y * grid.z <= sms;
-  auto launch = [&](auto kernel, int smem, bool* set) -> cudaError_t {
+  auto launch = [&](auto kernel, int smem, SmemOptIn* set) -> cudaError_t {
     cudaError_t e = ensure_smem(kernel, smem, set);
     if (e != cudaSuccess) return e;
     return launch_pdl(kernel, grid, dim3(kAttnThreads), static_cast<size_t>(smem), stream, p);
   };
-  static bool set128_2 = false, set128_4 = false, set64_2 = false, set64_4 = false;
+  static SmemOptIn set128_2, set128_4, set64_2, set64_4;
   if (a.head_dim == 128) {
     return deep ? launch(decode_splitkv_kernel<128, 4>, 2 * Tiles<128>::kSmem, &set128_4)
                 : launch(decode_splitkv_kernel<128, 2>, Tiles<128>::kSmem, &set128_2);
@@ -445,7 +455,8 @@ constexpr int kNoAllocMaxDevices = 64;
 
 static __device__ __align__(256) float g_decode_scratch[kNoAllocFloats];
 
-float* g_scratch_addr[kNoAllocMaxDevices] = {nullptr};
+// device address of the array per device ordinal; published once, concurrent first calls store the same value
+std::atomic<float*> g_scratch_addr[kNoAllocMaxDevices];
 thread_local char g_noalloc_err[256] = "";
 
 int noalloc_fail(int code, const char* what, const char* detail) {
@@ -482,17 +493,17 @@ extern "C" int tdb_decode_attn_noalloc(const void* q, const void* k_cache, const
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return noalloc_fail(TDB_NOALLOC_CUDA_ERROR, "cudaGetDevice", cudaGetErrorString(e));
   if (dev < 0 || dev >= kNoAllocMaxDevices) return noalloc_fail(TDB_NOALLOC_BAD_ARGUMENT, "device ordinal out of range", nullptr);
-  if (g_scratch_addr[dev] == nullptr) {
+  float* scratch = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     // first call on this device (it is the current one): resolve the symbol to its address on this device
-    float* p = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_decode_scratch);
-    if (e != cudaSuccess || p == nullptr)
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_decode_scratch);
+    if (e != cudaSuccess || scratch == nullptr)
       return noalloc_fail(TDB_NOALLOC_CUDA_ERROR, "cudaGetSymbolAddress", cudaGetErrorString(e));
-    g_scratch_addr[dev] = p;
+    g_scratch_addr[dev].store(scratch, std::memory_order_release);
   }
   tdb::DecodeArgs a;
   a.q = q;
-  a.workspace = g_scratch_addr[dev];
+  a.workspace = scratch;
   a.kv_lens = kv_lens;
   a.kv.k_cache = k_cache;
   a.kv.v_cache = v_cache;

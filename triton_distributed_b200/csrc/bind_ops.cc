@@ -101,8 +101,9 @@ void primitives_test(SymmHeap& h, at::Tensor& data, at::Tensor& scratch, at::Ten
              "launch_primitives_test");
 }
 
-void timeout_probe(SymmHeap& h, at::Tensor& flag, int64_t expected, double timeout_s) {
-  check_cuda(tdb::launch_timeout_probe(reinterpret_cast<const uint32_t*>(flag.data_ptr()), expected,
+// cmp: 0 ==, 1 >= (wrap-safe), 2 !=
+void timeout_probe(SymmHeap& h, at::Tensor& flag, int64_t expected, double timeout_s, int64_t cmp) {
+  check_cuda(tdb::launch_timeout_probe(reinterpret_cast<const uint32_t*>(flag.data_ptr()), expected, cmp,
                                        h.info(ns(timeout_s)), cur_stream()),
              "launch_timeout_probe");
 }
@@ -175,6 +176,8 @@ at::Tensor qk_norm_rope_kv(const at::Tensor& qkv, c10::optional<at::Tensor> qw, 
   TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous(), "positions must be int64");
   TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous(), "caches must be contiguous");
   const int64_t T = qkv.size(0);
+  TORCH_CHECK(k_cache.numel() == v_cache.numel() && k_cache.numel() % (Hkv * D) == 0, "qk_norm_rope_kv: cache shape mismatch");
+  const int64_t cache_rows = k_cache.numel() / (Hkv * D);
   at::Tensor q = at::empty({T, Hq, D}, qkv.options());
   const int64_t* sl = nullptr;
   if (slots.has_value()) {
@@ -185,7 +188,7 @@ at::Tensor qk_norm_rope_kv(const at::Tensor& qkv, c10::optional<at::Tensor> qw, 
   check_cuda(tdb::launch_qk_norm_rope_kv(qkv.data_ptr(), qw.has_value() ? qw->data_ptr() : nullptr,
                                          kw.has_value() ? kw->data_ptr() : nullptr, positions.data_ptr<int64_t>(), sl,
                                          q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), T, Hq, Hkv, D,
-                                         qkv.stride(0), eps, theta, Hkv * D, cur_stream()),
+                                         qkv.stride(0), eps, theta, Hkv * D, cache_rows, cur_stream()),
              "launch_qk_norm_rope_kv");
   return q;
 }
@@ -278,7 +281,8 @@ void bind_more(py::module_& m) {
   m.def("all_gather", &all_gather);
   m.def("all_gather_ll", &all_gather_ll);
   m.def("primitives_test", &primitives_test);
-  m.def("timeout_probe", &timeout_probe);
+  m.def("timeout_probe", &timeout_probe, py::arg("heap"), py::arg("flag"), py::arg("expected"), py::arg("timeout_s"),
+        py::arg("cmp") = 1);
   m.def("p2p_copy", &p2p_copy);
   m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("residual") = py::none());
   m.def("silu_mul", &silu_mul);

@@ -449,9 +449,10 @@ __global__ void primitives_test_kernel(int32_t* data, int32_t* scratch, uint32_t
   rank_barrier_block(symm, bar_flags, 2 * epoch, kKernelPrimitive, 3);
 }
 
-// A wait that nothing satisfies: used to check that bounded waits return a status.
-__global__ void timeout_probe_kernel(const uint32_t* flag, uint32_t expected, const SymmInfo symm) {
-  if (threadIdx.x == 0) wait_until(symm, flag, expected, kCmpGe, kKernelPrimitive, 99, -1, 0);
+// Stream-ordered bounded wait on one flag: the stream continues when cmp(flag, expected) holds, or after the time
+// limit with a status record (also the probe that shows a wait nothing satisfies returns a status).
+__global__ void timeout_probe_kernel(const uint32_t* flag, uint32_t expected, int cmp, const SymmInfo symm) {
+  if (threadIdx.x == 0) wait_until(symm, flag, expected, static_cast<CmpOp>(cmp), kKernelPrimitive, 99, -1, 0);
 }
 
 // ---------------------------------------------------------------------------
@@ -620,9 +621,10 @@ cudaError_t launch_primitives_test(int32_t* data, int32_t* scratch, uint32_t* si
   return cudaGetLastError();
 }
 
-cudaError_t launch_timeout_probe(const uint32_t* flag, uint32_t expected, const SymmInfoHost& symm,
+cudaError_t launch_timeout_probe(const uint32_t* flag, uint32_t expected, int cmp, const SymmInfoHost& symm,
                                  cudaStream_t stream) {
-  timeout_probe_kernel<<<1, 32, 0, stream>>>(flag, expected, to_dev(symm));
+  if (cmp < 0 || cmp > 2) return cudaErrorInvalidValue;
+  timeout_probe_kernel<<<1, 32, 0, stream>>>(flag, expected, cmp, to_dev(symm));
   return cudaGetLastError();
 }
 

@@ -21,6 +21,9 @@
 //   * All calls share the one array and it keeps the previous call's contents.  Nothing in it has to start at
 //     zero: every partial the combine step reads is written by the first step of the same call.  Two calls
 //     that overlap on the GPU (different streams, no ordering between them) race on the array; serialise them.
+//   * Host threads: the per-device set-up state (array address, shared-memory opt-in of the kernels) is published
+//     atomically, so several host threads may call concurrently, each with its own device current; what they must
+//     not do is overlap two calls on the SAME device's GPU timeline (previous point).
 //   * Returns 0 on success, a negative TDB_NOALLOC_* code otherwise; tdb_noalloc_last_error() gives the text of
 //     the last failure on the calling thread.
 #pragma once

@@ -143,15 +143,18 @@ TDB_DEVICE void task_rope_kv(const MegaOp& op, int t) {
   const int pos_i = kv_off[t];
   const float pos = static_cast<float>(pos_i);
   const int64_t slot = static_cast<int64_t>(t) * max_len + pos_i;
+  const bool slot_ok = pos_i >= 0 && pos_i < max_len;   // a sequence that is already full writes nothing
   const float eps = op.f[0], log2_theta = op.f[1];
   for (int h = threadIdx.x >> 5; h < Hq + 2 * Hkv; h += kThreads / 32) {
     const __nv_bfloat16* src = qkv + t * ld + static_cast<int64_t>(h) * D;
     if (h >= Hq + Hkv) {
+      if (!slot_ok) continue;
       __nv_bfloat16* dst = v_cache + slot * (Hkv * D) + static_cast<int64_t>(h - Hq - Hkv) * D;
       for (int i = lane; i < (D >> 3); i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
       continue;
     }
     const bool is_q = h < Hq;
+    if (!is_q && !slot_ok) continue;
     const __nv_bfloat16* wgt = is_q ? qw : kw;
     float ss = 0.f;
     for (int j = lane; j < (half >> 1); j += 32) {

@@ -127,7 +127,7 @@ __global__ void qk_norm_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, co
                                        const int64_t* __restrict__ slots, __nv_bfloat16* __restrict__ q_out,
                                        __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int T,
                                        int Hq, int Hkv, int D, int64_t ld_qkv, float eps, float log2_theta,
-                                       int64_t cache_slot_stride) {
+                                       int64_t cache_slot_stride, int64_t cache_rows) {
   pdl_wait();                 // qkv comes from the previous kernel
   pdl_launch_dependents();
   const int warps_per_block = blockDim.x >> 5;
@@ -140,8 +140,10 @@ __global__ void qk_norm_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, co
   const __nv_bfloat16* src = qkv + t * ld_qkv + static_cast<int64_t>(h) * D;
   const int half = D >> 1;
   const int64_t slot = slots ? slots[t] : t;
+  // rows outside the cache (negative = "do not store", or beyond its last row) are never written
+  const bool slot_ok = slot >= 0 && slot < cache_rows;
   if (h >= Hq + Hkv) {  // v: plain copy
-    if (slot < 0) return;
+    if (!slot_ok) return;
     __nv_bfloat16* dst = v_cache + slot * cache_slot_stride + static_cast<int64_t>(h - Hq - Hkv) * D;
     for (int i = lane; i < (D >> 3); i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
     return;
@@ -162,7 +164,7 @@ __global__ void qk_norm_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, co
   if (is_q) {
     dst = q_out + (static_cast<int64_t>(t) * Hq + h) * D;
   } else {
-    if (slot < 0) return;
+    if (!slot_ok) return;
     dst = k_cache + slot * cache_slot_stride + static_cast<int64_t>(h - Hq) * D;
   }
   for (int j = lane; j < (half >> 1); j += 32) {
@@ -301,7 +303,7 @@ cudaError_t launch_add(const void* a, const void* b, void* out, int64_t n, cudaS
 cudaError_t launch_qk_norm_rope_kv(const void* qkv, const void* qw, const void* kw, const int64_t* positions,
                                    const int64_t* slots, void* q_out, void* k_cache, void* v_cache, int T, int Hq,
                                    int Hkv, int D, int64_t ld_qkv, float eps, float rope_theta,
-                                   int64_t cache_slot_stride, cudaStream_t s) {
+                                   int64_t cache_slot_stride, int64_t cache_rows, cudaStream_t s) {
   if (D % 8 != 0 || (D / 2) % 2 != 0 || ld_qkv % 8 != 0) return cudaErrorInvalidValue;
   if (T == 0) return cudaSuccess;
   const int64_t warps = static_cast<int64_t>(T) * (Hq + 2 * Hkv);
@@ -310,7 +312,7 @@ cudaError_t launch_qk_norm_rope_kv(const void* qkv, const void* qw, const void* 
                     reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const __nv_bfloat16*>(qw),
                     reinterpret_cast<const __nv_bfloat16*>(kw), positions, slots, reinterpret_cast<__nv_bfloat16*>(q_out),
                     reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache), T, Hq, Hkv, D,
-                    ld_qkv, eps, log2f(rope_theta), cache_slot_stride);
+                    ld_qkv, eps, log2f(rope_theta), cache_slot_stride, cache_rows);
 }
 
 cudaError_t launch_embedding(const int64_t* ids, const void* table, void* out, int64_t T, int H, int64_t vocab,

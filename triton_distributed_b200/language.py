@@ -70,12 +70,23 @@ def set_signal(flag: torch.Tensor, value: int, stream=None):
         lib.stream_write_value32(flag.data_ptr(), int(value))
 
 
-def wait_eq(flag: torch.Tensor, value: int, stream=None, geq: bool = False):
-    """Stream-ordered wait on a 32-bit flag (cuStreamWaitValue32).  The stream blocks until the value is there: only
-    use it for flags that a kernel or stream of this job is certain to write."""
+def wait_eq(flag: torch.Tensor, value: int, stream=None, geq: bool = False, timeout_s=None, bounded: bool = True):
+    """Stream-ordered wait on a 32-bit flag: later work on the stream starts once the flag equals (``geq``: has
+    reached) ``value``.
+
+    By default the wait is a one-thread kernel with the runtime's time limit (``TDB200_WAIT_TIMEOUT_S`` or
+    ``timeout_s``): when nothing writes the flag the stream continues after the limit and
+    ``Runtime.check_status()`` raises ``CommTimeoutError``.  ``bounded=False`` uses the driver's stream memory
+    operation (cuStreamWaitValue32), which has NO time limit: the stream stays blocked until the value is there, so
+    only use it for flags that a kernel or stream of this job is certain to write."""
     lib = _native.load(True)
+    rt = get_runtime()
     with torch.cuda.stream(stream or torch.cuda.current_stream()):
-        lib.stream_wait_value32(flag.data_ptr(), int(value), bool(geq))
+        if bounded and rt.heap is not None:
+            lib.timeout_probe(rt.heap, flag, int(value), float(timeout_s if timeout_s is not None else rt.config.wait_timeout_s),
+                              CMP_GE if geq else CMP_EQ)
+        else:
+            lib.stream_wait_value32(flag.data_ptr(), int(value), bool(geq))
 
 
 notify = set_signal

@@ -147,8 +147,13 @@ class Runtime:
         if self.world_size > 1:
             dist.barrier(group=self.cpu_group)
 
-    def symm_tensor(self, shape: Sequence[int], dtype: torch.dtype, zero: bool = True) -> torch.Tensor:
-        """Allocate a tensor at the same heap offset on every rank (collective: same call order on all ranks)."""
+    def symm_tensor(self, shape: Sequence[int], dtype: torch.dtype, zero: bool = True, sync: bool = True) -> torch.Tensor:
+        """Allocate a tensor at the same heap offset on every rank (collective: same call order on all ranks).
+
+        Like the reference's ``nvshmem_create_tensor`` the call ends with a barrier over all ranks (``sync``): when
+        it returns, every rank has allocated AND zero-filled its copy, so a peer may write into it or raise a flag in
+        it right away.  Callers that allocate several tensors in a row may pass ``sync=False`` and finish with
+        ``torch.cuda.synchronize(); host_barrier()`` themselves."""
         shape = tuple(int(s) for s in shape)
         if self.heap is None:
             return torch.zeros(shape, dtype=dtype, device=self.device)
@@ -158,6 +163,9 @@ class Runtime:
         self._allocs[t.data_ptr()] = (off, nbytes)
         if zero:
             t.zero_()
+        if sync and self.world_size > 1:
+            torch.cuda.synchronize()
+            self.host_barrier()
         return t
 
     def symm_tensors(self, shape: Sequence[int], dtype: torch.dtype) -> List[torch.Tensor]:
