@@ -41,6 +41,38 @@ def timed(fn, iters, warmup, fl, rt):
     return statistics.median(t.tolist())
 
 
+def loop_ms(fn, iters, rt):
+    """Back-to-back calls with no barrier or flush in between (how a layer stack issues them): ms per call, max over
+    ranks."""
+    torch.cuda.synchronize()
+    if rt.world_size > 1:
+        dist.barrier(group=rt.group)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], device="cuda", dtype=torch.float64)
+    if rt.world_size > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=rt.group)
+    return float(t.item())
+
+
+def stall_summary(fn, ctx, rt, dev):
+    """One call with the pair kernel's stall counters on; returns the summary of the slowest rank's view (rank 0's)."""
+    ctx.stats = ops.new_stall_counters(dev)
+    torch.cuda.synchronize()
+    if rt.world_size > 1:
+        dist.barrier(group=rt.group)
+    fn()
+    torch.cuda.synchronize()
+    out = ops.summarize_stall_counters(ctx.stats)
+    ctx.stats = None
+    return {k: round(v, 4) if isinstance(v, float) else v for k, v in out.items()}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--M", type=int, default=8192)
@@ -48,7 +80,8 @@ def main():
     ap.add_argument("--N", type=int, default=28672)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--n-comm", default="8")
+    ap.add_argument("--n-comm", default="0", help="comma list of comm-CTA counts for the AG-GEMM (0 = automatic)")
+    ap.add_argument("--stats", type=int, default=1, help="also report the kernel's stall counters")
     ap.add_argument("--multimem", type=int, default=0)
     ap.add_argument("--only", default="", help="comma list of op names to run (default: all)")
     args = ap.parse_args()
@@ -109,17 +142,39 @@ def main():
         emit("own_gemm_only_ag_shape", timed(lambda: ops.gemm(full, w1, out=h), args.iters, args.warmup, fl, rt))
     if want("own_gemm_only_rs_shape"):
         emit("own_gemm_only_rs_shape", timed(lambda: ops.gemm(h, w2, out=part), args.iters, args.warmup, fl, rt))
+    if want("torch_gemm_only_rs_shape"):
+        emit("torch_gemm_only_rs_shape", timed(lambda: torch.matmul(h, w2t, out=part), args.iters, args.warmup, fl, rt))
     for nc in ([int(v) for v in args.n_comm.split(",")] if want("own_ag_gemm") else []):
         ag_ctx = ops.create_ag_gemm_context(max_M=M, K=K, dtype=torch.bfloat16, n_comm_ctas=nc,
                                             use_multimem=bool(args.multimem))
-        emit("own_ag_gemm", timed(lambda: ops.ag_gemm(a, w1, ag_ctx, out=h), args.iters, args.warmup, fl, rt),
-             {"n_comm": nc, "multimem": args.multimem})
+        f_ag = lambda: ops.ag_gemm(a, w1, ag_ctx, out=h)   # noqa: E731
+        extra = {"n_comm": nc, "multimem": args.multimem}
+        ms = timed(f_ag, args.iters, args.warmup, fl, rt)
+        extra["loop_ms"] = loop_ms(f_ag, args.iters, rt)
+        if args.stats and W > 1:
+            extra["stalls"] = stall_summary(f_ag, ag_ctx, rt, dev)
+        emit("own_ag_gemm", ms, extra)
         rt.check_status()
         ag_ctx.finalize()
     if want("own_gemm_rs"):
         rs_ctx = ops.create_gemm_rs_context(max_M=M, N=K)
-        emit("own_gemm_rs", timed(lambda: ops.gemm_rs(h, w2, rs_ctx, out=o), args.iters, args.warmup, fl, rt))
+        f_rs = lambda: ops.gemm_rs(h, w2, rs_ctx, out=o)   # noqa: E731
+        ms = timed(f_rs, args.iters, args.warmup, fl, rt)
+        extra = {"loop_ms": loop_ms(f_rs, args.iters, rt)}
+        if args.stats and W > 1:
+            extra["stalls"] = stall_summary(f_rs, rs_ctx, rt, dev)
+        emit("own_gemm_rs", ms, extra)
         rt.check_status()
+        if want("own_pair_loop") and W > 1:
+            ag_ctx = ops.create_ag_gemm_context(max_M=M, K=K, dtype=torch.bfloat16)
+
+            def both():
+                ops.ag_gemm(a, w1, ag_ctx, out=h)
+                ops.gemm_rs(h, w2, rs_ctx, out=o)
+            for _ in range(3):
+                both()
+            emit("own_pair_loop", loop_ms(both, args.iters, rt))
+            rt.check_status()
     tdb.finalize_distributed()
 
 

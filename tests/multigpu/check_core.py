@@ -131,7 +131,9 @@ def check_rs_ag(rt):
 
 def check_fused_gemms(rt, quick):
     W = rt.world_size
-    shapes = [(128, 256, 256), (300, 520, 264), (1024, 1024, 512)] + ([] if quick else [(1024, 3584, 8192)])
+    # (2560, 1024, 256): on two ranks 80 pair tiles, more than one wave, so the tail runs as half-width tiles
+    shapes = [(128, 256, 256), (300, 520, 264), (1024, 1024, 512), (2560, 1024, 256)] + (
+        [] if quick else [(1024, 3584, 8192)])
     for (m, N, K) in shapes:   # m = rows per rank
         for use_mc in ([True, False] if rt.has_multicast else [False]):
             ctx = ops.create_ag_gemm_context(max_M=m * W, K=K, dtype=torch.bfloat16, use_multimem=use_mc)
@@ -149,6 +151,7 @@ def check_fused_gemms(rt, quick):
                 rt.check_status()
                 err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
                 assert err < 2e-2, f"ag_gemm m={m} N={N} K={K} mc={use_mc} it={it}: rel err {err}"
+                torch.testing.assert_close(out.float(), ref, rtol=1e-2, atol=3e-2)
             ctx.finalize()
     for (m, N, K) in shapes:   # m = rows per rank of the output
         ctx = ops.create_gemm_rs_context(max_M=m * W, N=N)

@@ -17,6 +17,9 @@ def _check(M, N, K, block_n=0, seed=0):
     err = (out.float() - ref).abs().max().item()
     scale = ref.abs().max().item() + 1e-6
     assert err / scale < 2e-2, f"M={M} N={N} K={K} block_n={block_n}: max err {err} (scale {scale})"
+    # element-wise: the only error a correct kernel makes is the bf16 rounding of the output (2^-9 relative); one
+    # dropped or doubled 64-wide k-block moves an element by about 0.05 * 8 = 0.4, far outside this band
+    torch.testing.assert_close(out.float(), ref, rtol=1e-2, atol=2e-2)
 
 
 @pytest.mark.parametrize("shape", [(128, 256, 64), (128, 256, 256), (256, 512, 1024), (1024, 1024, 2048)])
@@ -39,6 +42,34 @@ def test_gemm_block_n(block_n):
 def test_gemm_cta_pair(shape):
     # 256 x 256 tiles over two SMs (cta_group::2); 384 and 1000 rows leave the second CTA of a pair without rows
     _check(*shape, block_n=512)
+
+
+def test_gemm_large_k():
+    # the benchmark's K: 128 k-blocks per tile, the smem ring wraps 21 times per tile
+    _check(512, 512, 8192, block_n=512)
+    _check(256, 384, 8192)
+
+
+@pytest.mark.parametrize("shape", [(2048, 2560, 512),    # 80 pair tiles on 74 pairs: 6 tail tiles run as 12 halves
+                                   (2048, 2460, 256),    # last tile column is 156 wide: second half has 28 columns
+                                   (2048, 2360, 256),    # last tile column is 56 wide: its second half is empty
+                                   (2304, 2560, 320)])   # 90 tiles: 16 tail tiles as 32 halves
+def test_gemm_cta_pair_split_tail(shape):
+    _check(*shape, block_n=512)
+
+
+def test_gemm_stall_counters():
+    from triton_distributed_b200.ops import STALL_COUNTERS, gemm, new_stall_counters, summarize_stall_counters
+
+    a = torch.randn(2048, 1024, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(2560, 1024, device="cuda") * 0.05).to(torch.bfloat16)
+    st = new_stall_counters(a.device)
+    out = gemm(a, b, block_n=512, stats=st)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.float(), a.float() @ b.float().t(), rtol=1e-2, atol=2e-2)
+    summ = summarize_stall_counters(st)
+    assert summ["ctas"] == 148 and summ["cta_total_cycles_max"] > 0
+    assert all(0.0 <= summ[f"{n}_mean_frac"] <= 1.0 for n in STALL_COUNTERS[:-1])
 
 
 def test_gemm_many_tiles_per_cta():

@@ -301,21 +301,9 @@ __global__ void dist_combine_kernel(const DistCombineParams p) {
   }
 }
 
-// The opt-in to more than 48 KB of dynamic shared memory is an attribute of the kernel ON ONE DEVICE, so it is
-// remembered per device ordinal (one bit each); the attribute call itself allocates nothing and may be repeated.
-struct SmemOptIn {
-  std::atomic<uint64_t> done{0};
-};
 template <typename K>
 cudaError_t ensure_smem(K kernel, int bytes, SmemOptIn* st) {
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  const uint64_t bit = 1ull << (dev & 63);
-  if (st->done.load(std::memory_order_acquire) & bit) return cudaSuccess;
-  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) st->done.fetch_or(bit, std::memory_order_release);
-  return e;
+  return st->ensure(kernel, bytes);
 }
 
 PagedKV make_kv(const AttnKV& kv) {

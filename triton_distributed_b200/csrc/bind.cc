@@ -118,8 +118,27 @@ bool pick_cta_pair(int64_t rows, int64_t N, int block_n, bool tma_store_ok) {
 
 int sm_count() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
 
+// Half-width tail tiles of the pair kernel (TDB200_SPLIT_TAIL=0 turns them off).
+bool split_tail_enabled() {
+  static const bool enabled = [] {
+    const char* e = std::getenv("TDB200_SPLIT_TAIL");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  return enabled;
+}
+
+// Optional stall-counter buffer: int64 [num_ctas, 8], zeroed by the caller.
+void* stats_ptr(const c10::optional<at::Tensor>& stats, int num_ctas) {
+  if (!stats.has_value()) return nullptr;
+  TORCH_CHECK(stats->is_cuda() && stats->scalar_type() == at::kLong && stats->is_contiguous() &&
+                  stats->numel() >= static_cast<int64_t>(num_ctas) * 8,
+              "stats: contiguous int64 CUDA tensor of at least num_ctas * 8 elements expected");
+  return stats->data_ptr();
+}
+
 // C[M,N] = A[M,K] @ B[N,K]^T   (bf16)
-void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int block_n, int num_ctas) {
+void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int block_n, int num_ctas,
+               const c10::optional<at::Tensor>& stats) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && c.is_cuda(), "gemm: CUDA tensors expected");
   TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && c.scalar_type() == at::kBFloat16,
               "gemm: bf16 expected");
@@ -149,6 +168,11 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int bloc
   const int tile_m = g.cta_pair ? 256 : 128;
   const int tiles = ((M + tile_m - 1) / tile_m) * ((N + g.block_n - 1) / g.block_n) * (g.cta_pair ? 2 : 1);
   g.num_ctas = std::min<int>(num_ctas > 0 ? num_ctas : sm_count(), tiles);
+  if (g.cta_pair && split_tail_enabled()) {
+    g.tmap_b_half = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, 64, 64);
+    g.split_tail = 1;
+  }
+  g.stats = stats_ptr(stats, g.num_ctas);
   g.symm.world = 1;
   g.symm.timeout_ns = 2000000000ull;
   check_cuda(tdb::launch_gemm(g, cur_stream()), "launch_gemm");
@@ -158,7 +182,8 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int bloc
 // ws / flags / ctx live in the symmetric heap (ws, flags) and in device memory (ctx).
 void ag_gemm_bf16(SymmHeap& h, const at::Tensor& a_local, const at::Tensor& b, at::Tensor& c, at::Tensor& ws,
                   at::Tensor& flags, at::Tensor& ctx, int64_t max_seg_rows, int64_t max_chunks, int n_comm,
-                  int block_n, int num_ctas, bool use_multimem, double timeout_s) {
+                  int block_n, int num_ctas, bool use_multimem, double timeout_s,
+                  const c10::optional<at::Tensor>& stats) {
   TORCH_CHECK(a_local.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "ag_gemm: bf16 expected");
   TORCH_CHECK(a_local.is_contiguous() && b.stride(1) == 1 && c.stride(1) == 1, "ag_gemm: contiguous inputs expected");
   const int W = h.world();
@@ -197,13 +222,18 @@ void ag_gemm_bf16(SymmHeap& h, const at::Tensor& a_local, const at::Tensor& b, a
   g.ctx = reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr());
   g.symm = h.info(static_cast<uint64_t>(timeout_s * 1e9));
   g.use_multimem = use_multimem ? 1 : 0;
+  if (g.cta_pair && split_tail_enabled()) {
+    g.tmap_b_half = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, 64, 64);
+    g.split_tail = 1;
+  }
+  g.stats = stats_ptr(stats, g.num_ctas);
   check_cuda(tdb::launch_gemm(g, cur_stream()), "launch_gemm(all-gather)");
 }
 
 // Fused GEMM + reduce-scatter.  a [M, K_local]; b [N, K_local]; out [M/W, N].
 void gemm_rs_bf16(SymmHeap& h, const at::Tensor& a, const at::Tensor& b, at::Tensor& out, at::Tensor& slots,
                   at::Tensor& flags, at::Tensor& ctx, int64_t max_seg_rows, int64_t max_tiles, int block_n,
-                  int num_ctas, double timeout_s) {
+                  int num_ctas, double timeout_s, const c10::optional<at::Tensor>& stats) {
   TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_rs: bf16 expected");
   TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1, "gemm_rs: contiguous inputs expected");
   const int W = h.world();
@@ -246,6 +276,11 @@ void gemm_rs_bf16(SymmHeap& h, const at::Tensor& a, const at::Tensor& b, at::Ten
   g.ld_out = out.stride(0);
   g.ctx = reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr());
   g.symm = h.info(static_cast<uint64_t>(timeout_s * 1e9));
+  if (g.cta_pair && split_tail_enabled()) {
+    g.tmap_b_half = make_tmap3(b.data_ptr(), tdb::kBF16, 1, N, K, b.stride(0) * 2, b.stride(0) * 2 * N, 64, 64);
+    g.split_tail = 1;
+  }
+  g.stats = stats_ptr(stats, g.num_ctas);
   check_cuda(tdb::launch_gemm(g, cur_stream()), "launch_gemm(reduce-scatter)");
 }
 
@@ -444,9 +479,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
 
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("block_n") = 0,
-        py::arg("num_ctas") = 0);
-  m.def("ag_gemm_bf16", &ag_gemm_bf16);
-  m.def("gemm_rs_bf16", &gemm_rs_bf16);
+        py::arg("num_ctas") = 0, py::arg("stats") = py::none());
+  m.def("ag_gemm_bf16", &ag_gemm_bf16, py::arg("heap"), py::arg("a_local"), py::arg("b"), py::arg("c"), py::arg("ws"),
+        py::arg("flags"), py::arg("ctx"), py::arg("max_seg_rows"), py::arg("max_chunks"), py::arg("n_comm"),
+        py::arg("block_n"), py::arg("num_ctas"), py::arg("use_multimem"), py::arg("timeout_s"),
+        py::arg("stats") = py::none());
+  m.def("gemm_rs_bf16", &gemm_rs_bf16, py::arg("heap"), py::arg("a"), py::arg("b"), py::arg("out"), py::arg("slots"),
+        py::arg("flags"), py::arg("ctx"), py::arg("max_seg_rows"), py::arg("max_tiles"), py::arg("block_n"),
+        py::arg("num_ctas"), py::arg("timeout_s"), py::arg("stats") = py::none());
   m.def("gemm_smem_bytes", &tdb::gemm_smem_bytes);
   m.def("skinny_gemm_bf16", &skinny_gemm_bf16);
   m.def("gemm_ar_bf16", &gemm_ar_bf16);

@@ -33,6 +33,7 @@
 #include <cuda.h>
 
 #include "tdb/api.h"
+#include "tdb/launch.cuh"
 #include "tdb/symm_device.cuh"
 
 namespace tdb {
@@ -46,7 +47,18 @@ constexpr int kThreads = 192;
 constexpr int kGroupM = 8;
 constexpr int kEpiCols = 64;      // columns per epilogue staging buffer (128-byte rows)
 constexpr int kEpiBytes = kBM * kEpiCols * 2;
-constexpr uint64_t kMbarTimeoutNs = 4000000000ull;  // 4 s
+// Slots of the optional per-CTA stall counters (KParams::stats, SM clock cycles).
+enum StatSlot : int {
+  kStatProdFlagWait = 0,   // producer: all-gather chunk flags
+  kStatProdEmptyWait = 1,  // producer: ring slots held by the tensor core
+  kStatMmaFullWait = 2,    // MMA issuer: operands not yet in shared memory
+  kStatMmaTmemWait = 3,    // MMA issuer: accumulator buffer still owned by the epilogue
+  kStatEpiTmemWait = 4,    // epilogue: accumulator not finished
+  kStatEpiFlagWait = 5,    // epilogue: partial tiles of the other ranks (reduce-scatter, own segment)
+  kStatEpiStoreWait = 6,   // epilogue: TMA stores in flight (staging reuse / completion before a flag)
+  kStatTotal = 7,          // CTA lifetime
+  kStatSlots = 8,
+};
 
 template <int BN>
 struct SmemLayout {
@@ -98,7 +110,26 @@ struct KParams {
   const int32_t* tile_expert;   // grouped GEMM: expert (third coordinate of B) of every M tile, < 0 = skip the tile
   CtxDev* ctx;
   SymmInfo symm;
+  uint64_t mbar_timeout_ns;     // limit of every shared-memory barrier wait
+  int split_tail;               // pair kernel: tiles of an incomplete last wave are computed as two 128-column halves
+  unsigned long long* stats;    // optional [grid][kStatSlots] stall counters (cycles), null = off
 };
+
+// Accumulates the cycles spent between construction and stop() into a stall counter (no-op when stats are off).
+struct StallTimer {
+  long long t0;
+  bool on;
+  TDB_DEVICE explicit StallTimer(const KParams& p) : t0(0), on(p.stats != nullptr) {
+    if (on) t0 = clock64();
+  }
+  TDB_DEVICE void stop(long long& acc) {
+    if (on) acc += clock64() - t0;
+  }
+};
+TDB_DEVICE void stat_flush(const KParams& p, int slot, long long v) {
+  if (p.stats != nullptr && v != 0)
+    atomicAdd(p.stats + static_cast<uint64_t>(blockIdx.x) * kStatSlots + slot, static_cast<unsigned long long>(v));
+}
 
 struct Tile {
   int seg, mt, nt, m0, n0, m_end;
@@ -233,7 +264,7 @@ __device__ void ag_push_bulk(const KParams& p, uint32_t epoch, uint8_t* smem) {
     if (step >= kPushAhead) {
       // ---- store piece `st_i`
       const int slot = st_i % kPushSlots;
-      if (!mbar_wait(&bars[slot], (st_i / kPushSlots) & 1, nullptr, kMbarTimeoutNs)) {
+      if (!mbar_wait(&bars[slot], (st_i / kPushSlots) & 1, nullptr, p.mbar_timeout_ns)) {
         report(p.symm, kTimeoutMbarrier, kKernelAgGemm, 40, -1, slot, 0, static_cast<int>(st_i));
         ok = false;
         break;
@@ -415,7 +446,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int kb = 0; kb < num_kb; ++kb, ++it) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1;
-            if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kMbarTimeoutNs)) {
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.mbar_timeout_ns)) {
               ok = false;
               report(p.symm, kTimeoutMbarrier, kKernelGemm, 10, -1, s, (int)ph, t);
               break;
@@ -455,7 +486,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const int b = local & 1;
           const uint32_t aph = (local >> 1) & 1;
           ++local;
-          if (!mbar_wait(&tmem_empty[b], aph ^ 1, abort_flag, kMbarTimeoutNs)) {
+          if (!mbar_wait(&tmem_empty[b], aph ^ 1, abort_flag, p.mbar_timeout_ns)) {
             ok = false;
             report(p.symm, kTimeoutMbarrier, kKernelGemm, 20, -1, b, (int)aph, t);
             break;
@@ -465,7 +496,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int kb = 0; kb < num_kb; ++kb, ++it) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1;
-            if (!mbar_wait(&full_bar[s], ph, abort_flag, kMbarTimeoutNs)) {
+            if (!mbar_wait(&full_bar[s], ph, abort_flag, p.mbar_timeout_ns)) {
               ok = false;
               report(p.symm, kTimeoutMbarrier, kKernelGemm, 21, -1, s, (int)ph, t);
               break;
@@ -500,7 +531,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int b = local & 1;
         const uint32_t aph = (local >> 1) & 1;
         ++local;
-        if (!mbar_wait(&tmem_full[b], aph, abort_flag, kMbarTimeoutNs)) {
+        if (!mbar_wait(&tmem_full[b], aph, abort_flag, p.mbar_timeout_ns)) {
           ok = false;
           if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemm, 30, -1, b, (int)aph, t);
           break;
@@ -667,23 +698,47 @@ struct PairLayout {
 };
 constexpr int kPairBN = 256;
 
-// tile order of the pair kernel: like decode_tile, with M tiles of 256 rows; r.mt is the pair-row index
-__device__ __forceinline__ Tile decode_tile_pair(const KParams& p, int t, int tiles_m_pair) {
-  Tile r;
-  const int per_seg = tiles_m_pair * p.tiles_n;
+// Work items of the pair kernel.  Items [0, full_items) are 256 x 256 tiles in the order of decode_tile (M tiles of
+// 256 rows; r.mt is the pair-row index).  When the tile count leaves an incomplete last wave of at most half the
+// pairs, each tile of that wave is computed as two 256 x 128 halves by two pairs (items full_items + 2 j + h), so
+// the tail costs half a tile time instead of a whole one.  r.bn is the item's width in columns, 0 for a half that
+// lies beyond N.
+struct PairSched {
+  int tiles_m_pair, full_items, total_items;
+};
+__device__ __forceinline__ PairSched make_pair_sched(const KParams& p, int n_pairs) {
+  PairSched s;
+  s.tiles_m_pair = (p.tiles_m_seg + 1) / 2;
+  const int num_tiles = p.num_seg * s.tiles_m_pair * p.tiles_n;
+  const int rem = num_tiles % n_pairs;
+  const bool split = p.split_tail != 0 && rem > 0 && 2 * rem <= n_pairs;
+  s.full_items = split ? num_tiles - rem : num_tiles;
+  s.total_items = s.full_items + (split ? 2 * rem : 0);
+  return s;
+}
+struct PairTile {
+  int seg, mt, nt, n0, bn;
+};
+__device__ __forceinline__ PairTile decode_pair_item(const KParams& p, const PairSched& sc, int w) {
+  int t = w, half = -1;
+  if (w >= sc.full_items) {
+    t = sc.full_items + ((w - sc.full_items) >> 1);
+    half = (w - sc.full_items) & 1;
+  }
+  PairTile r;
+  const int per_seg = sc.tiles_m_pair * p.tiles_n;
   const int si = t / per_seg;
   const int rem = t - si * per_seg;
   r.seg = (p.seg_first + si) % p.num_seg;
   const int group_sz = kGroupM * p.tiles_n;
   const int g = rem / group_sz;
   const int first_m = g * kGroupM;
-  const int gm = min(tiles_m_pair - first_m, kGroupM);
+  const int gm = min(sc.tiles_m_pair - first_m, kGroupM);
   const int in_g = rem - g * group_sz;
   r.mt = first_m + in_g % gm;
   r.nt = in_g / gm;
-  r.m0 = r.seg * p.seg_rows + r.mt * 2 * kBM;
-  r.n0 = r.nt * kPairBN;
-  r.m_end = min(p.M, (r.seg + 1) * p.seg_rows);
+  r.n0 = r.nt * kPairBN + (half > 0 ? 128 : 0);
+  r.bn = half < 0 ? kPairBN : (r.n0 < p.N ? 128 : 0);
   return r;
 }
 
@@ -691,7 +746,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ PeerMaps peer_maps,
                  const __grid_constant__ CUtensorMap tmap_a_local, const __grid_constant__ CUtensorMap tmap_out,
-                 const KParams p) {
+                 const __grid_constant__ CUtensorMap tmap_b_half, const KParams p) {
   using L = PairLayout;
   constexpr int kStages = L::kStages;
   constexpr int BN = kPairBN;
@@ -709,6 +764,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t cr = cluster_ctarank();
   const uint32_t epoch = (p.ctx != nullptr) ? ld_volatile(&p.ctx->epoch) : 1u;
   const int buf = epoch & 1;
+  const long long cta_t0 = p.stats != nullptr ? clock64() : 0;
 
   // n_comm is even, so both CTAs of a pair take the same role
   const bool is_comm = (p.mode == kGemmAllGather) && (static_cast<int>(blockIdx.x) < p.n_comm);
@@ -732,6 +788,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       fence_mbar_init();
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_b);
+      if (p.split_tail) tma_prefetch_desc(&tmap_b_half);
       if (p.mode == kGemmAllGather) tma_prefetch_desc(&tmap_a_local);
       if (p.mode != kGemmReduceScatter) tma_prefetch_desc(&tmap_c);
     }
@@ -747,47 +804,64 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
     const int n_pairs = (gridDim.x - p.n_comm) / 2;
     const int pair_idx = (blockIdx.x - p.n_comm) / 2;
-    const int tiles_m_pair = (p.tiles_m_seg + 1) / 2;
-    const int num_tiles = p.num_seg * tiles_m_pair * p.tiles_n;
+    const PairSched sched = make_pair_sched(p, n_pairs);
     const int num_kb = (p.K + kBK - 1) / kBK;
+    const int tiles_n128 = (p.N + 127) / 128;   // reduce-scatter flags are kept per 128 x 128 unit
 
     if (warp == 0) {
       // ------------------------------------------------------------ TMA producer (both CTAs, own operand halves)
       if (lane == 0) {
         uint32_t it = 0;
         bool ok = true;
-        for (int t = pair_idx; t < num_tiles && ok; t += n_pairs) {
-          const Tile tl = decode_tile_pair(p, t, tiles_m_pair);
+        long long w_flag = 0, w_empty = 0;
+        for (int w = pair_idx; w < sched.total_items && ok; w += n_pairs) {
+          const PairTile tl = decode_pair_item(p, sched, w);
+          if (tl.bn == 0) continue;
           const int mt = 2 * tl.mt + static_cast<int>(cr);     // this CTA's 128-row chunk of the segment
           const bool valid_m = mt < p.tiles_m_seg;
           const bool local_seg = (p.mode == kGemmAllGather) && tl.seg == p.symm.rank;
           if (p.mode == kGemmAllGather && !local_seg && valid_m) {
+            StallTimer st(p);
             const uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * p.symm.world + tl.seg) * p.max_chunks + mt;
             ok = wait_until(p.symm, flag, epoch, kCmpGe, kKernelAgGemm, 1, tl.seg, mt);
+            st.stop(w_flag);
             if (!ok) break;
             fence_proxy_async();
           }
+          const bool half = tl.bn != BN;
+          const uint32_t tx = 2u * (L::kABytes + (half ? L::kBBytes / 2 : L::kBBytes));
           for (int kb = 0; kb < num_kb; ++kb, ++it) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1;
-            if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kMbarTimeoutNs)) {
-              ok = false;
-              report(p.symm, kTimeoutMbarrier, kKernelGemm, 110, -1, s, (int)ph, t);
-              break;
+            if (!mbar_try_wait(&empty_bar[s], ph ^ 1)) {
+              StallTimer st(p);
+              const bool got = mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.mbar_timeout_ns);
+              st.stop(w_empty);
+              if (!got) {
+                ok = false;
+                report(p.symm, kTimeoutMbarrier, kKernelGemm, 110, -1, s, (int)ph, w);
+                break;
+              }
             }
             uint8_t* sa = smem + s * L::kStageBytes;
             uint8_t* sb = sa + L::kABytes;
             const uint32_t full0 = mapa_u32(smem_u32(&full_bar[s]), 0);
-            if (cr == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * L::kStageBytes);
+            if (cr == 0) mbar_arrive_expect_tx(&full_bar[s], tx);
             if (local_seg) {
               tma_load_3d_pair(sa, &tmap_a_local, full0, kb * kBK, mt * kBM, 0);
             } else {
               tma_load_3d_pair(sa, &tmap_a, full0, kb * kBK, tl.seg * p.seg_rows + mt * kBM,
                                (p.mode == kGemmAllGather) ? buf : 0);
             }
-            tma_load_3d_pair(sb, &tmap_b, full0, kb * kBK, tl.n0 + static_cast<int>(cr) * 128, 0);
+            if (half) {
+              tma_load_3d_pair(sb, &tmap_b_half, full0, kb * kBK, tl.n0 + static_cast<int>(cr) * 64, 0);
+            } else {
+              tma_load_3d_pair(sb, &tmap_b, full0, kb * kBK, tl.n0 + static_cast<int>(cr) * 128, 0);
+            }
           }
         }
+        stat_flush(p, kStatProdFlagWait, w_flag);
+        stat_flush(p, kStatProdEmptyWait, w_empty);
         if (!ok) {
           *abort_flag = 1;
           // loads already issued land within microseconds; give them time before the CTA may leave
@@ -798,28 +872,43 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else if (warp == 1) {
       // ------------------------------------------------------------ MMA issuer (CTA 0 of the pair only)
       if (lane == 0 && cr == 0) {
-        constexpr uint32_t idesc = make_idesc(1u, 2 * kBM, BN);
+        constexpr uint32_t idesc_full = make_idesc(1u, 2 * kBM, BN);
+        constexpr uint32_t idesc_half = make_idesc(1u, 2 * kBM, 128);
         uint32_t it = 0;
         int local = 0;
         bool ok = true;
-        for (int t = pair_idx; t < num_tiles && ok; t += n_pairs) {
+        long long w_full = 0, w_tmem = 0;
+        for (int w = pair_idx; w < sched.total_items && ok; w += n_pairs) {
+          const PairTile tl = decode_pair_item(p, sched, w);
+          if (tl.bn == 0) continue;
+          const uint32_t idesc = tl.bn == BN ? idesc_full : idesc_half;
           const int b = local & 1;
           const uint32_t aph = (local >> 1) & 1;
           ++local;
-          if (!mbar_wait(&tmem_empty[b], aph ^ 1, abort_flag, kMbarTimeoutNs)) {
-            ok = false;
-            report(p.symm, kTimeoutMbarrier, kKernelGemm, 120, -1, b, (int)aph, t);
-            break;
+          if (!mbar_try_wait(&tmem_empty[b], aph ^ 1)) {
+            StallTimer st(p);
+            const bool got = mbar_wait(&tmem_empty[b], aph ^ 1, abort_flag, p.mbar_timeout_ns);
+            st.stop(w_tmem);
+            if (!got) {
+              ok = false;
+              report(p.symm, kTimeoutMbarrier, kKernelGemm, 120, -1, b, (int)aph, w);
+              break;
+            }
           }
           tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + b * BN;
           for (int kb = 0; kb < num_kb; ++kb, ++it) {
             const int s = it % kStages;
             const uint32_t ph = (it / kStages) & 1;
-            if (!mbar_wait(&full_bar[s], ph, abort_flag, kMbarTimeoutNs)) {
-              ok = false;
-              report(p.symm, kTimeoutMbarrier, kKernelGemm, 121, -1, s, (int)ph, t);
-              break;
+            if (!mbar_try_wait(&full_bar[s], ph)) {
+              StallTimer st(p);
+              const bool got = mbar_wait(&full_bar[s], ph, abort_flag, p.mbar_timeout_ns);
+              st.stop(w_full);
+              if (!got) {
+                ok = false;
+                report(p.symm, kTimeoutMbarrier, kKernelGemm, 121, -1, s, (int)ph, w);
+                break;
+              }
             }
             tc_fence_after_sync();
             const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
@@ -838,6 +927,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             umma_commit_pair(mapa_u32(f, 1));
           }
         }
+        stat_flush(p, kStatMmaFullWait, w_full);
+        stat_flush(p, kStatMmaTmemWait, w_tmem);
         if (!ok) *abort_flag = 1;
       }
     } else {
@@ -849,17 +940,25 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t chunk_ctr = 0;
       int local = 0;
       bool ok = true;
-      for (int t = pair_idx; t < num_tiles && ok; t += n_pairs) {
-        const Tile tl = decode_tile_pair(p, t, tiles_m_pair);
+      long long w_tmem = 0, w_flag = 0, w_store = 0;
+      for (int w = pair_idx; w < sched.total_items && ok; w += n_pairs) {
+        const PairTile tl = decode_pair_item(p, sched, w);
+        if (tl.bn == 0) continue;
+        const int n_chunks = tl.bn / kEpiCols;
         const int mt = 2 * tl.mt + static_cast<int>(cr);
         const bool valid_m = mt < p.tiles_m_seg;
         const int b = local & 1;
         const uint32_t aph = (local >> 1) & 1;
         ++local;
-        if (!mbar_wait(&tmem_full[b], aph, abort_flag, kMbarTimeoutNs)) {
-          ok = false;
-          if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemm, 130, -1, b, (int)aph, t);
-          break;
+        {
+          StallTimer st(p);
+          const bool got = mbar_wait(&tmem_full[b], aph, abort_flag, p.mbar_timeout_ns);
+          if (leader) st.stop(w_tmem);
+          if (!got) {
+            ok = false;
+            if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemm, 130, -1, b, (int)aph, w);
+            break;
+          }
         }
         tc_fence_after_sync();
         const uint32_t t_acc = tmem_base + b * BN + (static_cast<uint32_t>(q * 32) << 16);
@@ -869,13 +968,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const bool own_seg = (p.mode == kGemmReduceScatter) && tl.seg == p.symm.rank;
         const CUtensorMap* cmap = own_seg ? &tmap_out : (p.mode == kGemmReduceScatter) ? &peer_maps.m[tl.seg] : &tmap_c;
         const int c2 = own_seg ? 0 : (p.mode == kGemmReduceScatter) ? (buf * p.symm.world + p.symm.rank) : tl.seg;
+        // flags of the 128-column units this item covers
+        const int unit0 = mt * tiles_n128 + tl.n0 / 128;
+        const int n_units = min(tl.bn / 128, tiles_n128 - tl.n0 / 128);
         if (own_seg && valid_m) {
           const int et = threadIdx.x - 64;
           bool wok = true;
           if (et < p.symm.world && et != p.symm.rank) {
-            const uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + et) * p.max_tiles +
-                                   mt * p.tiles_n + tl.nt;
-            wok = wait_until(p.symm, flag, epoch, kCmpGe, kKernelGemmRs, 3, et, mt * p.tiles_n + tl.nt);
+            StallTimer st(p);
+            const uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + et) * p.max_tiles + unit0;
+            for (int u = 0; u < n_units && wok; ++u)
+              wok = wait_until(p.symm, flag + u, epoch, kCmpGe, kKernelGemmRs, 3, et, unit0 + u);
+            st.stop(w_flag);
           }
           if (!wok) *abort_flag = 1;
           epi_bar();
@@ -887,12 +991,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int seg_row = mt * kBM + row_in_tile;
         const bool row_ok = valid_m && seg_row < p.seg_rows;
 #pragma unroll 1
-        for (int c = 0; c < BN / kEpiCols; ++c, ++chunk_ctr) {
+        for (int c = 0; c < n_chunks; ++c, ++chunk_ctr) {
           uint32_t r0[32], r1[32];
           tmem_ld_32x32(t_acc + c * kEpiCols, r0);
           tmem_ld_32x32(t_acc + c * kEpiCols + 32, r1);
           tmem_ld_wait();
-          if (c == BN / kEpiCols - 1) {
+          if (c == n_chunks - 1) {
             tc_fence_before_sync();
             mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty[b]), 0));
           }
@@ -937,7 +1041,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           uint8_t* stg = stage_base + (chunk_ctr & 1) * kEpiBytes;
-          if (leader) bulk_wait_read<1>();
+          if (leader) {
+            StallTimer st(p);
+            bulk_wait_read<1>();
+            st.stop(w_store);
+          }
           epi_bar();
           uint8_t* srow = stg + row_in_tile * 128;
           const int sw = row_in_tile & 7;
@@ -967,14 +1075,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
         if (p.mode == kGemmReduceScatter && !own_seg && leader && valid_m) {
+          StallTimer st(p);
           bulk_wait<0>();
+          st.stop(w_store);
           fence_proxy_async();
           fence_acq_rel_sys();
-          uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.max_tiles +
-                           mt * p.tiles_n + tl.nt;
-          st_release_sys(symm_at(p.symm, flag, tl.seg), epoch);
+          uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.max_tiles + unit0;
+          uint32_t* dst = symm_at(p.symm, flag, tl.seg);
+          for (int u = 0; u < n_units; ++u) st_release_sys(dst + u, epoch);
         }
       }
+      if (leader) {
+        stat_flush(p, kStatEpiTmemWait, w_tmem);
+        stat_flush(p, kStatEpiStoreWait, w_store);
+      }
+      stat_flush(p, kStatEpiFlagWait, w_flag);
       if (!ok) *abort_flag = 1;
       if (leader) bulk_wait<0>();
     }
@@ -988,6 +1103,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tmem_dealloc_pair(tmem_base, 2 * BN);
     }
   }
+  if (threadIdx.x == 0 && p.stats != nullptr) stat_flush(p, kStatTotal, clock64() - cta_t0);
 
   if (p.ctx != nullptr) {
     __syncthreads();
@@ -1034,8 +1150,15 @@ cudaError_t fill_params(const GemmArgs& a, int BN, KParams& p) {
   p.ctx = a.ctx;
   static_assert(sizeof(SymmInfo) == sizeof(SymmInfoHost), "SymmInfo mirrors must match");
   memcpy(&p.symm, &a.symm, sizeof(SymmInfo));
+  // shared-memory barriers complete within microseconds when everything works; their limit follows the configured
+  // wait limit (a flag wait of a producer can legitimately hold a consumer's barrier for that long)
+  p.mbar_timeout_ns = a.symm.timeout_ns > 0 ? a.symm.timeout_ns : 4000000000ull;
+  p.split_tail = a.split_tail;
+  p.stats = reinterpret_cast<unsigned long long*>(a.stats);
   if (a.mode == kGemmAllGather && p.tiles_m_seg > a.max_chunks) return cudaErrorInvalidValue;
-  if (a.mode == kGemmReduceScatter && p.tiles_m_seg * p.tiles_n > a.max_tiles) return cudaErrorInvalidValue;
+  // the pair kernel keeps reduce-scatter flags per 128 x 128 unit, the single-CTA kernel per tile
+  const int rs_flag_units = a.cta_pair ? p.tiles_m_seg * ((a.N + 127) / 128) : p.tiles_m_seg * p.tiles_n;
+  if (a.mode == kGemmReduceScatter && rs_flag_units > a.max_tiles) return cudaErrorInvalidValue;
   if (a.mode == kGemmAllGather && (a.n_comm_ctas < 1 || a.n_comm_ctas >= a.num_ctas)) return cudaErrorInvalidValue;
   if (a.K % 8 != 0) return cudaErrorInvalidValue;
   return cudaSuccess;
@@ -1046,11 +1169,10 @@ cudaError_t launch_impl(const GemmArgs& a, cudaStream_t stream) {
   using L = SmemLayout<BN>;
   static_assert(kPushSlots * kPushPiece + kPushSlots * 8 <= L::kTotal, "push ring must fit the GEMM's shared memory");
   const int smem = L::kTotal + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  {
+    static SmemOptIn opt_in;
+    cudaError_t e = opt_in.ensure(gemm_kernel<BN>, smem);
     if (e != cudaSuccess) return e;
-    attr_set = true;
   }
   KParams p;
   cudaError_t e = fill_params(a, BN, p);
@@ -1073,11 +1195,10 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   static_assert(kPushSlots * kPushPiece + kPushSlots * 8 <= L::kTotal, "push ring must fit the GEMM's shared memory");
   static_assert(L::kTotal + 1024 <= 227 * 1024, "pair kernel exceeds the shared memory of an SM");
   const int smem = L::kTotal + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  {
+    static SmemOptIn opt_in;
+    cudaError_t e = opt_in.ensure(gemm_pair_kernel, smem);
     if (e != cudaSuccess) return e;
-    attr_set = true;
   }
   if (!a.use_tma_store || a.tile_expert != nullptr) return cudaErrorInvalidValue;
   KParams p;
@@ -1093,9 +1214,10 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   memcpy(&tc, a.tmap_c.bytes, sizeof(CUtensorMap));
   PeerMaps pm;
   memcpy(&pm, a.tmap_peer_c, sizeof(PeerMaps));
-  CUtensorMap to;
+  CUtensorMap to, tbh;
   memcpy(&to, a.tmap_out.bytes, sizeof(CUtensorMap));
-  gemm_pair_kernel<<<grid, kThreads, smem, stream>>>(ta, tb, tc, pm, tl, to, p);
+  memcpy(&tbh, a.tmap_b_half.bytes, sizeof(CUtensorMap));
+  gemm_pair_kernel<<<grid, kThreads, smem, stream>>>(ta, tb, tc, pm, tl, to, tbh, p);
   return cudaGetLastError();
 }
 

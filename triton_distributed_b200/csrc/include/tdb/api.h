@@ -68,6 +68,9 @@ struct GemmArgs {
   TensorMap tmap_a_local;   // all-gather: the local shard [seg_rows, K], read in place
   TensorMap tmap_peer_c[kMaxRanksHost];
   TensorMap tmap_out;       // reduce-scatter with the pair kernel: the output [1][seg_rows][N], box [128 x 64]
+  TensorMap tmap_b_half;    // pair kernel with split_tail: B with a 64-row box (half-width tail tiles)
+  int split_tail;           // pair kernel: compute an incomplete last wave as 256 x 128 half tiles
+  void* stats;              // optional device buffer [num_ctas][8] of uint64 stall counters (cycles), null = off
   int use_tma_store;
   int block_n;      // 128 or 256
   int cta_pair;     // 1: CTA-pair kernel (256 x 256 tiles over two SMs); tmap_b then has a 128-row box

@@ -2,9 +2,27 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdlib>
 
 namespace tdb {
+
+// The opt-in to more than 48 KB of dynamic shared memory is an attribute of a kernel ON ONE DEVICE.  One object per
+// kernel remembers, one bit per device ordinal, where it has been set; safe to call from several host threads.
+struct SmemOptIn {
+  std::atomic<unsigned long long> done{0};
+  template <typename K>
+  cudaError_t ensure(K kernel, int bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+    return e;
+  }
+};
 
 // Launch with the programmatic-dependent-launch attribute: the kernel may be scheduled while its predecessor in the
 // stream drains, and must execute griddepcontrol.wait (pdl_wait) before touching anything the predecessor writes.

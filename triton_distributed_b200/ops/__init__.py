@@ -1,5 +1,6 @@
 """Overlapped ops, collectives and single-GPU kernels (the reference's ``triton_dist.kernels.nvidia``)."""
-from .gemm import gemm, linear, gemm_reference  # noqa: F401
+from .gemm import (gemm, linear, gemm_reference, new_stall_counters, summarize_stall_counters,  # noqa: F401
+                   STALL_COUNTERS)
 from .ag_gemm import (AllGatherGEMMTensorParallelContext, create_ag_gemm_context, ag_gemm,  # noqa: F401
                       ag_gemm_reference)
 from .gemm_rs import (GEMMReduceScatterTensorParallelContext, create_gemm_rs_context, gemm_rs,  # noqa: F401

@@ -45,6 +45,7 @@ class AllGatherGEMMTensorParallelContext:
     ctx_dev: Optional[torch.Tensor] = None
     max_chunks: int = 0
     calls: int = 0
+    stats: Optional[torch.Tensor] = None       # optional int64 [num_ctas, 8] stall counters filled by the pair kernel
 
     @property
     def max_seg_rows(self) -> int:
@@ -96,19 +97,47 @@ def create_ag_gemm_context(tensor_A: Optional[torch.Tensor] = None, tensor_B: Op
     return ctx
 
 
-def pick_comm_ctas(rows_per_rank: int, n_local: int, world: int, block_n: int, n_sms: int, pair: bool = False) -> int:
-    """Comm CTAs of the fused launch: at least enough push bandwidth for the remote shards to stay ahead of the GEMM
-    (about 45 GB/s per bulk-TMA CTA; a segment of the GEMM consumes its shard in 1/world of the GEMM time), and every
-    SM that the tile count leaves idle in the last wave anyway.  With the CTA-pair kernel the work units are 256 x 256
-    tiles on SM pairs and the count is even."""
-    n_min = 4 if world <= 2 else 8
+PUSH_GBS_PER_CTA = 45.0     # measured: one bulk-TMA comm CTA moves about 45 GB/s (local memory -> shared -> peer)
+LINK_GBS = 770.0            # measured peer-copy bandwidth per direction
+PAIR_TILE_TFLOPS = 20.5     # measured: one CTA pair sustains about 20.5 TFLOP/s on 256 x 256 tiles
+
+
+def pair_wave_time(tiles: int, pairs: int) -> float:
+    """Duration of a pair-kernel GEMM in tile times: full waves, and an incomplete last wave that costs half a tile
+    when it occupies at most half the pairs (its tiles are then computed as two 128-column halves)."""
+    full, rem = divmod(tiles, pairs)
+    if rem == 0:
+        return float(full)
+    return full + (0.5 if 2 * rem <= pairs else 1.0)
+
+
+def pick_comm_ctas(rows_per_rank: int, n_local: int, world: int, block_n: int, n_sms: int, pair: bool = False,
+                   k: int = 8192) -> int:
+    """Comm CTAs of the fused launch.  Every comm CTA is an SM the GEMM does not get, so the count is the smallest
+    one whose push bandwidth keeps the remote shards ahead of the GEMM (rank distance d's shard is needed after d
+    segments of GEMM time), unless taking more SMs away does not lengthen the GEMM's wave count anyway.  With the
+    CTA-pair kernel the work units are 256 x 256 tiles on SM pairs and the count is even."""
+    n_floor = 2 if world <= 2 else 4
     if pair:
-        tiles = world * ((rows_per_rank + 2 * BLOCK_M - 1) // (2 * BLOCK_M)) * ((n_local + 255) // 256)
-        units = (n_sms - n_min) // 2
-        waves = max(1, -(-tiles // units))
-        n_gemm = 2 * -(-tiles // waves)
-        n = max(n_min, min(32, n_sms - n_gemm))
-        return int(n - (n & 1))
+        tiles_seg = ((rows_per_rank + 2 * BLOCK_M - 1) // (2 * BLOCK_M)) * ((n_local + 255) // 256)
+        tiles = world * tiles_seg
+        tile_us = 2.0 * 256 * 256 * k / (PAIR_TILE_TFLOPS * 1e6)
+        shard_mb = rows_per_rank * k * 2 / 1e6
+        best, best_t = n_floor, None
+        for n in range(n_floor, 34, 2):
+            pairs = (n_sms - n) // 2
+            if pairs < 1:
+                break
+            gemm_us = pair_wave_time(tiles, pairs) * tile_us
+            seg_us = gemm_us / world
+            push_gbs = min(n * PUSH_GBS_PER_CTA, LINK_GBS)
+            # shard d (d = 1 .. world-1) has arrived after d * shard / rate and is needed after d * seg_us
+            stall_us = max(0.0, (world - 1) * (shard_mb * 1e3 / push_gbs - seg_us)) if world > 1 else 0.0
+            t = gemm_us + stall_us
+            if best_t is None or t < best_t - 1e-9:
+                best, best_t = n, t
+        return int(best)
+    n_min = 4 if world <= 2 else 8
     tiles = world * ((rows_per_rank + BLOCK_M - 1) // BLOCK_M) * ((n_local + block_n - 1) // block_n)
     waves = max(1, -(-tiles // (n_sms - n_min)))
     n_gemm = -(-tiles // waves)
@@ -153,11 +182,12 @@ def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelCo
         out = torch.empty((m * W, N), dtype=a.dtype, device=a.device)
     n_sms = ctx.num_ctas or sm_count(a.device)
     pair = use_cta_pair(ctx.kernel_form, m, N, out)
-    n_comm = ctx.n_comm_ctas or pick_comm_ctas(m, N, W, ctx.BLOCK_N, n_sms, pair)
+    n_comm = ctx.n_comm_ctas or pick_comm_ctas(m, N, W, ctx.BLOCK_N, n_sms, pair, K)
     n_comm = max(1, min(n_comm, n_sms - 1))
     if pair and n_comm % 2:
         n_comm += 1
     lib.ag_gemm_bf16(rt.heap, a, b, out, ctx.workspace, ctx.flags, ctx.ctx_dev, ctx.max_seg_rows, ctx.max_chunks,
-                     n_comm, 512 if pair else ctx.BLOCK_N, n_sms, bool(ctx.use_multimem and rt.has_multicast), rt.config.wait_timeout_s)
+                     n_comm, 512 if pair else ctx.BLOCK_N, n_sms, bool(ctx.use_multimem and rt.has_multicast),
+                     rt.config.wait_timeout_s, ctx.stats)
     ctx.calls += 1
     return out

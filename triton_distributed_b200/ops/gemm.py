@@ -35,8 +35,35 @@ def gemm_reference(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return (a.float() @ b.float().t()).to(a.dtype)
 
 
+STALL_COUNTERS = ("producer_flag_wait", "producer_ring_wait", "mma_operand_wait", "mma_accumulator_wait",
+                  "epilogue_accumulator_wait", "epilogue_peer_flag_wait", "epilogue_store_wait", "cta_total")
+
+
+def new_stall_counters(device, num_ctas: int = 148) -> torch.Tensor:
+    """Zeroed ``[num_ctas, 8]`` int64 buffer for the pair kernel's optional stall counters (SM cycles per CTA, columns
+    named by ``STALL_COUNTERS``).  Pass it as ``stats=`` to :func:`gemm` or set it as ``ctx.stats`` of an AG-GEMM /
+    GEMM-RS context; the kernel adds to it, so zero it between measurements."""
+    return torch.zeros(num_ctas, len(STALL_COUNTERS), dtype=torch.int64, device=device)
+
+
+def summarize_stall_counters(stats: torch.Tensor) -> dict:
+    """Mean share of a CTA's lifetime spent in each kind of wait (CTAs that ran), plus the maximum per counter."""
+    s = stats.detach().to("cpu").double()
+    live = s[:, -1] > 0
+    if not bool(live.any()):
+        return {}
+    s = s[live]
+    tot = s[:, -1:].clamp(min=1.0)
+    frac = s / tot
+    out = {f"{n}_mean_frac": float(frac[:, i].mean()) for i, n in enumerate(STALL_COUNTERS[:-1])}
+    out.update({f"{n}_max_frac": float(frac[:, i].max()) for i, n in enumerate(STALL_COUNTERS[:-1])})
+    out["cta_total_cycles_max"] = float(s[:, -1].max())
+    out["ctas"] = int(live.sum())
+    return out
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, block_n: int = 0,
-         num_ctas: int = 0) -> torch.Tensor:
+         num_ctas: int = 0, stats: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``a`` [M,K] x ``b`` [N,K] -> [M,N].  bf16 CUDA tensors run the sm_100a kernel."""
     if _native.use_native(a, b) and a.dtype == torch.bfloat16:
         lib = _native.load(True)
@@ -60,7 +87,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, b
             else:
                 skinny_gemm(a2, b, out=o2)
         else:
-            lib.gemm_bf16(a2, b, out.view(a2.shape[0], b.shape[0]), block_n, num_ctas)
+            lib.gemm_bf16(a2, b, out.view(a2.shape[0], b.shape[0]), block_n, num_ctas, stats)
         return out.view(*lead, b.shape[0])
     res = torch.matmul(a, b.t())
     if out is not None:

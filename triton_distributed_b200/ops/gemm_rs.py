@@ -42,6 +42,7 @@ class GEMMReduceScatterTensorParallelContext:
     ctx_dev: Optional[torch.Tensor] = None
     max_tiles: int = 0
     calls: int = 0
+    stats: Optional[torch.Tensor] = None   # optional int64 [num_ctas, 8] stall counters filled by the pair kernel
 
     @property
     def max_seg_rows(self) -> int:
@@ -112,6 +113,6 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParall
         out = torch.empty((M // W, N), dtype=a.dtype, device=a.device)
     pair = use_cta_pair(ctx.kernel_form, M // W, N, out)
     lib.gemm_rs_bf16(rt.heap, a, b, out, ctx.slots, ctx.flags, ctx.ctx_dev, ctx.max_seg_rows, ctx.max_tiles,
-                     512 if pair else ctx.BLOCK_N, ctx.num_ctas or sm_count(a.device), rt.config.wait_timeout_s)
+                     512 if pair else ctx.BLOCK_N, ctx.num_ctas or sm_count(a.device), rt.config.wait_timeout_s, ctx.stats)
     ctx.calls += 1
     return out

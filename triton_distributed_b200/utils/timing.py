@@ -68,8 +68,20 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.period_ms = period_ms
         self.rows: List[List[str]] = []
+        self.stamps: List[float] = []                     # host time of every row
+        self.windows: List[Tuple[float, float]] = []      # timed regions: only their samples are summarised
+        self._win_t0: Optional[float] = None
         self._proc = None
         self._thread = None
+
+    def begin_window(self):
+        """Start of a timed region (samples outside any window, e.g. during set-up, are ignored by ``stop``)."""
+        self._win_t0 = time.time()
+
+    def end_window(self):
+        if self._win_t0 is not None:
+            self.windows.append((self._win_t0, time.time()))
+            self._win_t0 = None
 
     def start(self):
         try:
@@ -83,11 +95,21 @@ class ClockSampler:
         self._thread.start()
         return self
 
+    def wait_first_sample(self, timeout_s: float = 5.0) -> bool:
+        """Block until the query tool has delivered its first line (its start-up is over) or ``timeout_s`` passed."""
+        t0 = time.time()
+        while not self.rows and time.time() - t0 < timeout_s:
+            if self._proc is None or self._proc.poll() is not None:
+                return False
+            time.sleep(0.02)
+        return bool(self.rows)
+
     def _read(self):
         for line in self._proc.stdout:
             parts = [p.strip() for p in line.strip().split(",")]
             if len(parts) >= 9:
                 self.rows.append(parts)
+                self.stamps.append(time.time())
 
     def stop(self) -> dict:
         if self._proc is not None:
@@ -97,8 +119,14 @@ class ClockSampler:
                 self._proc.wait(timeout=2)
             except subprocess.TimeoutExpired:
                 self._proc.kill()
+        self.end_window()
         sm, mx, reasons = [], [], set()
-        for r in self.rows:
+        slack = self.period_ms / 1000.0
+        in_win = [any(a - slack <= t <= b + slack for a, b in self.windows) for t in self.stamps]
+        use_windows = bool(self.windows) and any(in_win)
+        for idx, r in enumerate(self.rows):
+            if use_windows and not (idx < len(in_win) and in_win[idx]):
+                continue
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
