@@ -1089,7 +1089,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         stat_flush(p, kStatEpiTmemWait, w_tmem);
         stat_flush(p, kStatEpiStoreWait, w_store);
       }
-      stat_flush(p, kStatEpiFlagWait, w_flag);
+      // one representative waiter: the partials of rank + 1 are produced last
+      if (static_cast<int>(threadIdx.x) - 64 == (p.symm.rank + 1) % p.symm.world) stat_flush(p, kStatEpiFlagWait, w_flag);
       if (!ok) *abort_flag = 1;
       if (leader) bulk_wait<0>();
     }
