@@ -175,6 +175,35 @@ def main():
                 both()
             emit("own_pair_loop", loop_ms(both, args.iters, rt))
             rt.check_status()
+    # ---------------------------------------------------------------- block-scaled fp8 variant of the same shapes
+    if want("own_fp8") or want("own_gemm_fp8_only") or want("own_ag_gemm_fp8") or want("own_gemm_rs_fp8"):
+        aq, a_s = ops.quantize_act_1x128(a)
+        w1q, w1s = ops.quantize_weight_128x128(w1)
+        w2q, w2s = ops.quantize_weight_128x128(w2)
+        fullq, full_s = ops.quantize_act_1x128(full)
+        hq, h_s = ops.quantize_act_1x128(h)
+        emit("own_gemm_fp8_only_ag_shape", timed(lambda: ops.gemm_fp8_blockscaled(fullq, full_s, w1q, w1s, out=h),
+                                                 args.iters, args.warmup, fl, rt))
+        emit("own_gemm_fp8_only_rs_shape", timed(lambda: ops.gemm_fp8_blockscaled(hq, h_s, w2q, w2s, out=part),
+                                                 args.iters, args.warmup, fl, rt))
+        if W > 1:
+            link8 = {"link_bytes_fp8": (W - 1) / W * M * (K + K // 128 * 4)}
+            agc = ops.create_ag_gemm_fp8_context(max_M=M, K=K)
+            f_ag8 = lambda: ops.ag_gemm_fp8(aq, a_s, w1q, w1s, agc, out=h)   # noqa: E731
+            ms = timed(f_ag8, args.iters, args.warmup, fl, rt)
+            extra = dict(link8, loop_ms=loop_ms(f_ag8, args.iters, rt))
+            if args.stats:
+                extra["stalls"] = stall_summary(f_ag8, agc, rt, dev)
+            emit("own_ag_gemm_fp8", ms, extra)
+            rt.check_status()
+            rsc = ops.create_gemm_rs_fp8_context(max_M=M, N=K)
+            f_rs8 = lambda: ops.gemm_rs_fp8(hq, h_s, w2q, w2s, rsc, out=o)   # noqa: E731
+            ms = timed(f_rs8, args.iters, args.warmup, fl, rt)
+            extra = {"loop_ms": loop_ms(f_rs8, args.iters, rt)}
+            if args.stats:
+                extra["stalls"] = stall_summary(f_rs8, rsc, rt, dev)
+            emit("own_gemm_rs_fp8", ms, extra)
+            rt.check_status()
     tdb.finalize_distributed()
 
 

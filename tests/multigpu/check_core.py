@@ -171,6 +171,41 @@ def check_fused_gemms(rt, quick):
     log(rt, "OK ag_gemm / gemm_rs")
 
 
+def check_fp8_fused(rt):
+    """Block-scaled fp8 AG-GEMM / GEMM-RS (one launch each) against the fp32 restatement over NCCL-gathered operands."""
+    W = rt.world_size
+    for (m, N, K) in [(128, 256, 256), (300, 520, 384), (1024, 1024, 1024), (2560, 512, 512)]:   # m = rows per rank
+        ctx = ops.create_ag_gemm_fp8_context(max_M=m * W, K=K)
+        b = torch.randn(N, K, device="cuda") * 0.05
+        bq, bs = ops.quantize_weight_128x128(b)
+        for it in range(3):
+            a = (torch.randn(m, K, device="cuda") * (0.5 + rt.rank + it)).to(torch.bfloat16)
+            aq, a_s = ops.quantize_act_1x128(a)
+            out = ops.ag_gemm_fp8(aq, a_s, bq, bs, ctx)
+            ref = ops.ag_gemm_fp8_reference(aq, a_s, bq, bs, rt.group)
+            torch.cuda.synchronize()
+            rt.check_status()
+            torch.testing.assert_close(out.float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().mean().item() + 1e-3)
+        ctx.finalize()
+    for (m, N, K) in [(128, 256, 256), (300, 520, 384), (1024, 1024, 1024), (2560, 512, 512)]:   # m = output rows per rank
+        ctx = ops.create_gemm_rs_fp8_context(max_M=m * W, N=N)
+        for it in range(3):
+            a = (torch.randn(m * W, K, device="cuda") * (0.5 + 0.3 * rt.rank)).to(torch.bfloat16)
+            b = torch.randn(N, K, device="cuda") * 0.05
+            aq, a_s = ops.quantize_act_1x128(a)
+            bq, bs = ops.quantize_weight_128x128(b)
+            out = ops.gemm_rs_fp8(aq, a_s, bq, bs, ctx)
+            part = ops.gemm_fp8_blockscaled_reference(aq, a_s, bq, bs)
+            dist.all_reduce(part, group=rt.group)
+            ref = part[rt.rank * m:(rt.rank + 1) * m]
+            torch.cuda.synchronize()
+            rt.check_status()
+            # partial tiles travel as bf16: one rounding per source rank on top of the output rounding
+            torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().mean().item() + 1e-3)
+        ctx.finalize()
+    log(rt, "OK fp8 ag_gemm / gemm_rs")
+
+
 def check_gemm_ar(rt):
     W = rt.world_size
     for (N, K) in [(5120, 3200), (1280, 640), (520, 264)]:
@@ -272,7 +307,7 @@ def main():
     t0 = time.time()
     checks = {"primitives": lambda: check_primitives(rt), "allreduce": lambda: check_allreduce(rt, args.quick),
               "rs_ag": lambda: check_rs_ag(rt), "fused": lambda: check_fused_gemms(rt, args.quick),
-              "gemm_ar": lambda: check_gemm_ar(rt), "gemv_ar": lambda: check_gemv_ar(rt),
+              "fp8": lambda: check_fp8_fused(rt), "gemm_ar": lambda: check_gemm_ar(rt), "gemv_ar": lambda: check_gemv_ar(rt),
               "dist_decode": lambda: check_dist_decode(rt)}
     for name, fn in checks.items():
         if args.only and name not in args.only.split(","):

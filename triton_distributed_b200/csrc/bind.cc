@@ -284,6 +284,131 @@ void gemm_rs_bf16(SymmHeap& h, const at::Tensor& a, const at::Tensor& b, at::Ten
   check_cuda(tdb::launch_gemm(g, cur_stream()), "launch_gemm(reduce-scatter)");
 }
 
+// ------------------------------------------------------------------ block-scaled fp8 GEMM family
+void check_fp8_operands(const at::Tensor& a_q, const at::Tensor& a_s, const at::Tensor& b_q, const at::Tensor& b_s,
+                        const char* name) {
+  TORCH_CHECK(a_q.is_cuda() && b_q.is_cuda() && a_s.is_cuda() && b_s.is_cuda(), name, ": CUDA tensors expected");
+  TORCH_CHECK(a_q.scalar_type() == at::kFloat8_e4m3fn && b_q.scalar_type() == at::kFloat8_e4m3fn, name,
+              ": e4m3 operands expected");
+  TORCH_CHECK(a_s.scalar_type() == at::kFloat && b_s.scalar_type() == at::kFloat && a_s.is_contiguous() && b_s.is_contiguous(),
+              name, ": contiguous fp32 scales expected");
+  TORCH_CHECK(a_q.dim() == 2 && b_q.dim() == 2 && a_q.stride(1) == 1 && b_q.stride(1) == 1, name, ": 2-D K-major operands expected");
+  const int64_t K = a_q.size(1);
+  TORCH_CHECK(K >= 128 && K % 128 == 0 && b_q.size(1) == K, name, ": K must be a multiple of 128 and equal for both operands");
+  TORCH_CHECK(a_q.stride(0) % 16 == 0 && b_q.stride(0) % 16 == 0 && (reinterpret_cast<uintptr_t>(a_q.data_ptr()) & 15u) == 0 &&
+                  (reinterpret_cast<uintptr_t>(b_q.data_ptr()) & 15u) == 0, name, ": operand rows must be 16-byte aligned");
+  TORCH_CHECK(a_s.dim() == 2 && a_s.size(0) == a_q.size(0) && a_s.size(1) == K / 128, name, ": a_scales must be [M, K/128]");
+  TORCH_CHECK(b_s.dim() == 2 && b_s.size(0) == (b_q.size(0) + 127) / 128 && b_s.size(1) == K / 128, name,
+              ": b_scales must be [ceil(N/128), K/128]");
+}
+
+// C[M,N] (bf16) = blockscaled(A8 [M,K], a_s [M,K/128]) x blockscaled(B8 [N,K], b_s [ceil(N/128),K/128])^T
+void gemm_fp8(const at::Tensor& a_q, const at::Tensor& a_s, const at::Tensor& b_q, const at::Tensor& b_s, at::Tensor& c,
+              int num_ctas, const c10::optional<at::Tensor>& stats) {
+  check_fp8_operands(a_q, a_s, b_q, b_s, "gemm_fp8");
+  const int64_t M = a_q.size(0), K = a_q.size(1), N = b_q.size(0);
+  TORCH_CHECK(c.is_cuda() && c.scalar_type() == at::kBFloat16 && c.dim() == 2 && c.size(0) == M && c.size(1) == N &&
+                  c.stride(1) == 1, "gemm_fp8: bf16 [M, N] output expected");
+  if (M == 0 || N == 0) return;
+  c10::cuda::CUDAGuard guard(a_q.device());
+  tdb::GemmFp8Args g;
+  std::memset(&g, 0, sizeof(g));
+  g.mode = tdb::kGemmPlain;
+  g.M = M; g.N = N; g.K = K;
+  g.c = c.data_ptr();
+  g.ldc = c.stride(0);
+  g.a_scales = a_s.data_ptr<float>();
+  g.b_scales = b_s.data_ptr<float>();
+  g.tmap_a = make_tmap3(a_q.data_ptr(), tdb::kU8, 1, M, K, a_q.stride(0), a_q.stride(0) * M, 128, 128);
+  g.tmap_b = make_tmap3(b_q.data_ptr(), tdb::kU8, 1, N, K, b_q.stride(0), b_q.stride(0) * N, 128, 128);
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256) * 2;
+  g.num_ctas = std::max(2, std::min<int>(num_ctas > 0 ? num_ctas : sm_count(), tiles)) & ~1;
+  g.stats = stats_ptr(stats, g.num_ctas);
+  g.symm.world = 1;
+  g.symm.timeout_ns = 2000000000ull;
+  check_cuda(tdb::launch_gemm_fp8(g, cur_stream()), "launch_gemm_fp8");
+}
+
+// Fused all-gather + block-scaled fp8 GEMM: the local fp8 rows [m, K] and their scales [m, K/128] are pushed into
+// every rank's workspace by comm CTAs of the launch.
+void ag_gemm_fp8(SymmHeap& h, const at::Tensor& a_q, const at::Tensor& a_s, const at::Tensor& b_q, const at::Tensor& b_s,
+                 at::Tensor& c, at::Tensor& ws, at::Tensor& ws_scales, at::Tensor& flags, at::Tensor& ctx,
+                 int64_t max_seg_rows, int64_t max_chunks, int n_comm, int num_ctas, double timeout_s,
+                 const c10::optional<at::Tensor>& stats) {
+  check_fp8_operands(a_q, a_s, b_q, b_s, "ag_gemm_fp8");
+  TORCH_CHECK(a_q.is_contiguous(), "ag_gemm_fp8: contiguous local shard expected");
+  const int W = h.world();
+  const int64_t m = a_q.size(0), K = a_q.size(1), N = b_q.size(0), M = m * W, KB = K / 128;
+  TORCH_CHECK(c.scalar_type() == at::kBFloat16 && c.size(0) == M && c.size(1) == N && c.stride(1) == 1,
+              "ag_gemm_fp8: bf16 [W*m, N] output expected");
+  TORCH_CHECK(m <= max_seg_rows, "ag_gemm_fp8: more rows than the context was created for");
+  const uint64_t buf_rows = static_cast<uint64_t>(W) * max_seg_rows;
+  TORCH_CHECK(static_cast<uint64_t>(ws.numel()) * ws.element_size() >= 2 * buf_rows * K, "ag_gemm_fp8: workspace too small");
+  TORCH_CHECK(static_cast<uint64_t>(ws_scales.numel()) >= 2 * buf_rows * KB, "ag_gemm_fp8: scale workspace too small");
+  TORCH_CHECK(((m % 128) * KB * 4) % 16 == 0, "ag_gemm_fp8: rows-per-rank % 128 times K/128 must be a multiple of 4");
+  c10::cuda::CUDAGuard guard(a_q.device());
+  tdb::GemmFp8Args g;
+  std::memset(&g, 0, sizeof(g));
+  g.mode = tdb::kGemmAllGather;
+  g.M = M; g.N = N; g.K = K;
+  g.c = c.data_ptr();
+  g.ldc = c.stride(0);
+  g.b_scales = b_s.data_ptr<float>();
+  g.tmap_a = make_tmap3(ws.data_ptr(), tdb::kU8, 2, M, K, K, buf_rows * K, 128, 128);
+  g.tmap_a_local = make_tmap3(a_q.data_ptr(), tdb::kU8, 1, m, K, K, static_cast<uint64_t>(m) * K, 128, 128);
+  g.tmap_b = make_tmap3(b_q.data_ptr(), tdb::kU8, 1, N, K, b_q.stride(0), b_q.stride(0) * N, 128, 128);
+  g.num_ctas = (num_ctas > 0 ? num_ctas : sm_count()) & ~1;
+  g.seg_rows = m;
+  g.max_seg_rows = max_seg_rows;
+  g.n_comm_ctas = n_comm;
+  g.a_local = a_q.data_ptr();
+  g.a_scales_local = a_s.data_ptr<float>();
+  g.ag_ws = ws.data_ptr();
+  g.ag_ws_scales = ws_scales.data_ptr<float>();
+  g.ag_flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
+  g.max_chunks = max_chunks;
+  g.ctx = reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr());
+  g.symm = h.info(static_cast<uint64_t>(timeout_s * 1e9));
+  g.stats = stats_ptr(stats, g.num_ctas);
+  check_cuda(tdb::launch_gemm_fp8(g, cur_stream()), "launch_gemm_fp8(all-gather)");
+}
+
+// Fused block-scaled fp8 GEMM + reduce-scatter.  a_q [M, K_local]; out [M/W, N] bf16.
+void gemm_rs_fp8(SymmHeap& h, const at::Tensor& a_q, const at::Tensor& a_s, const at::Tensor& b_q, const at::Tensor& b_s,
+                 at::Tensor& out, at::Tensor& slots, at::Tensor& flags, at::Tensor& ctx, int64_t max_seg_rows,
+                 int64_t max_tiles, int num_ctas, double timeout_s, const c10::optional<at::Tensor>& stats) {
+  check_fp8_operands(a_q, a_s, b_q, b_s, "gemm_rs_fp8");
+  const int W = h.world();
+  const int64_t M = a_q.size(0), K = a_q.size(1), N = b_q.size(0);
+  TORCH_CHECK(M % W == 0, "gemm_rs_fp8: M must be divisible by the world size");
+  const int64_t m = M / W;
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == m && out.size(1) == N && out.stride(1) == 1,
+              "gemm_rs_fp8: bf16 [M/W, N] output expected");
+  TORCH_CHECK(m <= max_seg_rows && N % 8 == 0, "gemm_rs_fp8: rows exceed the context / N must be a multiple of 8");
+  TORCH_CHECK(static_cast<uint64_t>(slots.numel()) >= 2ull * W * max_seg_rows * N, "gemm_rs_fp8: slot buffer too small");
+  c10::cuda::CUDAGuard guard(a_q.device());
+  tdb::GemmFp8Args g;
+  std::memset(&g, 0, sizeof(g));
+  g.mode = tdb::kGemmReduceScatter;
+  g.M = M; g.N = N; g.K = K;
+  g.a_scales = a_s.data_ptr<float>();
+  g.b_scales = b_s.data_ptr<float>();
+  g.tmap_a = make_tmap3(a_q.data_ptr(), tdb::kU8, 1, M, K, a_q.stride(0), a_q.stride(0) * M, 128, 128);
+  g.tmap_b = make_tmap3(b_q.data_ptr(), tdb::kU8, 1, N, K, b_q.stride(0), b_q.stride(0) * N, 128, 128);
+  g.num_ctas = (num_ctas > 0 ? num_ctas : sm_count()) & ~1;
+  g.seg_rows = m;
+  g.max_seg_rows = max_seg_rows;
+  g.rs_slots = slots.data_ptr();
+  g.rs_flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
+  g.max_tiles = max_tiles;
+  g.rs_out = out.data_ptr();
+  g.ld_out = out.stride(0);
+  g.ctx = reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr());
+  g.symm = h.info(static_cast<uint64_t>(timeout_s * 1e9));
+  g.stats = stats_ptr(stats, g.num_ctas);
+  check_cuda(tdb::launch_gemm_fp8(g, cur_stream()), "launch_gemm_fp8(reduce-scatter)");
+}
+
 // Small-M GEMM (decode): out[M,N] = x[M,K] @ w[N,K]^T with split-K; acc / counters are caller-kept scratch.
 void skinny_gemm_bf16(const at::Tensor& x, const at::Tensor& w, at::Tensor& out, at::Tensor& acc, at::Tensor& counters,
                       int splits, int num_ctas) {
@@ -486,6 +611,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("stats") = py::none());
   m.def("gemm_rs_bf16", &gemm_rs_bf16, py::arg("heap"), py::arg("a"), py::arg("b"), py::arg("out"), py::arg("slots"),
         py::arg("flags"), py::arg("ctx"), py::arg("max_seg_rows"), py::arg("max_tiles"), py::arg("block_n"),
+        py::arg("num_ctas"), py::arg("timeout_s"), py::arg("stats") = py::none());
+  m.def("gemm_fp8", &gemm_fp8, py::arg("a_q"), py::arg("a_s"), py::arg("b_q"), py::arg("b_s"), py::arg("c"),
+        py::arg("num_ctas") = 0, py::arg("stats") = py::none());
+  m.def("ag_gemm_fp8", &ag_gemm_fp8, py::arg("heap"), py::arg("a_q"), py::arg("a_s"), py::arg("b_q"), py::arg("b_s"),
+        py::arg("c"), py::arg("ws"), py::arg("ws_scales"), py::arg("flags"), py::arg("ctx"), py::arg("max_seg_rows"),
+        py::arg("max_chunks"), py::arg("n_comm"), py::arg("num_ctas"), py::arg("timeout_s"), py::arg("stats") = py::none());
+  m.def("gemm_rs_fp8", &gemm_rs_fp8, py::arg("heap"), py::arg("a_q"), py::arg("a_s"), py::arg("b_q"), py::arg("b_s"),
+        py::arg("out"), py::arg("slots"), py::arg("flags"), py::arg("ctx"), py::arg("max_seg_rows"), py::arg("max_tiles"),
         py::arg("num_ctas"), py::arg("timeout_s"), py::arg("stats") = py::none());
   m.def("gemm_smem_bytes", &tdb::gemm_smem_bytes);
   m.def("skinny_gemm_bf16", &skinny_gemm_bf16);

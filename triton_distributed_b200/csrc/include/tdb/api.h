@@ -97,6 +97,39 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream);
 int gemm_smem_bytes(int block_n);
 
 // ---------------------------------------------------------------------------
+// Block-scaled fp8 GEMM (gemm_fp8_sm100.cu): e4m3 operands, fp32 scales 1 x 128 for A rows and 128 x 128 for B,
+// bf16 output; plain / all-gather / reduce-scatter modes with the protocols of the bf16 pair kernel.
+// ---------------------------------------------------------------------------
+struct GemmFp8Args {
+  int mode;                 // GemmMode
+  int M, N, K;              // K a multiple of 128
+  void* c;                  // bf16 [M, ldc] (plain / all-gather)
+  int64_t ldc;
+  const float* a_scales;    // [M, K/128] (plain / reduce-scatter)
+  const float* b_scales;    // [ceil(N/128), K/128]
+  TensorMap tmap_a;         // e4m3 as bytes: [d2][rows][K], box [128 x 128], 128-byte swizzle
+  TensorMap tmap_b;         // [1][N][K], box [128 x 128]
+  TensorMap tmap_a_local;   // all-gather: local shard [1][seg_rows][K]
+  int num_ctas;
+  int seg_rows, max_seg_rows, n_comm_ctas;
+  const void* a_local;          // all-gather: local e4m3 shard [seg_rows, K]
+  const float* a_scales_local;  // [seg_rows, K/128]
+  void* ag_ws;                  // heap [2][world*max_seg_rows][K] bytes
+  float* ag_ws_scales;          // heap [2][world*max_seg_rows][K/128]
+  uint32_t* ag_flags;           // heap [2][world][max_chunks]
+  int max_chunks;
+  void* rs_slots;               // heap [2][world][max_seg_rows][N] bf16
+  uint32_t* rs_flags;           // heap [2][world][max_tiles] (one per 128 x 128 unit)
+  int max_tiles;
+  void* rs_out;                 // bf16 [seg_rows, ld_out]
+  int64_t ld_out;
+  CtxDev* ctx;
+  SymmInfoHost symm;
+  void* stats;
+};
+cudaError_t launch_gemm_fp8(const GemmFp8Args& a, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------
 // Small-M GEMM with split-K and optional fused all-reduce (gemm_ar_sm100.cu):
 // out[M,N] = (sum over ranks) X[M,K] * W[N,K]^T, M <= 256.
 // ---------------------------------------------------------------------------

@@ -32,5 +32,7 @@ from .all_to_all import (AllToAllSingle2DContext, create_all_to_all_single_2d_co
 from .gdn import (chunk_gated_delta_rule_fwd, gated_delta_rule_chunked, gated_delta_rule_recurrent,  # noqa: F401,E402
                   prepare_chunk_indices, prepare_lens)
 from .fp8 import (ag_gemm_fp8, dequantize_act_1x128, dequantize_weight_128x128, gemm_fp8_blockscaled,  # noqa: F401,E402
-                  gemm_fp8_blockscaled_reference, quantize_act_1x128, quantize_weight_128x128)
+                  gemm_fp8_blockscaled_reference, quantize_act_1x128, quantize_weight_128x128,
+                  create_ag_gemm_fp8_context, create_gemm_rs_fp8_context, gemm_rs_fp8, ag_gemm_fp8_reference,
+                  gemm_rs_fp8_reference, AGGemmFp8Context, GemmRSFp8Context)
 from .moe import tile_arrival_order  # noqa: F401,E402
