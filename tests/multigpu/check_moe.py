@@ -44,6 +44,51 @@ def check_tp_moe(rt):
     log(rt, "OK TP-MoE (AG+grouped GEMM, grouped GEMM+RS / AR)")
 
 
+def check_tp_moe_ops(rt):
+    """The two fused launches against their fp32 restatements over NCCL-gathered inputs, with several chunk counts,
+    ragged token counts per expert and back-to-back calls (epoch parity of the workspaces, flags and counters)."""
+    W = rt.world_size
+    for (tl, H, I, E, k) in [(64, 512, 256, 16, 4), (200, 1024, 384, 8, 2), (256, 768, 128, 32, 8)]:
+        T = tl * W
+        g = torch.Generator(device="cuda").manual_seed(31)                      # same weights / routing on every rank
+        w1 = (torch.randn(E, I, H, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+        w2 = (torch.randn(E, H, I, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+        agc = ops.create_ag_group_gemm_context(T, I, H, E, k)
+        rsc = ops.create_moe_rs_context(max_token_num=T, hidden_dim=H, num_experts=E, topk=k)
+        for it in range(4):
+            ids, tw = ops.topk_router(torch.randn(T, E, device="cuda", generator=g), k)
+            x_full = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+            x = x_full[rt.rank * tl:(rt.rank + 1) * tl].contiguous()
+            # all-gather -> grouped GEMM, (token, slot) order and sorted layout
+            ref_h = ops.group_gemm_reference(x_full, w1, ids).float()
+            h = ops.ag_group_gemm(x, w1, agc, ids)
+            torch.cuda.synchronize()
+            rt.check_status()
+            torch.testing.assert_close(h.float(), ref_h, rtol=3e-2, atol=3e-2)
+            hs, srt = ops.ag_group_gemm(x, w1, agc, ids, sorted_output=True)
+            torch.cuda.synchronize()
+            rt.check_status()
+            sid = srt.sorted_ids.long()
+            torch.testing.assert_close(hs[sid >= 0].float(), ref_h[sid[sid >= 0]], rtol=3e-2, atol=3e-2)
+            # grouped GEMM -> top-k reduce -> reduce-scatter / all-reduce: every rank holds its own slice of the
+            # intermediate dimension, so the partial products differ per rank and the sum over ranks is the result
+            act = (torch.randn(T * k, I, device="cuda") * (0.2 + 0.1 * rt.rank)).to(torch.bfloat16)
+            part = ops.moe_reduce_reference(act, w2, ids, tw).float()
+            dist.all_reduce(part, group=rt.group)
+            n_chunks = (1, 2, 4, 3)[it]
+            out = ops.run_moe_reduce_rs(act, w2, ids, tw, rsc, n_chunks=n_chunks)
+            torch.cuda.synchronize()
+            rt.check_status()
+            torch.testing.assert_close(out.float(), part[rt.rank * tl:(rt.rank + 1) * tl], rtol=5e-2, atol=5e-2)
+            out_ar = ops.run_moe_reduce_ar(act, w2, ids, tw, rsc, n_chunks=n_chunks)
+            torch.cuda.synchronize()
+            rt.check_status()
+            torch.testing.assert_close(out_ar.float(), part, rtol=5e-2, atol=5e-2)
+        agc.finalize()
+        rsc.finalize()
+    log(rt, "OK fused TP-MoE ops (AG -> grouped GEMM, grouped GEMM -> top-k reduce -> RS / AR)")
+
+
 def check_ep(rt):
     W = rt.world_size
     H, I, E, k, T = 1024, 256, 8 * W, 4, 96
@@ -104,6 +149,7 @@ def main():
     tdb.initialize_distributed(seed=5)
     rt = tdb.get_runtime()
     check_tp_moe(rt)
+    check_tp_moe_ops(rt)
     check_ep(rt)
     check_a2a_single(rt)
     log(rt, "MOE OK")

@@ -75,3 +75,48 @@ def test_moe_mlp_single_rank(rt, cfg):
     hs, srt = ops.ag_group_gemm(x, w1, agc, ids, sorted_output=True)
     out2 = ops.run_moe_reduce_rs(ops.silu_mul(hs), w2, ids, tw, rsc, sort=srt)
     torch.testing.assert_close(out2.float(), ref.float(), rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("cfg", [(512, 16, 4, 4, 1), (1024, 64, 8, 8, 3), (96, 8, 2, 2, 0)])
+def test_staged_sort_and_device_tile_schedule(rt, cfg):
+    """The staged sort keeps every expert's rows together, ordered by ring distance; the device-side tile schedule
+    equals the host C++ reference on the same layout."""
+    from triton_distributed_b200 import ops
+
+    T, E, k, W, rank = cfg
+    ids, _ = ops.topk_router(torch.randn(T, E, device="cuda"), k)
+    tpr = T // W
+    srt = ops.sort_topk_ids_staged(ids, E, tpr, rank, W)
+    flat = ids.reshape(-1).long()
+    sid = srt.sorted_ids.long()
+    offs = srt.offsets.long().tolist()
+    cnt = srt.counts.long().tolist()
+    assert sorted(sid[sid >= 0].tolist()) == list(range(T * k))
+    for e in range(E):
+        rows = sid[offs[e]:offs[e] + cnt[e]]
+        assert (flat[rows] == e).all() and (sid[offs[e] + cnt[e]:offs[e + 1]] == -1).all()
+        stage = ((rows // k) // tpr - rank) % W
+        assert (stage[1:] >= stage[:-1]).all(), "rows of an expert must be ordered by arrival stage"
+    assert torch.equal(srt.sorted_ids[srt.pos_of.long()].long(), torch.arange(T * k, device="cuda"))
+    order, stage = ops.tile_schedule(srt, tpr, rank, W)
+    ref_order, ref_stage = ops.tile_arrival_order(srt, tpr, rank, W)
+    assert torch.equal(stage.cpu(), ref_stage) and torch.equal(order.cpu(), ref_order)
+
+
+@pytest.mark.parametrize("cfg", [(300, 16, 2, 256, 512), (1024, 8, 4, 7168, 256), (77, 4, 1, 64, 136)])
+def test_group_gemm_with_in_kernel_gather(rt, cfg):
+    from triton_distributed_b200 import ops
+
+    T, E, k, H, N = cfg
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(E, N, H, device="cuda") * 0.03).to(torch.bfloat16)
+    ids, tw = ops.topk_router(torch.randn(T, E, device="cuda"), k)
+    srt = ops.sort_topk_ids_align_block_size(ids, E)
+    ref = ops.group_gemm_reference(x, w, ids).float()                       # (token, slot) order
+    y = ops.group_gemm_gather(x, w, srt, a_row_div=k, scatter_out=True)
+    torch.testing.assert_close(y.float(), ref, rtol=3e-2, atol=3e-2)
+    ys = ops.group_gemm_gather(x, w, srt, a_row_div=k, scatter_out=False, row_weight=tw)
+    sid = srt.sorted_ids.long()
+    ok = sid >= 0
+    torch.testing.assert_close(ys[ok].float(), ref[sid[ok]] * tw.reshape(-1)[sid[ok]].unsqueeze(-1), rtol=3e-2, atol=3e-2)
+    assert (ys[: int(srt.meta[0])][~ok[: int(srt.meta[0])]] == 0).all()     # padding rows of visited tiles are zeros

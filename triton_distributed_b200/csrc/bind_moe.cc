@@ -7,6 +7,7 @@
 
 #include "tdb/api.h"
 #include "tdb/moe.h"
+#include "tdb/symm_heap.h"
 
 namespace py = pybind11;
 
@@ -135,9 +136,157 @@ std::vector<at::Tensor> moe_tile_arrival_order(const at::Tensor& sorted_ids, int
   return {o, st};
 }
 
+// Staged variant of moe_align_sort: inside an expert the rows are ordered by the ring distance of their token's source
+// rank.  Returns {sorted_ids, pos_of, tile_expert, offsets, meta, counts}.
+std::vector<at::Tensor> moe_align_sort_staged(const at::Tensor& ids, int64_t E, int64_t align, int64_t topk,
+                                              int64_t tokens_per_rank, int64_t rank, int64_t world) {
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kInt && ids.is_contiguous(), "moe_align_sort_staged: contiguous int32 ids");
+  c10::cuda::CUDAGuard guard(ids.device());
+  const int64_t n = ids.numel();
+  int64_t cap = n + E * (align - 1);
+  cap = (cap + align - 1) / align * align;
+  if (cap == 0) cap = align;
+  auto o = ids.options();
+  at::Tensor buckets = at::empty({E * world}, o), cursor = at::empty({E * world}, o);
+  at::Tensor counts = at::empty({E}, o), offsets = at::empty({E + 1}, o);
+  at::Tensor sorted_ids = at::empty({cap}, o), pos_of = at::empty({std::max<int64_t>(n, 1)}, o);
+  at::Tensor tile_expert = at::empty({cap / align}, o), meta = at::empty({2}, o);
+  at::Tensor idsc = ids.reshape({-1});
+  check_cuda(tdb::launch_moe_align_sort_staged(idsc.data_ptr<int32_t>(), n, E, align, topk, tokens_per_rank, rank, world,
+                                               i32(buckets), i32(counts), i32(offsets), i32(cursor), i32(sorted_ids), cap,
+                                               i32(pos_of), i32(tile_expert), cap / align, i32(meta), cur_stream()),
+             "launch_moe_align_sort_staged");
+  return {sorted_ids, pos_of, tile_expert, offsets, meta, counts};
+}
+
+// Device-side tile schedule: {order [tiles], stage [tiles], bucket_start [world + 2]}.
+std::vector<at::Tensor> moe_tile_schedule(const at::Tensor& sorted_ids, int64_t topk, int64_t tokens_per_rank, int64_t rank,
+                                          int64_t world, int64_t block) {
+  TORCH_CHECK(sorted_ids.is_cuda() && sorted_ids.scalar_type() == at::kInt && sorted_ids.is_contiguous(), "moe_tile_schedule: int32 ids");
+  c10::cuda::CUDAGuard guard(sorted_ids.device());
+  const int64_t n = sorted_ids.numel(), tiles = (n + block - 1) / block;
+  auto o = sorted_ids.options();
+  at::Tensor order = at::empty({tiles}, o), stage = at::empty({tiles}, o), bstart = at::empty({world + 2}, o);
+  check_cuda(tdb::launch_moe_tile_schedule(sorted_ids.data_ptr<int32_t>(), n, topk, tokens_per_rank, rank, world, block,
+                                           i32(stage), i32(order), i32(bstart), cur_stream()),
+             "launch_moe_tile_schedule");
+  return {order, stage, bstart};
+}
+
+void fill_moe_common(tdb::MoeFusedArgs& g, const at::Tensor& x, const at::Tensor& w, const at::Tensor& sorted_ids,
+                     const at::Tensor& tile_expert, const c10::optional<at::Tensor>& order, const at::Tensor& meta,
+                     at::Tensor& y, int64_t k_top, int64_t a_row_div, bool scatter_out,
+                     const c10::optional<at::Tensor>& row_weight, int num_ctas) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "moe_fused: bf16 x [rows, K]");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kBFloat16 && w.dim() == 3 && w.is_contiguous(), "moe_fused: bf16 w [E, N, K]");
+  TORCH_CHECK(y.is_cuda() && y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.stride(1) == 1, "moe_fused: bf16 y");
+  const int64_t K = x.size(1), E = w.size(0), N = w.size(1);
+  TORCH_CHECK(w.size(2) == K && y.size(1) == N, "moe_fused: shape mismatch");
+  TORCH_CHECK(sorted_ids.scalar_type() == at::kInt && tile_expert.scalar_type() == at::kInt && meta.scalar_type() == at::kInt,
+              "moe_fused: int32 index tensors expected");
+  TORCH_CHECK(sorted_ids.numel() == tile_expert.numel() * 128, "moe_fused: sorted_ids must hold 128 rows per tile");
+  std::memset(&g, 0, sizeof(g));
+  g.K = K; g.N = N; g.k_top = k_top;
+  g.x = x.data_ptr();
+  g.ldx = x.stride(0);
+  g.a_row_div = a_row_div;
+  g.sorted_ids = sorted_ids.data_ptr<int32_t>();
+  g.tile_expert = tile_expert.data_ptr<int32_t>();
+  if (order.has_value()) {
+    TORCH_CHECK(order->scalar_type() == at::kInt && order->numel() >= tile_expert.numel(), "moe_fused: order too small");
+    g.order = order->data_ptr<int32_t>();
+  }
+  g.meta = meta.data_ptr<int32_t>();
+  g.max_tiles = tile_expert.numel();
+  int r = tdb::encode_tensor_map_3d(&g.tmap_b, w.data_ptr(), tdb::kBF16, E, N, K, K * 2, static_cast<uint64_t>(N) * K * 2, 256, 64, 128);
+  TORCH_CHECK(r == 0, "tensor map (w) failed: ", r);
+  g.y = y.data_ptr();
+  g.ldy = y.stride(0);
+  g.scatter_out = scatter_out ? 1 : 0;
+  if (row_weight.has_value()) {
+    TORCH_CHECK(row_weight->scalar_type() == at::kFloat && row_weight->is_contiguous(), "moe_fused: fp32 row weights");
+    g.row_weight = row_weight->data_ptr<float>();
+  }
+  g.num_ctas = num_ctas > 0 ? num_ctas : at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  g.symm.world = 1;
+  g.symm.timeout_ns = 2000000000ull;
+}
+
+// Grouped GEMM with the rows gathered inside the kernel (single GPU): y = x[sorted_ids / a_row_div] @ w[expert]^T.
+void moe_group_gemm_gather(const at::Tensor& x, const at::Tensor& w, const at::Tensor& sorted_ids, const at::Tensor& tile_expert,
+                           const c10::optional<at::Tensor>& order, const at::Tensor& meta, at::Tensor& y, int64_t k_top,
+                           int64_t a_row_div, bool scatter_out, const c10::optional<at::Tensor>& row_weight, int num_ctas) {
+  c10::cuda::CUDAGuard guard(x.device());
+  tdb::MoeFusedArgs g;
+  fill_moe_common(g, x, w, sorted_ids, tile_expert, order, meta, y, k_top, a_row_div, scatter_out, row_weight, num_ctas);
+  g.mode = tdb::kMoePlain;
+  check_cuda(tdb::launch_moe_fused(g, cur_stream()), "launch_moe_fused(plain)");
+}
+
+// All-gather -> grouped GEMM in one launch.  x: local tokens [t_local, K]; ws / flags in the symmetric heap.
+void moe_ag_group_gemm(tdb::SymmHeap& h, const at::Tensor& x, const at::Tensor& w, const at::Tensor& sorted_ids,
+                       const at::Tensor& tile_expert, const c10::optional<at::Tensor>& order, const at::Tensor& meta,
+                       at::Tensor& y, int64_t k_top, bool scatter_out, at::Tensor& ws, at::Tensor& flags, at::Tensor& ctx,
+                       int64_t max_t_local, int64_t max_chunks, int n_comm, int num_ctas, double timeout_s) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous(), "moe_ag_group_gemm: contiguous local tokens expected");
+  tdb::MoeFusedArgs g;
+  fill_moe_common(g, x, w, sorted_ids, tile_expert, order, meta, y, k_top, k_top, scatter_out, c10::nullopt, num_ctas);
+  g.mode = tdb::kMoeAllGather;
+  g.t_local = x.size(0);
+  g.max_t_local = max_t_local;
+  g.n_comm = n_comm;
+  TORCH_CHECK(static_cast<uint64_t>(ws.numel()) >= 2ull * h.world() * max_t_local * g.K, "moe_ag_group_gemm: workspace too small");
+  g.ag_ws = ws.data_ptr();
+  g.ag_flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
+  g.max_chunks = max_chunks;
+  g.ctx = reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr());
+  g.symm = h.info(static_cast<uint64_t>(timeout_s * 1e9));
+  check_cuda(tdb::launch_moe_fused(g, cur_stream()), "launch_moe_fused(all-gather)");
+}
+
+// Grouped GEMM -> routing weight -> top-k reduce -> reduce-scatter (all_reduce = false) or all-reduce, one launch.
+// x: [pairs or sorted rows, K]; y_sorted: scratch [cap, N]; out: [T / W, N] or [T, N].
+void moe_group_gemm_reduce(tdb::SymmHeap& h, const at::Tensor& x, const at::Tensor& w, const at::Tensor& sorted_ids,
+                           const at::Tensor& tile_expert, const at::Tensor& meta, at::Tensor& y_sorted, int64_t k_top,
+                           int64_t a_row_div, const c10::optional<at::Tensor>& row_weight, const at::Tensor& pos_of,
+                           int64_t T, at::Tensor& chunk_done, at::Tensor& slots, at::Tensor& flags, at::Tensor& ctx,
+                           at::Tensor& out, int64_t n_chunks, int64_t n_red, bool all_reduce, int num_ctas, double timeout_s) {
+  c10::cuda::CUDAGuard guard(x.device());
+  tdb::MoeFusedArgs g;
+  fill_moe_common(g, x, w, sorted_ids, tile_expert, c10::nullopt, meta, y_sorted, k_top, a_row_div, false, row_weight, num_ctas);
+  const int W = h.world();
+  g.mode = all_reduce ? tdb::kMoeReduceAR : tdb::kMoeReduceRS;
+  g.n_chunks = n_chunks;
+  g.n_red = n_red;
+  g.T = T;
+  TORCH_CHECK(pos_of.scalar_type() == at::kInt && pos_of.numel() >= T * k_top, "moe_group_gemm_reduce: pos_of too small");
+  g.pos_of = pos_of.data_ptr<int32_t>();
+  TORCH_CHECK(chunk_done.scalar_type() == at::kInt && chunk_done.numel() >= 2 * n_chunks, "moe_group_gemm_reduce: chunk counters");
+  g.chunk_done = reinterpret_cast<uint32_t*>(chunk_done.data_ptr());
+  const int64_t slot_rows = all_reduce ? T : T / W;
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.size(0) == slot_rows && out.size(1) == g.N && out.stride(1) == 1,
+              "moe_group_gemm_reduce: output shape");
+  TORCH_CHECK(static_cast<uint64_t>(slots.numel()) >= 2ull * W * slot_rows * g.N, "moe_group_gemm_reduce: slot buffer too small");
+  TORCH_CHECK(flags.numel() >= 2ll * W * n_chunks * n_red, "moe_group_gemm_reduce: flag buffer too small");
+  g.red_slots = slots.data_ptr();
+  g.red_slot_elems = static_cast<uint64_t>(slot_rows) * g.N;
+  g.red_flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
+  g.out = out.data_ptr();
+  g.ld_out = out.stride(0);
+  g.ctx = reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr());
+  g.symm = h.info(static_cast<uint64_t>(timeout_s * 1e9));
+  check_cuda(tdb::launch_moe_fused(g, cur_stream()), "launch_moe_fused(reduce)");
+}
+
 }  // namespace
 
 void bind_moe(py::module_& m) {
+  m.def("moe_align_sort_staged", &moe_align_sort_staged);
+  m.def("moe_tile_schedule", &moe_tile_schedule);
+  m.def("moe_group_gemm_gather", &moe_group_gemm_gather);
+  m.def("moe_ag_group_gemm", &moe_ag_group_gemm);
+  m.def("moe_group_gemm_reduce", &moe_group_gemm_reduce);
   m.def("topk_router", &topk_router);
   m.def("moe_align_sort", &moe_align_sort);
   m.def("moe_tile_arrival_order", &moe_tile_arrival_order);

@@ -405,12 +405,9 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
             for (int k = 0; k < kBKB / kUmmaKB; ++k)
               umma_f8_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
-            const uint32_t e = smem_u32(&empty_bar[s]);
-            umma_commit_pair(mapa_u32(e, 0));
-            umma_commit_pair(mapa_u32(e, 1));
-            const uint32_t f = smem_u32(&part_full[b]);
-            umma_commit_pair(mapa_u32(f, 0));
-            umma_commit_pair(mapa_u32(f, 1));
+            umma_commit_pair_mask(&empty_bar[s], 3);
+            umma_commit_pair_mask(&part_full[b], 3);
+
           }
         }
         stat_flush(p, kStatMmaFullWait, w_full);
@@ -485,10 +482,13 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             tmem_ld_32x32(t_part + c * 32, r);
             tmem_ld_wait();
             if (c == 3) {
-              // this warp has read its share of the partial buffer: hand it back to the tensor core
+              // This warp has read its share of the partial buffer: hand it back to the tensor core.  The ordering
+              // that matters (TMEM reads before the next MMA overwrites them) is carried by the tcgen05 fence, so the
+              // arrival is relaxed: a release at cluster scope would make the warp wait for all of its outstanding
+              // memory operations once per K block.
               tc_fence_before_sync();
               __syncwarp();
-              if (lane == 0) mbar_arrive_cluster(b ? part_empty1 : part_empty0);
+              if (lane == 0) mbar_arrive_cluster_relaxed(b ? part_empty1 : part_empty0);
             }
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__uint_as_float(r[j]), scale, acc[c * 32 + j]);
@@ -597,6 +597,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
       }
       if (et == 0) stat_flush(p, kStatEpiTmemWait, w_part);
+   // here: latency of the first pair of TMEM loads of every block
       stat_flush(p, kStatEpiFlagWait, w_flag);
       if (!ok) *abort_flag = 1;
     }

@@ -917,15 +917,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int k = 0; k < kBK / kUmmaK; ++k)
               umma_f16_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-            const uint32_t e = smem_u32(&empty_bar[s]);
-            umma_commit_pair(mapa_u32(e, 0));
-            umma_commit_pair(mapa_u32(e, 1));
+            umma_commit_pair_mask(&empty_bar[s], 3);
           }
-          if (ok) {
-            const uint32_t f = smem_u32(&tmem_full[b]);
-            umma_commit_pair(mapa_u32(f, 0));
-            umma_commit_pair(mapa_u32(f, 1));
-          }
+          if (ok) umma_commit_pair_mask(&tmem_full[b], 3);
         }
         stat_flush(p, kStatMmaFullWait, w_full);
         stat_flush(p, kStatMmaTmemWait, w_tmem);

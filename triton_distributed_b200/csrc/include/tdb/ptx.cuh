@@ -237,6 +237,12 @@ TDB_DEVICE void cluster_sync_all() {
 TDB_DEVICE void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Same without release semantics: for hand-offs whose ordering is carried by tcgen05 fences (TMEM reads before the
+// tensor core may overwrite them), not by memory visibility.  A release at cluster scope makes the warp wait for all
+// of its outstanding memory operations, which costs about a microsecond when it is paid once per K block.
+TDB_DEVICE void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 // TMA load into this CTA's shared memory whose byte count is credited to a barrier of the pair's CTA 0
 TDB_DEVICE void tma_load_3d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int32_t c0, int32_t c1,
                                  int32_t c2) {
@@ -282,6 +288,17 @@ TDB_DEVICE void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, ui
 TDB_DEVICE void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                : "memory");
+}
+
+// One commit that arrives on the barrier at the same shared-memory offset in every CTA of `cta_mask` (bit r = CTA r of
+// the cluster) once all pair MMAs issued so far are done: half the commit instructions of the issuing thread, which
+// is the busiest thread of the kernel.  `bar` is this CTA's barrier.
+TDB_DEVICE void umma_commit_pair_mask(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(cta_mask)
+      : "memory");
 }
 
 // Shared-memory matrix descriptor for a K-major tile stored with the 128-byte

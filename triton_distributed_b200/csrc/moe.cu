@@ -197,6 +197,143 @@ __global__ void moe_unsort_kernel(const __nv_bfloat16* __restrict__ y, const int
   }
 }
 
+
+// ---- staged sort and device-side tile schedule for the all-gather -> grouped GEMM overlap ---------------------------
+// Ring distance ("stage") of a (token, slot) pair's source rank: tokens are laid out rank-major in the gathered buffer.
+__device__ __forceinline__ int pair_stage(int flat, int k, int tokens_per_rank, int rank, int world) {
+  const int src = (flat / k) / tokens_per_rank;
+  return ((src - rank) % world + world) % world;
+}
+
+// counts[e * world + stage]
+__global__ void moe_count_staged_kernel(const int32_t* __restrict__ ids, int64_t n, int E, int k, int tokens_per_rank,
+                                        int rank, int world, int32_t* counts) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(counts + e * world + pair_stage(static_cast<int>(i), k, tokens_per_rank, rank, world), 1);
+  }
+}
+
+// One CTA.  Experts are padded to `align` rows as in moe_offsets_kernel; inside an expert the rows of stage 0 come
+// first, then stage 1, ...: cursor[e * world + st] = first row of that bucket.  expert_counts[e] = rows of expert e.
+__global__ void moe_offsets_staged_kernel(const int32_t* __restrict__ counts, int E, int world, int align, int32_t* offsets,
+                                          int32_t* cursor, int32_t* expert_counts, int32_t* tile_expert, int max_tiles,
+                                          int32_t* meta) {
+  extern __shared__ int32_t sh[];   // E + 1
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int c = 0;
+    for (int st = 0; st < world; ++st) c += counts[e * world + st];
+    expert_counts[e] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      sh[e] = acc;
+      acc += (expert_counts[e] + align - 1) / align * align;
+    }
+    sh[E] = acc;
+    meta[0] = acc;
+    meta[1] = acc / align;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    offsets[e] = sh[e];
+    if (e < E) {
+      int acc = sh[e];
+      for (int st = 0; st < world; ++st) {
+        cursor[e * world + st] = acc;
+        acc += counts[e * world + st];
+      }
+    }
+  }
+  const int total_tiles = sh[E] / align;
+  for (int tl = threadIdx.x; tl < max_tiles; tl += blockDim.x) {
+    int ex = -1;
+    if (tl < total_tiles) {
+      int lo = 0, hi = E - 1;
+      const int row = tl * align;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (sh[mid] <= row) lo = mid; else hi = mid - 1;
+      }
+      ex = lo;
+    }
+    tile_expert[tl] = ex;
+  }
+}
+
+__global__ void moe_scatter_staged_kernel(const int32_t* __restrict__ ids, int64_t n, int E, int k, int tokens_per_rank,
+                                          int rank, int world, int32_t* cursor, int32_t* sorted_ids, int32_t* pos_of) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) {
+      const int pos = atomicAdd(cursor + e * world + pair_stage(static_cast<int>(i), k, tokens_per_rank, rank, world), 1);
+      sorted_ids[pos] = static_cast<int32_t>(i);
+      pos_of[i] = pos;
+    } else {
+      pos_of[i] = -1;
+    }
+  }
+}
+
+// Device-side tile schedule (one CTA of 1024 threads): stage[t] = largest ring distance of tile t's rows (-1: padding
+// only), order = tiles by stage, padding-only tiles last, expert order kept inside a stage - the order of the host
+// reference moe_tile_arrival_order.  A warp computes the stage of a tile; then warp b collects the tiles of bucket b
+// (stage b, bucket `world` = padding only) in index order with ballots, and the buckets are laid end to end.
+__global__ void __launch_bounds__(1024) moe_tile_schedule_kernel(const int32_t* __restrict__ sorted_ids, int64_t n_sorted,
+                                                                 int k, int tokens_per_rank, int rank, int world, int block,
+                                                                 int32_t* stage, int32_t* order, int32_t* bucket_start) {
+  const int tiles = static_cast<int>((n_sorted + block - 1) / block);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  __shared__ int32_t s_count[16];
+  __shared__ int32_t s_start[16];
+  for (int t = warp; t < tiles; t += nwarps) {
+    int s = -1;
+    for (int64_t r = static_cast<int64_t>(t) * block + lane; r < min(n_sorted, static_cast<int64_t>(t + 1) * block); r += 32) {
+      const int id = sorted_ids[r];
+      if (id >= 0) s = max(s, pair_stage(id, k, tokens_per_rank, rank, world));
+    }
+    for (int o = 16; o > 0; o >>= 1) s = max(s, __shfl_xor_sync(0xffffffffu, s, o));
+    if (lane == 0) stage[t] = s;
+  }
+  __syncthreads();
+  // pass 1: bucket sizes
+  if (warp <= world) {
+    int cnt = 0;
+    for (int t0 = 0; t0 < tiles; t0 += 32) {
+      const int t = t0 + lane;
+      const int b = t < tiles ? (stage[t] < 0 ? world : stage[t]) : -1;
+      cnt += __popc(__ballot_sync(0xffffffffu, b == warp));
+    }
+    if (lane == 0) s_count[warp] = cnt;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int b = 0; b <= world; ++b) {
+      s_start[b] = acc;
+      if (bucket_start != nullptr) bucket_start[b] = acc;
+      acc += s_count[b];
+    }
+    if (bucket_start != nullptr) bucket_start[world + 1] = acc;
+  }
+  __syncthreads();
+  // pass 2: stable placement
+  if (warp <= world) {
+    int base = s_start[warp];
+    for (int t0 = 0; t0 < tiles; t0 += 32) {
+      const int t = t0 + lane;
+      const int b = t < tiles ? (stage[t] < 0 ? world : stage[t]) : -1;
+      const unsigned m = __ballot_sync(0xffffffffu, b == warp);
+      if (b == warp) order[base + __popc(m & ((1u << lane) - 1u))] = t;
+      base += __popc(m);
+    }
+  }
+}
+
 int grid_1d(int64_t n, int threads, int cap) {
   int64_t g = (n + threads - 1) / threads;
   return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
@@ -224,6 +361,32 @@ cudaError_t launch_moe_align_sort(const int32_t* ids, int64_t n, int E, int alig
   if (n > 0) moe_count_kernel<<<grid_1d(n, 256, 592), 256, 0, s>>>(ids, n, E, counts);
   moe_offsets_kernel<<<1, 256, (E + 1) * sizeof(int32_t), s>>>(counts, E, align, offsets, cursor, tile_expert, max_tiles, meta);
   if (n > 0) moe_scatter_kernel<<<grid_1d(n, 256, 592), 256, 0, s>>>(ids, n, E, cursor, sorted_ids, pos_of);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_align_sort_staged(const int32_t* ids, int64_t n, int E, int align, int k, int tokens_per_rank, int rank,
+                                         int world, int32_t* bucket_counts, int32_t* counts, int32_t* offsets,
+                                         int32_t* cursor, int32_t* sorted_ids, int64_t sorted_cap, int32_t* pos_of,
+                                         int32_t* tile_expert, int max_tiles, int32_t* meta, cudaStream_t s) {
+  if (E < 1 || E > 4096 || align < 1 || world < 1 || world > 8 || k < 1 || tokens_per_rank < 1) return cudaErrorInvalidValue;
+  cudaError_t e = cudaMemsetAsync(bucket_counts, 0, sizeof(int32_t) * E * world, s);
+  if (e != cudaSuccess) return e;
+  e = cudaMemsetAsync(sorted_ids, 0xff, sizeof(int32_t) * sorted_cap, s);   // -1 = padding
+  if (e != cudaSuccess) return e;
+  if (n > 0) moe_count_staged_kernel<<<grid_1d(n, 256, 592), 256, 0, s>>>(ids, n, E, k, tokens_per_rank, rank, world, bucket_counts);
+  moe_offsets_staged_kernel<<<1, 256, (E + 1) * sizeof(int32_t), s>>>(bucket_counts, E, world, align, offsets, cursor, counts,
+                                                                     tile_expert, max_tiles, meta);
+  if (n > 0) moe_scatter_staged_kernel<<<grid_1d(n, 256, 592), 256, 0, s>>>(ids, n, E, k, tokens_per_rank, rank, world, cursor,
+                                                                           sorted_ids, pos_of);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_tile_schedule(const int32_t* sorted_ids, int64_t n_sorted, int k, int tokens_per_rank, int rank, int world,
+                                     int block, int32_t* stage, int32_t* order, int32_t* bucket_start, cudaStream_t s) {
+  if (world < 1 || world > 8 || block < 1 || k < 1 || tokens_per_rank < 1) return cudaErrorInvalidValue;
+  if (n_sorted == 0) return cudaSuccess;
+  moe_tile_schedule_kernel<<<1, 1024, 0, s>>>(sorted_ids, n_sorted, k, tokens_per_rank, rank, world, block, stage, order,
+                                             bucket_start);
   return cudaGetLastError();
 }
 

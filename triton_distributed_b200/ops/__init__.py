@@ -35,4 +35,5 @@ from .fp8 import (ag_gemm_fp8, dequantize_act_1x128, dequantize_weight_128x128, 
                   gemm_fp8_blockscaled_reference, quantize_act_1x128, quantize_weight_128x128,
                   create_ag_gemm_fp8_context, create_gemm_rs_fp8_context, gemm_rs_fp8, ag_gemm_fp8_reference,
                   gemm_rs_fp8_reference, AGGemmFp8Context, GemmRSFp8Context)
-from .moe import tile_arrival_order  # noqa: F401,E402
+from .moe import (tile_arrival_order, tile_schedule, sort_topk_ids_staged, group_gemm_gather,  # noqa: F401,E402
+                  MoESort, MoEAgScatterGroupGemmContext, MoEReduceRSContext)

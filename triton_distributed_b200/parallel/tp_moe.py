@@ -96,7 +96,7 @@ class TP_MoE:
         """x [T, H] replicated -> [T, H] replicated (grouped GEMMs + all-reduce)."""
         ids, w = self._route(x)
         srt = ops.sort_topk_ids_align_block_size(ids, self.num_experts)
-        hs = ops.group_gemm_sorted(ops.gather_sorted(x, srt), self.w13, srt)
+        hs = ops.group_gemm_gather(x, self.w13, srt, a_row_div=self.topk)   # token rows gathered inside the GEMM
         act = ops.silu_mul(hs)
         return ops.run_moe_reduce_ar(act, self.w2, ids, w, self.rs_ctx, sort=srt)
 
