@@ -85,9 +85,9 @@ def bench_allreduce(rt, sizes):
     ctx.finalize()
 
 
-def bench_gemm_ar(rt, Ms):
+def bench_gemm_ar(rt, Ms, k_local=0):
     W = rt.world_size
-    K, N = 25600 // W, 5120
+    K, N = (k_local or 25600 // W), 5120
     w = (torch.randn(N, K, device=rt.device) * 0.02).to(torch.bfloat16)
     wt = w.t()
     gctx = ops.create_gemm_ar_context(max_M=max(Ms), N=N)
@@ -101,7 +101,8 @@ def bench_gemm_ar(rt, Ms):
             rec["kernel"] = "gemv"
         else:
             rec["fused_us"] = round(timed(lambda: ops.gemm_allreduce_op(gctx, x, w, output=out), rt), 2)
-            rec["kernel"] = "tcgen05 stream-K"
+            rec["kernel"] = "tcgen05 swap-AB"
+            rec["splits"] = ops.gemm_ar.pick_gemm_ar_splits(M)
 
         def ref():
             torch.matmul(x, wt, out=out)
@@ -151,6 +152,7 @@ def main():
     ap.add_argument("--sizes", default="16384,65536,262144,1048576,4194304,16777216,67108864")
     ap.add_argument("--Ms", default="1,8,32,128")
     ap.add_argument("--ep-tokens", default="128,4096")
+    ap.add_argument("--gemm-ar-k", type=int, default=0, help="local K of the GEMM-AR sweep (default 25600 / world)")
     args = ap.parse_args()
     tdb.initialize_distributed(seed=0)
     rt = tdb.get_runtime()
@@ -158,7 +160,7 @@ def main():
     if "allreduce" in what and rt.world_size > 1:
         bench_allreduce(rt, [int(s) for s in args.sizes.split(",")])
     if "gemm_ar" in what and rt.world_size > 1:
-        bench_gemm_ar(rt, [int(m) for m in args.Ms.split(",")])
+        bench_gemm_ar(rt, [int(m) for m in args.Ms.split(",")], args.gemm_ar_k)
     if "ep" in what and rt.world_size > 1:
         bench_ep(rt, [int(t) for t in args.ep_tokens.split(",")])
     torch.cuda.synchronize()

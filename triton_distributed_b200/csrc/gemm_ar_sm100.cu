@@ -218,41 +218,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       const int n = nt * kTN + q * 32 + lane;   // this thread's output column
       const bool n_ok = n < p.N;
       const int pieces = pieces_of_tile(p, nt);
-      const bool direct = (pieces == 1 && p.mode == 0);
-      constexpr bool has_k = true;
-#pragma unroll 1
-      for (int c = 0; c < MPAD / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld_32x16(tmem_base + b * MPAD + c * 16 + (static_cast<uint32_t>(q * 32) << 16), r);
-        tmem_ld_wait();
-        if (!has_k || !n_ok) continue;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = c * 16 + j;
-          if (m < p.M) {
-            if (direct) {
-              p.out[static_cast<int64_t>(m) * p.ld_out + n] = __float2bfloat16(__uint_as_float(r[j]));
-            } else {
-              atomicAdd(p.acc + static_cast<int64_t>(m) * p.N + n, __uint_as_float(r[j]));
-            }
-          }
-        }
-      }
-      tc_fence_before_sync();
-      mbar_arrive(&tmem_empty[b]);
-      if (direct) continue;
-      // ---- tile arrival: the last split to finish owns the tile's finalisation
-      __threadfence();
-      epi_bar();
-      if (leader) {
-        const uint32_t prev = atomicAdd(p.counters + nt, 1u);
-        *is_last = (prev == static_cast<uint32_t>(pieces) - 1) ? 1 : 0;
-        if (*is_last) p.counters[nt] = 0;
-      }
-      epi_bar();
-      if (*is_last == 0) continue;
-      __threadfence();
-      // finalise: fp32 accumulation -> bf16 (out, or the heap partial for the all-reduce); clear the accumulator
+      // A piece that covers the tile's whole K needs no split accumulation: its values go straight to their bf16
+      // destination (the output, or the heap partial of the all-reduce).
+      const bool single = pieces == 1;
+      const bool direct = single && p.mode == 0;
       __nv_bfloat16* dst;
       int64_t ld_dst;
       if (p.mode == 0) {
@@ -265,19 +234,54 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         dst = p.partial + par * p.partial_half + static_cast<uint64_t>(rank) * p.m_cap * p.N;
         ld_dst = p.N;
       }
-      if (n_ok) {
-        // batches of independent loads: one L2 round trip per batch instead of one per row
-        constexpr int kBatch = MPAD < 32 ? MPAD : 32;
-        for (int m0 = 0; m0 < p.M; m0 += kBatch) {
-          float v[kBatch];
+#pragma unroll 1
+      for (int c = 0; c < MPAD / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld_32x16(tmem_base + b * MPAD + c * 16 + (static_cast<uint32_t>(q * 32) << 16), r);
+        tmem_ld_wait();
+        if (!n_ok) continue;
 #pragma unroll
-          for (int j = 0; j < kBatch; ++j)
-            v[j] = (m0 + j < p.M) ? __ldcg(p.acc + static_cast<int64_t>(m0 + j) * p.N + n) : 0.f;
+        for (int j = 0; j < 16; ++j) {
+          const int m = c * 16 + j;
+          if (m < p.M) {
+            if (single) {
+              dst[static_cast<int64_t>(m) * ld_dst + n] = __float2bfloat16(__uint_as_float(r[j]));
+            } else {
+              atomicAdd(p.acc + static_cast<int64_t>(m) * p.N + n, __uint_as_float(r[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tmem_empty[b]);
+      if (direct) continue;
+      if (!single) {
+        // ---- tile arrival: the last split to finish owns the tile's finalisation
+        __threadfence();
+        epi_bar();
+        if (leader) {
+          const uint32_t prev = atomicAdd(p.counters + nt, 1u);
+          *is_last = (prev == static_cast<uint32_t>(pieces) - 1) ? 1 : 0;
+          if (*is_last) p.counters[nt] = 0;
+        }
+        epi_bar();
+        if (*is_last == 0) continue;
+        __threadfence();
+        // finalise: fp32 accumulation -> bf16 (out, or the heap partial for the all-reduce); clear the accumulator
+        if (n_ok) {
+          // batches of independent loads: one L2 round trip per batch instead of one per row
+          constexpr int kBatch = MPAD < 32 ? MPAD : 32;
+          for (int m0 = 0; m0 < p.M; m0 += kBatch) {
+            float v[kBatch];
 #pragma unroll
-          for (int j = 0; j < kBatch; ++j) {
-            if (m0 + j < p.M) {
-              p.acc[static_cast<int64_t>(m0 + j) * p.N + n] = 0.f;
-              dst[static_cast<int64_t>(m0 + j) * ld_dst + n] = __float2bfloat16(v[j]);
+            for (int j = 0; j < kBatch; ++j)
+              v[j] = (m0 + j < p.M) ? __ldcg(p.acc + static_cast<int64_t>(m0 + j) * p.N + n) : 0.f;
+#pragma unroll
+            for (int j = 0; j < kBatch; ++j) {
+              if (m0 + j < p.M) {
+                p.acc[static_cast<int64_t>(m0 + j) * p.N + n] = 0.f;
+                dst[static_cast<int64_t>(m0 + j) * ld_dst + n] = __float2bfloat16(v[j]);
+              }
             }
           }
         }
@@ -317,26 +321,55 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         break;
       }
       const int vec_per_row = tn / 8;
-      for (int v = et; v < p.M * vec_per_row; v += 128) {
-        const int m = v / vec_per_row, cv = v - m * vec_per_row;
-        const int col = nt * kTN + cv * 8;
-        uint4 o;
-        if (p.use_mc) {
-          const __nv_bfloat16* src = p.partial + par * p.partial_half + static_cast<int64_t>(m) * p.N + col;
-          o = multimem_ld_reduce_bf16x8(mc_ptr(p.symm, src));
-        } else {
-          float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int s = 0; s < W; ++s) {
-            const __nv_bfloat16* src = p.partial + par * p.partial_half + (static_cast<uint64_t>(s) * p.m_cap + m) * p.N + col;
-            const uint4 u = ld_relaxed_sys_v4(src);
-            const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
-            accv[0] += f0.x; accv[1] += f0.y; accv[2] += f1.x; accv[3] += f1.y;
-            accv[4] += f2.x; accv[5] += f2.y; accv[6] += f3.x; accv[7] += f3.y;
+      const int total_vec = p.M * vec_per_row;
+      if (p.use_mc) {
+        // the switch returns the sum over all ranks; eight requests per thread are in flight at a time (one NVLS
+        // round trip costs microseconds, and a tile of 128 tokens has sixteen 16-byte vectors per thread)
+        constexpr int kInFlight = 8;
+        for (int v0 = et; v0 < total_vec; v0 += 128 * kInFlight) {
+          uint4 o[kInFlight];
+#pragma unroll
+          for (int i = 0; i < kInFlight; ++i) {
+            const int v = v0 + i * 128;
+            if (v < total_vec) {
+              const int m = v / vec_per_row, cv = v - m * vec_per_row;
+              const __nv_bfloat16* src = p.partial + par * p.partial_half + static_cast<int64_t>(m) * p.N + nt * kTN + cv * 8;
+              o[i] = multimem_ld_reduce_bf16x8(mc_ptr(p.symm, src));
+            }
           }
+#pragma unroll
+          for (int i = 0; i < kInFlight; ++i) {
+            const int v = v0 + i * 128;
+            if (v < total_vec) {
+              const int m = v / vec_per_row, cv = v - m * vec_per_row;
+              st_v4(p.out + static_cast<int64_t>(m) * p.ld_out + nt * kTN + cv * 8, o[i]);
+            }
+          }
+        }
+      } else {
+        for (int v = et; v < total_vec; v += 128) {
+          const int m = v / vec_per_row, cv = v - m * vec_per_row;
+          const int col = nt * kTN + cv * 8;
+          uint4 u[kMaxRanks];
+#pragma unroll
+          for (int s = 0; s < kMaxRanks; ++s)
+            if (s < W)
+              u[s] = ld_relaxed_sys_v4(p.partial + par * p.partial_half + (static_cast<uint64_t>(s) * p.m_cap + m) * p.N + col);
+          float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int s = 0; s < kMaxRanks; ++s) {
+            if (s < W) {
+              const float2 f0 = unpack_bf16x2(u[s].x), f1 = unpack_bf16x2(u[s].y), f2 = unpack_bf16x2(u[s].z),
+                           f3 = unpack_bf16x2(u[s].w);
+              accv[0] += f0.x; accv[1] += f0.y; accv[2] += f1.x; accv[3] += f1.y;
+              accv[4] += f2.x; accv[5] += f2.y; accv[6] += f3.x; accv[7] += f3.y;
+            }
+          }
+          uint4 o;
           o.x = pack_bf16x2(accv[0], accv[1]); o.y = pack_bf16x2(accv[2], accv[3]);
           o.z = pack_bf16x2(accv[4], accv[5]); o.w = pack_bf16x2(accv[6], accv[7]);
+          st_v4(p.out + static_cast<int64_t>(m) * p.ld_out + col, o);
         }
-        st_v4(p.out + static_cast<int64_t>(m) * p.ld_out + col, o);
       }
     }
     if (!ok) *abort_flag = 1;

@@ -65,6 +65,7 @@ class GemmARContext:
     max_tiles: int = 0
     ar_ctx: object = None                    # all-reduce library context for the large-M path
     calls: int = 0
+    splits: Optional[int] = None             # K splits per column tile: None = by M (see pick_gemm_ar_splits)
 
     def finalize(self):
         if self.partial is not None:
@@ -114,6 +115,18 @@ def create_ll_gemm_ar_context(rank: Optional[int] = None, world_size: Optional[i
     return create_gemm_ar_context(None, rank, world_size, local_world_size, max_M, N, dtype)
 
 
+def pick_gemm_ar_splits(M: int) -> int:
+    """K splits per 128-column tile of the swap-AB kernel.  Up to 16 tokens the weights are everything and the
+    stream-K partition over all SMs (0) wins; from 32 tokens on the fp32 split accumulation (M x 128 atomics per piece,
+    then a read-back by the last arriver) costs more than the idle SMs, so every tile is computed whole by one CTA and
+    goes straight to its bf16 destination.  ``TDB200_GEMM_AR_SPLITS`` overrides."""
+    import os
+    v = os.environ.get("TDB200_GEMM_AR_SPLITS")
+    if v not in (None, ""):
+        return int(v)
+    return 0 if M <= 16 else 1
+
+
 def gemm_ar_reference(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Tensor:
     return ref_all_reduce(torch.matmul(a, b.t()), group)
 
@@ -147,8 +160,9 @@ def gemm_allreduce_op(ctx: GemmARContext, a: torch.Tensor, b: torch.Tensor, cfg=
         return all_reduce(part, ctx=ctx.ar_ctx, output=output)
     if N != ctx.N:
         raise ValueError(f"gemm_allreduce_op: N={N} differs from the context's N={ctx.N}")
+    splits = ctx.splits if ctx.splits is not None else pick_gemm_ar_splits(M)
     lib.gemm_ar_bf16(rt.heap, a, b, output, ctx.acc, ctx.counters, ctx.partial, ctx.flags, ctx.ctx_dev, ctx.m_cap,
-                     ctx.max_tiles, 0, 0, bool(ctx.use_multimem), rt.config.wait_timeout_s)
+                     ctx.max_tiles, int(splits), 0, bool(ctx.use_multimem), rt.config.wait_timeout_s)
     ctx.calls += 1
     return output
 
