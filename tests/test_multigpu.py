@@ -33,3 +33,9 @@ def test_model_two_gpus():
 def test_moe_two_gpus():
     out = run_gpu_script("check_moe.py", 2)
     assert "MOE OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least two GPUs")
+def test_parallel_two_gpus():
+    out = run_gpu_script("check_parallel.py", 2)
+    assert "PARALLEL OK" in out
