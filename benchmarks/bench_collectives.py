@@ -102,7 +102,7 @@ def bench_gemm_ar(rt, Ms, k_local=0):
         else:
             rec["fused_us"] = round(timed(lambda: ops.gemm_allreduce_op(gctx, x, w, output=out), rt), 2)
             rec["kernel"] = "tcgen05 swap-AB"
-            rec["splits"] = ops.gemm_ar.pick_gemm_ar_splits(M)
+            rec["splits"] = ops.gemm_ar.pick_gemm_ar_splits(M, N, K)
 
         def ref():
             torch.matmul(x, wt, out=out)

@@ -260,37 +260,61 @@ __device__ void moe_reducer(const MoeParams& p, uint32_t epoch) {
       int pos[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) pos[j] = (j < p.k_top) ? p.pos_of[static_cast<int64_t>(t) * p.k_top + j] : -1;
-      for (int v = lane; v < vecs; v += 32) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        uint4 u[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          u[j] = pos[j] >= 0 ? ld_v4(p.y + static_cast<int64_t>(pos[j]) * p.ldy + c0 + 8 * v) : make_uint4(0u, 0u, 0u, 0u);
+      // two 16-byte column groups per lane and pass: sixteen row loads in flight per lane
+      for (int v0 = lane; v0 < vecs; v0 += 64) {
+        const int v1 = v0 + 32;
+        const bool has1 = v1 < vecs;
+        float acc0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        float acc1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        uint4 u0[8], u1[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float2 f0 = unpack_bf16x2(u[j].x), f1 = unpack_bf16x2(u[j].y), f2 = unpack_bf16x2(u[j].z),
-                       f3 = unpack_bf16x2(u[j].w);
-          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+          const __nv_bfloat16* rowp = p.y + static_cast<int64_t>(pos[j] >= 0 ? pos[j] : 0) * p.ldy + c0;
+          u0[j] = pos[j] >= 0 ? ld_v4(rowp + 8 * v0) : make_uint4(0u, 0u, 0u, 0u);
+          u1[j] = (pos[j] >= 0 && has1) ? ld_v4(rowp + 8 * v1) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float2 a0 = unpack_bf16x2(u0[j].x), a1 = unpack_bf16x2(u0[j].y), a2 = unpack_bf16x2(u0[j].z),
+                       a3 = unpack_bf16x2(u0[j].w);
+          acc0[0] += a0.x; acc0[1] += a0.y; acc0[2] += a1.x; acc0[3] += a1.y;
+          acc0[4] += a2.x; acc0[5] += a2.y; acc0[6] += a3.x; acc0[7] += a3.y;
+          const float2 b0 = unpack_bf16x2(u1[j].x), b1 = unpack_bf16x2(u1[j].y), b2 = unpack_bf16x2(u1[j].z),
+                       b3 = unpack_bf16x2(u1[j].w);
+          acc1[0] += b0.x; acc1[1] += b0.y; acc1[2] += b1.x; acc1[3] += b1.y;
+          acc1[4] += b2.x; acc1[5] += b2.y; acc1[6] += b3.x; acc1[7] += b3.y;
         }
         // more than eight slots per token: the remaining ones one at a time
         for (int j = 8; j < p.k_top; ++j) {
           const int pj = p.pos_of[static_cast<int64_t>(t) * p.k_top + j];
           if (pj < 0) continue;
-          const uint4 w = ld_v4(p.y + static_cast<int64_t>(pj) * p.ldy + c0 + 8 * v);
-          const float2 f0 = unpack_bf16x2(w.x), f1 = unpack_bf16x2(w.y), f2 = unpack_bf16x2(w.z), f3 = unpack_bf16x2(w.w);
-          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+          const __nv_bfloat16* rowp = p.y + static_cast<int64_t>(pj) * p.ldy + c0;
+          const uint4 w0 = ld_v4(rowp + 8 * v0);
+          const float2 a0 = unpack_bf16x2(w0.x), a1 = unpack_bf16x2(w0.y), a2 = unpack_bf16x2(w0.z), a3 = unpack_bf16x2(w0.w);
+          acc0[0] += a0.x; acc0[1] += a0.y; acc0[2] += a1.x; acc0[3] += a1.y;
+          acc0[4] += a2.x; acc0[5] += a2.y; acc0[6] += a3.x; acc0[7] += a3.y;
+          if (has1) {
+            const uint4 w1 = ld_v4(rowp + 8 * v1);
+            const float2 b0 = unpack_bf16x2(w1.x), b1 = unpack_bf16x2(w1.y), b2 = unpack_bf16x2(w1.z), b3 = unpack_bf16x2(w1.w);
+            acc1[0] += b0.x; acc1[1] += b0.y; acc1[2] += b1.x; acc1[3] += b1.y;
+            acc1[4] += b2.x; acc1[5] += b2.y; acc1[6] += b3.x; acc1[7] += b3.y;
+          }
         }
-        uint4 o;
-        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-        __nv_bfloat16* slot = p.red_slots + (static_cast<uint64_t>(buf) * W + rank) * p.red_slot_elems +
-                              static_cast<uint64_t>(row_dst) * p.N + c0 + 8 * v;
-        if (rs) {
-          st_v4(symm_at(p.symm, slot, owner), o);
-        } else {
-          for (int d = 0; d < W; ++d) st_v4(symm_at(p.symm, slot, (rank + d) % W), o);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          if (half == 1 && !has1) break;
+          const float* acc = half ? acc1 : acc0;
+          const int v = half ? v1 : v0;
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+          __nv_bfloat16* slot = p.red_slots + (static_cast<uint64_t>(buf) * W + rank) * p.red_slot_elems +
+                                static_cast<uint64_t>(row_dst) * p.N + c0 + 8 * v;
+          if (rs) {
+            st_v4(symm_at(p.symm, slot, owner), o);
+          } else {
+            for (int d = 0; d < W; ++d) st_v4(symm_at(p.symm, slot, (rank + d) % W), o);
+          }
         }
       }
     }
@@ -543,8 +567,13 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmap_b, const MoeParams p) 
       }
       if (!ok) *abort_flag = 1;
     } else {
-      // ------------------------------------------------------------ A gather (warps 6..9): thread g copies row g
+      // ------------------------------------------------------------ A gather (warps 6..9)
+      // Eight consecutive lanes copy the eight 16-byte pieces of one 128-byte row segment, so a warp instruction
+      // fetches four whole 128-byte lines (a lane per row would touch 32 half-used sectors); a thread owns piece
+      // g % 8 of the eight rows g / 8 + 16 i.
       const int g = threadIdx.x - 192;
+      const int piece = g & 7;
+      const int row0 = g >> 3;
       uint32_t it = 0;          // k-blocks issued (stage ring position)
       uint32_t done = 0;        // k-blocks whose stage has been handed to the tensor core
       bool ok = true;
@@ -562,26 +591,29 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmap_b, const MoeParams p) 
         int mt, nt, ch;
         decode(w, &mt, &nt, &ch);
         if (nt >= p.tiles_n || p.tile_expert[mt] < 0) continue;
-        const int id = p.sorted_ids[mt * kBM + g];
-        const char* src = nullptr;
-        if (id >= 0) {
-          const int64_t srow = id / p.a_row_div;
-          if (p.mode == kMoeAllGather) {
-            const int owner = static_cast<int>(srow / p.t_local);
-            const int lrow = static_cast<int>(srow - static_cast<int64_t>(owner) * p.t_local);
-            if (owner == p.symm.rank) {
-              src = reinterpret_cast<const char*>(p.x + static_cast<int64_t>(lrow) * p.ldx);
-            } else {
-              // wait for exactly the chunk this row lives in
-              const uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * p.symm.world + owner) * p.max_chunks + lrow / kBM;
-              if (!wait_until(p.symm, flag, epoch, kCmpGe, kKernelGroupGemm, 1, owner, lrow / kBM)) {
-                *abort_flag = 1;
+        const char* src[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = row0 + 16 * i;
+          const int id = p.sorted_ids[mt * kBM + r];
+          src[i] = nullptr;
+          if (id >= 0) {
+            const int64_t srow = id / p.a_row_div;
+            if (p.mode == kMoeAllGather) {
+              const int owner = static_cast<int>(srow / p.t_local);
+              const int lrow = static_cast<int>(srow - static_cast<int64_t>(owner) * p.t_local);
+              if (owner == p.symm.rank) {
+                src[i] = reinterpret_cast<const char*>(p.x + static_cast<int64_t>(lrow) * p.ldx);
+              } else {
+                // wait for exactly the chunk this row lives in
+                const uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * p.symm.world + owner) * p.max_chunks + lrow / kBM;
+                if (!wait_until(p.symm, flag, epoch, kCmpGe, kKernelGroupGemm, 1, owner, lrow / kBM)) *abort_flag = 1;
+                src[i] = reinterpret_cast<const char*>(p.ag_ws + buf * p.ag_buf_elems +
+                                                       (static_cast<uint64_t>(owner) * p.t_local + lrow) * p.K);
               }
-              src = reinterpret_cast<const char*>(p.ag_ws + buf * p.ag_buf_elems +
-                                                  (static_cast<uint64_t>(owner) * p.t_local + lrow) * p.K);
+            } else {
+              src[i] = reinterpret_cast<const char*>(p.x + srow * p.ldx);
             }
-          } else {
-            src = reinterpret_cast<const char*>(p.x + srow * p.ldx);
           }
         }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -592,12 +624,15 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmap_b, const MoeParams p) 
             if (g == 0) report(p.symm, kTimeoutMbarrier, kKernelGroupGemm, 50, -1, s, (int)ph, w);
             break;
           }
-          const uint32_t sa = smem_u32(smem + s * kStageBytes) + g * 128;
-          const int k0 = kb * kBK;
+          const uint32_t sa = smem_u32(smem + s * kStageBytes);
+          const int kcol = kb * kBK + 8 * piece;            // first element of this thread's piece
+          const bool k_ok = kcol + 8 <= p.K;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const bool valid = src != nullptr && (k0 + 8 * j + 8 <= p.K);
-            cp_async_16(sa + ((j ^ (g & 7)) << 4), valid ? src + (static_cast<int64_t>(k0) + 8 * j) * 2 : reinterpret_cast<const char*>(p.x), valid);
+          for (int i = 0; i < 8; ++i) {
+            const int r = row0 + 16 * i;
+            const bool valid = src[i] != nullptr && k_ok;
+            cp_async_16(sa + r * 128 + ((piece ^ (r & 7)) << 4),
+                        valid ? src[i] + static_cast<int64_t>(kcol) * 2 : reinterpret_cast<const char*>(p.x), valid);
           }
           cp_async_commit();
           // keep kGatherAhead groups in flight: everything older has landed

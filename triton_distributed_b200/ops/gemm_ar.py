@@ -115,16 +115,21 @@ def create_ll_gemm_ar_context(rank: Optional[int] = None, world_size: Optional[i
     return create_gemm_ar_context(None, rank, world_size, local_world_size, max_M, N, dtype)
 
 
-def pick_gemm_ar_splits(M: int) -> int:
+def pick_gemm_ar_splits(M: int, N: int = 5120, K: int = 3200, num_sms: int = 148) -> int:
     """K splits per 128-column tile of the swap-AB kernel.  Up to 16 tokens the weights are everything and the
     stream-K partition over all SMs (0) wins; from 32 tokens on the fp32 split accumulation (M x 128 atomics per piece,
-    then a read-back by the last arriver) costs more than the idle SMs, so every tile is computed whole by one CTA and
-    goes straight to its bf16 destination.  ``TDB200_GEMM_AR_SPLITS`` overrides."""
+    then a read-back by the last arriver) costs more than idle SMs, so a tile is computed whole by one CTA and goes
+    straight to its bf16 destination - unless K is so long (more than 64 k-blocks per CTA) that the few CTAs would
+    stream for too long; then K is split as far as the SM count allows.  ``TDB200_GEMM_AR_SPLITS`` overrides."""
     import os
     v = os.environ.get("TDB200_GEMM_AR_SPLITS")
     if v not in (None, ""):
         return int(v)
-    return 0 if M <= 16 else 1
+    if M <= 16:
+        return 0
+    tiles = (N + 127) // 128
+    kb = (K + 63) // 64
+    return max(1, min(num_sms // max(tiles, 1), -(-kb // 64)))
 
 
 def gemm_ar_reference(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Tensor:
@@ -160,7 +165,7 @@ def gemm_allreduce_op(ctx: GemmARContext, a: torch.Tensor, b: torch.Tensor, cfg=
         return all_reduce(part, ctx=ctx.ar_ctx, output=output)
     if N != ctx.N:
         raise ValueError(f"gemm_allreduce_op: N={N} differs from the context's N={ctx.N}")
-    splits = ctx.splits if ctx.splits is not None else pick_gemm_ar_splits(M)
+    splits = ctx.splits if ctx.splits is not None else pick_gemm_ar_splits(M, N, K)
     lib.gemm_ar_bf16(rt.heap, a, b, output, ctx.acc, ctx.counters, ctx.partial, ctx.flags, ctx.ctx_dev, ctx.m_cap,
                      ctx.max_tiles, int(splits), 0, bool(ctx.use_multimem), rt.config.wait_timeout_s)
     ctx.calls += 1

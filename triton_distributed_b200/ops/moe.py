@@ -383,7 +383,7 @@ class MoEReduceRSContext:
 def create_moe_rs_context(rank: Optional[int] = None, world_size: Optional[int] = None,
                           local_world_size: Optional[int] = None, max_token_num: int = 0, hidden_dim: int = 0,
                           num_experts: int = 0, topk: int = 0, input_dtype: torch.dtype = torch.bfloat16,
-                          n_chunks_max: int = 8, all_reduce: bool = False) -> MoEReduceRSContext:
+                          n_chunks_max: int = 8, all_reduce: bool = False, n_red_ctas: int = 16) -> MoEReduceRSContext:
     """Slots, flags and chunk counters of the fused grouped GEMM -> top-k reduce -> reduce-scatter / all-reduce launch
     (collective call).  ``all_reduce`` also allocates the larger slots of the all-reduce form."""
     rt = get_runtime()
@@ -391,7 +391,7 @@ def create_moe_rs_context(rank: Optional[int] = None, world_size: Optional[int] 
     world_size = rt.world_size if world_size is None else world_size
     max_token_num = (max_token_num + world_size - 1) // world_size * world_size
     ctx = MoEReduceRSContext(rt, rank, world_size, max_token_num, hidden_dim, num_experts, topk, input_dtype,
-                             n_chunks_max=n_chunks_max)
+                             n_chunks_max=n_chunks_max, n_red_ctas=n_red_ctas)
     if rt.is_cuda and world_size > 1:
         W = world_size
         ctx.rs_slots = rt.symm_tensor((2, W, max_token_num // W, hidden_dim), input_dtype, zero=False, sync=False)
