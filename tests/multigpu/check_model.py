@@ -11,34 +11,68 @@ import triton_distributed_b200 as tdb  # noqa: E402
 from triton_distributed_b200.models import ArchConfig, Engine, ModelConfig, PRESETS  # noqa: E402
 
 
+def compare_generation(ref_logits, ref_toks, logits, toks, rel=0.15, abs_=0.05):
+    """Greedy decoding of two numerically different backends can part ways at a near-tie, after which their logits are
+    not comparable.  Compare, step by step, only the sequences whose token history is still identical; returns the
+    largest error seen and the number of (step, sequence) pairs compared."""
+    worst, n = 0.0, 0
+    for i, (a, b) in enumerate(zip(ref_logits, logits)):
+        same = (ref_toks[:, :i] == toks[:, :i]).all(dim=1) if i > 0 else torch.ones(a.shape[0], dtype=torch.bool, device=a.device)
+        if not bool(same.any()):
+            break
+        err = (a[same] - b[same]).abs().max().item()
+        tol = rel * a[same].abs().max().item() + abs_
+        assert err < tol, f"step {i}: max|dlogits| {err:.4f} exceeds {tol:.3f} on sequences with identical history"
+        worst = max(worst, err)
+        n += int(same.sum())
+    return worst, n
+
+
 def main():
     tdb.initialize_distributed(seed=3)
     rt = tdb.get_runtime()
     W = rt.world_size
     PRESETS["check"] = ArchConfig("check", 1024, 2048, 3, 16, 8, 128, 4096)
+    # the per-rank shapes of "check" on eight ranks (2 query heads, 1 KV head, 256 intermediate columns per rank and a
+    # batch of 16), whatever the world size is: narrow shards take other kernel paths than wide ones
+    PRESETS["check-narrow"] = ArchConfig("check-narrow", 1024, 256 * W, 3, 2 * W, W, 128, 4096)
+    for name, B in (("check", 2 * W), ("check-narrow", 16)):
+        check_backends(rt, ModelConfig(model_name=name, max_length=256, rank=rt.rank, world_size=W), B)
     cfg = ModelConfig(model_name="check", max_length=256, rank=rt.rank, world_size=W)
-    B = 2 * W
+    check_megakernel(rt, cfg)
+    if rt.rank == 0:
+        print("MODEL OK", flush=True)
+    torch.cuda.synchronize()
+    rt.host_barrier()
+    sys.stdout.flush()
+    os._exit(0)   # skip interpreter teardown: nothing left to check, and it must not delay the launcher
+
+
+def check_backends(rt, cfg, B):
     ids = torch.randint(0, 4096, (B, 33), device=rt.device, generator=torch.Generator(device=rt.device).manual_seed(1))
     ref = None
-    for backend, graph in [("torch", False), ("triton_dist_AR", True), ("triton_dist_gemm_ar", True),
+    for backend, graph in [("torch", False), ("triton_dist_AR", False), ("triton_dist_AR", True), ("triton_dist_gemm_ar", True),
                            ("triton_dist", False), ("triton_dist", True)]:
         eng = Engine(cfg)
         eng.backend = backend
         eng.no_graph = not graph
+        eng.keep_logits = True
         toks = eng.serve(ids, 8)
         torch.cuda.synchronize()
         rt.check_status()
-        logits = eng._logits.float().clone()
         if ref is None:
-            ref = logits
-        err = (logits - ref).abs().max().item()
-        tol = 0.15 * ref.abs().max().item() + 0.05
+            ref = (eng.step_logits, toks)
+        err, n = compare_generation(ref[0], ref[1], eng.step_logits, toks)
         if rt.rank == 0:
-            print(f"backend {backend:22s} graph={graph} max|dlogits|={err:.4f} (tol {tol:.3f}) "
-                  f"decode {eng.last_decode_ms:.3f} ms/step", flush=True)
-        assert err < tol, backend
+            print(f"{cfg.model_name} B={B} backend {backend:22s} graph={graph} max|dlogits|={err:.4f} over {n} (step, sequence) "
+                  f"pairs with identical history, decode {eng.last_decode_ms:.3f} ms/step", flush=True)
+        assert n >= 2 * B, "too few comparable steps"
         rt.host_barrier()
-    # decode megakernel (fused GEMM+AR tasks across ranks) against the layer-wise model
+
+
+def check_megakernel(rt, cfg):
+    """decode megakernel (fused GEMM+AR tasks across ranks) against the layer-wise model"""
+    W = rt.world_size
     from triton_distributed_b200.mega import Qwen3Model
     from triton_distributed_b200.models import DenseLLM, KV_Cache
     model = DenseLLM(cfg)
@@ -68,11 +102,6 @@ def main():
         rt.host_barrier()
     if rt.rank == 0:
         print("megakernel matches the layer-wise decode on", W, "ranks", flush=True)
-        print("MODEL OK", flush=True)
-    torch.cuda.synchronize()
-    rt.host_barrier()
-    sys.stdout.flush()
-    os._exit(0)   # skip interpreter teardown: nothing left to check, and it must not delay the launcher
 
 
 if __name__ == "__main__":

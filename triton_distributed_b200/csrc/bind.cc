@@ -398,6 +398,12 @@ void gemm_rs_fp8(SymmHeap& h, const at::Tensor& a_q, const at::Tensor& a_s, cons
   g.num_ctas = (num_ctas > 0 ? num_ctas : sm_count()) & ~1;
   g.seg_rows = m;
   g.max_seg_rows = max_seg_rows;
+  {
+    const uint64_t off = heap_offset_of(h, slots);
+    for (int r = 0; r < W; ++r)
+      g.tmap_peer_c[r] = make_tmap3(reinterpret_cast<void*>(h.peer_base(r) + off), tdb::kBF16, 2 * W, m, N, N * 2,
+                                    static_cast<uint64_t>(max_seg_rows) * N * 2, 128, 64);
+  }
   g.rs_slots = slots.data_ptr();
   g.rs_flags = reinterpret_cast<uint32_t*>(flags.data_ptr());
   g.max_tiles = max_tiles;

@@ -46,11 +46,13 @@ constexpr int kThreads = 128 + kEpiThreads;  // 384: warp group 0 = producer, MM
 constexpr int kRegsControl = 40;             // registers per thread of warp group 0 after setmaxnreg
 constexpr int kRegsEpilogue = 232;           // ... of the two epilogue warp groups (128 accumulators + a chunk)
 constexpr int kGroupM = 8;
-constexpr int kStages = 6;
+constexpr int kStages = 5;
 constexpr int kABytes = kBM * kBKB;          // 16 KB: this CTA's 128 rows of A
 constexpr int kBBytes = 128 * kBKB;          // 16 KB: this CTA's half of the 256-row B tile
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kBarOffset = kStages * kStageBytes;
+constexpr int kStgBoxBytes = kBM * 64 * 2;   // one TMA-store box: 128 rows x 64 bf16 columns, 128-byte swizzle
+constexpr int kStgOffset = kStages * kStageBytes;          // staging of a whole 128 x 256 bf16 tile (four boxes)
+constexpr int kBarOffset = kStgOffset + 4 * kStgBoxBytes;
 constexpr int kSmemTotal = kBarOffset + (2 * kStages + 4) * 8 + 16;
 
 // comm CTA ring (same dynamic shared memory)
@@ -61,6 +63,10 @@ static_assert(kPushSlots * kPushPiece + kPushSlots * 8 <= kSmemTotal, "push ring
 
 enum StatSlot : int { kStatProdFlagWait = 0, kStatProdEmptyWait = 1, kStatMmaFullWait = 2, kStatMmaTmemWait = 3,
                       kStatEpiTmemWait = 4, kStatEpiFlagWait = 5, kStatEpiStoreWait = 6, kStatTotal = 7, kStatSlots = 8 };
+
+struct PeerMaps {
+  CUtensorMap m[kMaxRanks];
+};
 
 struct F8Params {
   int mode;
@@ -256,7 +262,8 @@ __device__ void ag_push(const F8Params& p, uint32_t epoch, uint8_t* smem) {
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     const __grid_constant__ CUtensorMap tmap_a_local, const F8Params p) {
+                     const __grid_constant__ CUtensorMap tmap_a_local, const __grid_constant__ PeerMaps peer_maps,
+                     const F8Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kBarOffset);
@@ -550,49 +557,73 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             }
           }
         }
-        // destination row of this thread
-        __nv_bfloat16* dst_row = nullptr;
-        int64_t n_lim = p.N;
-        if (row_ok && col_ok) {
-          if (p.mode == kGemmReduceScatter) {
-            if (own_seg) {
-              dst_row = p.rs_out + static_cast<uint64_t>(seg_row) * p.ld_out;
-            } else {
-              __nv_bfloat16* slot = p.rs_slots + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.rs_slot_elems +
-                                    static_cast<uint64_t>(seg_row) * p.N;
-              dst_row = symm_at(p.symm, slot, tl.seg);
-            }
-          } else {
-            dst_row = p.c + (static_cast<uint64_t>(tl.seg) * p.seg_rows + seg_row) * p.ldc;
-          }
-        }
-        if (dst_row != nullptr) {
-          const bool vec_ok = (reinterpret_cast<uintptr_t>(dst_row + col0) & 15u) == 0;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int cc = col0 + 8 * j;
-            if (cc + 8 <= n_lim && vec_ok) {
-              uint4 o;
-              o.x = pack_bf16x2(acc[8 * j + 0], acc[8 * j + 1]);
-              o.y = pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]);
-              o.z = pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]);
-              o.w = pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]);
-              st_v4(dst_row + cc, o);
-            } else {
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                if (cc + e < n_lim) dst_row[cc + e] = __float2bfloat16(acc[8 * j + e]);
-            }
-          }
-        }
         if (p.mode == kGemmReduceScatter && !own_seg) {
-          // all 256 threads' stores into the owner's slot precede the flags
+          // Partial tile for another rank: staged in shared memory in the 128-byte-swizzled box layout and written
+          // into the owner's slot with four TMA stores (whole 128-byte lines over NVLink; 16-byte stores from
+          // registers would cross the link as half-used sectors), then the tile's two unit flags.
+          epi_bar();   // the leader is past the completion wait of the previous staged tile: the staging is free
+          uint8_t* stg = smem + kStgOffset;
+          const int sw = row_in_tile & 7;
+#pragma unroll
+          for (int cb = 0; cb < 2; ++cb) {
+            uint8_t* srow = stg + (half * 2 + cb) * kStgBoxBytes + row_in_tile * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float* a8 = &acc[cb * 64 + 8 * j];
+              uint4 o;
+              o.x = pack_bf16x2(a8[0], a8[1]);
+              o.y = pack_bf16x2(a8[2], a8[3]);
+              o.z = pack_bf16x2(a8[4], a8[5]);
+              o.w = pack_bf16x2(a8[6], a8[7]);
+              *reinterpret_cast<uint4*>(srow + ((j ^ sw) << 4)) = o;
+            }
+          }
+          fence_proxy_async_smem();
           epi_bar();
           if (et == 0 && valid_m) {
+            const int c2 = buf * p.symm.world + p.symm.rank;
+#pragma unroll
+            for (int bx = 0; bx < 4; ++bx) {
+              const int col = tl.n0 + bx * 64;
+              if (col < p.N) tma_store_3d(&peer_maps.m[tl.seg], stg + bx * kStgBoxBytes, col, mt * kBM, c2);
+            }
+            bulk_commit();
+            bulk_wait<0>();
+            fence_proxy_async();
             fence_acq_rel_sys();
             uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.max_tiles + unit0;
             uint32_t* dst = symm_at(p.symm, flag, tl.seg);
-            for (int u = 0; u < n_units; ++u) st_release_sys(dst + u, epoch);
+            if (n_units == 2 && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+              st_release_sys_u64(reinterpret_cast<uint64_t*>(dst), (static_cast<uint64_t>(epoch) << 32) | epoch);
+            } else {
+              for (int u = 0; u < n_units; ++u) st_release_sys(dst + u, epoch);
+            }
+          }
+        } else {
+          // output rows of this rank (plain / all-gather result, or the reduce-scatter's own segment)
+          __nv_bfloat16* dst_row = nullptr;
+          if (row_ok && col_ok) {
+            dst_row = own_seg ? p.rs_out + static_cast<uint64_t>(seg_row) * p.ld_out
+                              : p.c + (static_cast<uint64_t>(tl.seg) * p.seg_rows + seg_row) * p.ldc;
+          }
+          if (dst_row != nullptr) {
+            const bool vec_ok = (reinterpret_cast<uintptr_t>(dst_row + col0) & 15u) == 0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int cc = col0 + 8 * j;
+              if (cc + 8 <= p.N && vec_ok) {
+                uint4 o;
+                o.x = pack_bf16x2(acc[8 * j + 0], acc[8 * j + 1]);
+                o.y = pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]);
+                o.z = pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]);
+                o.w = pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]);
+                st_v4(dst_row + cc, o);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (cc + e < p.N) dst_row[cc + e] = __float2bfloat16(acc[8 * j + e]);
+              }
+            }
           }
         }
       }
@@ -600,6 +631,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
    // here: latency of the first pair of TMEM loads of every block
       stat_flush(p, kStatEpiFlagWait, w_flag);
       if (!ok) *abort_flag = 1;
+      if (et == 0) bulk_wait<0>();   // shared memory stays valid until the last TMA store has read it
     }
 
     // ------------------------------------------------------------ teardown
@@ -686,7 +718,9 @@ cudaError_t launch_gemm_fp8(const GemmFp8Args& a, cudaStream_t stream) {
   memcpy(&ta, a.tmap_a.bytes, sizeof(CUtensorMap));
   memcpy(&tb, a.tmap_b.bytes, sizeof(CUtensorMap));
   memcpy(&tl, a.tmap_a_local.bytes, sizeof(CUtensorMap));
-  gemm_fp8_pair_kernel<<<grid, kThreads, smem, stream>>>(ta, tb, tl, p);
+  PeerMaps pm;
+  memcpy(&pm, a.tmap_peer_c, sizeof(PeerMaps));
+  gemm_fp8_pair_kernel<<<grid, kThreads, smem, stream>>>(ta, tb, tl, pm, p);
   return cudaGetLastError();
 }
 

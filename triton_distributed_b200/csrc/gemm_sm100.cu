@@ -317,6 +317,124 @@ __device__ void ag_push_bulk(const KParams& p, uint32_t epoch, uint8_t* smem) {
   for (int j = 0; j < pend_n; ++j) raise_flag(pend_peer[j], pend_chunk[j]);
 }
 
+// ---------------------------------------------------------------------------
+// All-gather push, NVLS ring flavour (CTA-pair kernel): every byte leaves this GPU once and the switch replicates it to
+// all ranks, so a few comm CTAs are enough.  The comm CTAs work on the shard chunk by chunk TOGETHER: CTA i owns rows
+// [i, i + 1) * 128 / n_comm of every 128-row chunk, so chunk c is complete everywhere before chunk c + 1 starts and the
+// GEMM (which visits remote tiles chunk-major in this mode) never waits for the tail of a shard.  One thread streams
+// the rows local memory -> shared memory with bulk copies through a ring of slots; all threads move a landed slot to
+// the multicast address with multimem.st.  Flag (chunk, comm CTA) is raised on every rank after the CTA's rows.
+// ---------------------------------------------------------------------------
+__device__ void ag_push_mc_ring(const KParams& p, uint32_t epoch, uint8_t* smem) {
+  const int buf = epoch & 1;
+  const int W = p.symm.world, rank = p.symm.rank;
+  const int tid = threadIdx.x;
+  const int bi = blockIdx.x;
+  const int chunks = (p.seg_rows + kBM - 1) / kBM;
+  const int rows_per_cta = kBM / p.n_comm;          // n_comm divides 128 (checked on the host)
+  const uint64_t row_bytes = static_cast<uint64_t>(p.K) * 2;
+  char* ws_local = reinterpret_cast<char*>(p.ag_ws + buf * p.ag_buf_elems);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPushSlots * kPushPiece);
+  __shared__ int s_ok;
+  if (tid == 0) {
+    for (int i = 0; i < kPushSlots; ++i) mbar_init(&bars[i], 1);
+    fence_mbar_init();
+    s_ok = 1;
+  }
+  __syncthreads();
+  // this CTA's byte range of chunk c: [lo, hi) relative to the chunk's first byte
+  auto range = [&](int c, uint64_t* lo, uint64_t* hi) {
+    const int rows_c = min(kBM, p.seg_rows - c * kBM);
+    *lo = static_cast<uint64_t>(min(rows_c, bi * rows_per_cta)) * row_bytes;
+    *hi = static_cast<uint64_t>(min(rows_c, (bi + 1) * rows_per_cta)) * row_bytes;
+  };
+  // piece cursor for loads (thread 0) and for the copy (all threads)
+  struct Cur {
+    int c;
+    uint64_t off;
+  };
+  auto piece_of = [&](const Cur& cu, uint64_t* src_off, uint32_t* bytes) -> bool {   // false: past the end
+    if (cu.c >= chunks) return false;
+    uint64_t lo, hi;
+    range(cu.c, &lo, &hi);
+    const uint64_t left = hi - lo - cu.off;
+    *bytes = static_cast<uint32_t>(left < static_cast<uint64_t>(kPushPiece) ? left : static_cast<uint64_t>(kPushPiece));
+    *src_off = static_cast<uint64_t>(cu.c) * kBM * row_bytes + lo + cu.off;
+    return true;
+  };
+  auto advance = [&](Cur& cu, uint32_t bytes) -> bool {   // true: that was the chunk's last piece
+    uint64_t lo, hi;
+    range(cu.c, &lo, &hi);
+    cu.off += bytes;
+    if (cu.off < hi - lo) return false;
+    cu.off = 0;
+    ++cu.c;
+    return true;
+  };
+  auto skip_empty = [&](Cur& cu) {   // chunks in which this CTA has no rows (ragged last chunk)
+    while (cu.c < chunks) {
+      uint64_t lo, hi;
+      range(cu.c, &lo, &hi);
+      if (hi > lo) break;
+      ++cu.c;
+    }
+  };
+  Cur ld = {0, 0}, cp = {0, 0};
+  uint32_t ld_i = 0, cp_i = 0;
+  const char* src_base = reinterpret_cast<const char*>(p.a_local);
+  char* dst_base = mc_ptr(p.symm, ws_local + static_cast<uint64_t>(rank) * p.seg_rows * row_bytes);
+  auto issue_load = [&]() {   // thread 0
+    skip_empty(ld);
+    uint64_t so;
+    uint32_t bytes;
+    if (!piece_of(ld, &so, &bytes)) return;
+    const int slot = ld_i % kPushSlots;
+    mbar_arrive_expect_tx(&bars[slot], bytes);
+    bulk_load(smem + slot * kPushPiece, src_base + so, bytes, &bars[slot]);
+    ++ld_i;
+    advance(ld, bytes);
+  };
+  if (tid == 0)
+    for (int i = 0; i < kPushAhead; ++i) issue_load();
+  // flags of chunks in which this CTA has no rows are raised as well, so that a consumer can wait for all n_comm
+  auto raise = [&](int c) {
+    if (tid < W) {
+      fence_acq_rel_sys();
+      uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * W + rank) * p.max_chunks + c * p.n_comm + bi;
+      st_release_sys(symm_at(p.symm, flag, (rank + tid) % W), epoch);
+    }
+  };
+  int next_flag = 0;   // chunks below this one have been flagged
+  while (true) {
+    skip_empty(cp);
+    uint64_t so;
+    uint32_t bytes;
+    if (!piece_of(cp, &so, &bytes)) break;
+    const int slot = cp_i % kPushSlots;
+    if (!mbar_wait(&bars[slot], (cp_i / kPushSlots) & 1, nullptr, p.mbar_timeout_ns)) {
+      if (tid == 0) report(p.symm, kTimeoutMbarrier, kKernelAgGemm, 42, -1, slot, 0, static_cast<int>(cp_i));
+      s_ok = 0;
+    }
+    __syncthreads();
+    if (s_ok == 0) break;
+    const uint8_t* sl = smem + slot * kPushPiece;
+    char* dst = dst_base + so;
+    const uint32_t nvec = bytes >> 4;
+    for (uint32_t v = tid; v < nvec; v += kThreads)
+      multimem_st_v4(dst + (static_cast<uint64_t>(v) << 4), *reinterpret_cast<const uint4*>(sl + (static_cast<uint64_t>(v) << 4)));
+    const int c_done = cp.c;
+    const bool last = advance(cp, bytes);
+    ++cp_i;
+    __syncthreads();           // the slot has been read by everyone; the CTA's stores of this piece are issued
+    if (tid == 0) issue_load();
+    if (last) {
+      for (; next_flag <= c_done; ++next_flag) raise(next_flag);
+    }
+  }
+  if (s_ok != 0)
+    for (; next_flag < chunks; ++next_flag) raise(next_flag);
+}
+
 // Owner-side reduction of the reduce-scatter mode: out[rows of my segment] = sum over sources.
 __device__ void rs_reduce(const KParams& p, uint32_t epoch, int BN) {
   const int buf = epoch & 1;
@@ -727,16 +845,33 @@ __device__ __forceinline__ PairTile decode_pair_item(const KParams& p, const Pai
   }
   PairTile r;
   const int per_seg = sc.tiles_m_pair * p.tiles_n;
-  const int si = t / per_seg;
-  const int rem = t - si * per_seg;
-  r.seg = (p.seg_first + si) % p.num_seg;
-  const int group_sz = kGroupM * p.tiles_n;
-  const int g = rem / group_sz;
-  const int first_m = g * kGroupM;
-  const int gm = min(sc.tiles_m_pair - first_m, kGroupM);
-  const int in_g = rem - g * group_sz;
-  r.mt = first_m + in_g % gm;
-  r.nt = in_g / gm;
+  if (p.mode == kGemmAllGather && p.use_mc && t >= per_seg) {
+    // NVLS all-gather: every shard arrives chunk by chunk at the same pace, so the remote part is visited chunk-major:
+    // the M tiles are ordered (pair chunk, ring distance) and swept in groups of kGroupM over all columns
+    const int rem = t - per_seg;
+    const int nrem = p.num_seg - 1;
+    const int total_m = sc.tiles_m_pair * nrem;
+    const int group_sz = kGroupM * p.tiles_n;
+    const int g = rem / group_sz;
+    const int first_m = g * kGroupM;
+    const int gm = min(total_m - first_m, kGroupM);
+    const int in_g = rem - g * group_sz;
+    const int m_lin = first_m + in_g % gm;
+    r.nt = in_g / gm;
+    r.mt = m_lin / nrem;
+    r.seg = (p.seg_first + 1 + m_lin % nrem) % p.num_seg;
+  } else {
+    const int si = t / per_seg;
+    const int rem = t - si * per_seg;
+    r.seg = (p.seg_first + si) % p.num_seg;
+    const int group_sz = kGroupM * p.tiles_n;
+    const int g = rem / group_sz;
+    const int first_m = g * kGroupM;
+    const int gm = min(sc.tiles_m_pair - first_m, kGroupM);
+    const int in_g = rem - g * group_sz;
+    r.mt = first_m + in_g % gm;
+    r.nt = in_g / gm;
+  }
   r.n0 = r.nt * kPairBN + (half > 0 ? 128 : 0);
   r.bn = half < 0 ? kPairBN : (r.n0 < p.N ? 128 : 0);
   return r;
@@ -770,7 +905,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const bool is_comm = (p.mode == kGemmAllGather) && (static_cast<int>(blockIdx.x) < p.n_comm);
   if (is_comm) {
     if (p.use_mc) {
-      ag_push_multimem(p, epoch);
+      ag_push_mc_ring(p, epoch, smem);
     } else {
       ag_push_bulk(p, epoch, smem);
     }
@@ -822,8 +957,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const bool local_seg = (p.mode == kGemmAllGather) && tl.seg == p.symm.rank;
           if (p.mode == kGemmAllGather && !local_seg && valid_m) {
             StallTimer st(p);
-            const uint32_t* flag = p.ag_flags + (static_cast<uint64_t>(buf) * p.symm.world + tl.seg) * p.max_chunks + mt;
-            ok = wait_until(p.symm, flag, epoch, kCmpGe, kKernelAgGemm, 1, tl.seg, mt);
+            const uint32_t* flags = p.ag_flags + (static_cast<uint64_t>(buf) * p.symm.world + tl.seg) * p.max_chunks;
+            if (p.use_mc) {
+              // one flag per comm CTA of the source: all of them have delivered their rows of this chunk
+              for (int i = 0; i < p.n_comm && ok; ++i)
+                ok = wait_until(p.symm, flags + mt * p.n_comm + i, epoch, kCmpGe, kKernelAgGemm, 2, tl.seg, mt * p.n_comm + i);
+            } else {
+              ok = wait_until(p.symm, flags + mt, epoch, kCmpGe, kKernelAgGemm, 1, tl.seg, mt);
+            }
             st.stop(w_flag);
             if (!ok) break;
             fence_proxy_async();
@@ -1076,7 +1217,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           fence_acq_rel_sys();
           uint32_t* flag = p.rs_flags + (static_cast<uint64_t>(buf) * p.symm.world + p.symm.rank) * p.max_tiles + unit0;
           uint32_t* dst = symm_at(p.symm, flag, tl.seg);
-          for (int u = 0; u < n_units; ++u) st_release_sys(dst + u, epoch);
+          if (n_units == 2 && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+            // both 128-column units of the tile with one release store
+            st_release_sys_u64(reinterpret_cast<uint64_t*>(dst), (static_cast<uint64_t>(epoch) << 32) | epoch);
+          } else {
+            for (int u = 0; u < n_units; ++u) st_release_sys(dst + u, epoch);
+          }
         }
       }
       if (leader) {
@@ -1151,6 +1297,10 @@ cudaError_t fill_params(const GemmArgs& a, int BN, KParams& p) {
   p.split_tail = a.split_tail;
   p.stats = reinterpret_cast<unsigned long long*>(a.stats);
   if (a.mode == kGemmAllGather && p.tiles_m_seg > a.max_chunks) return cudaErrorInvalidValue;
+  if (a.mode == kGemmAllGather && a.cta_pair && p.use_mc) {
+    // the NVLS ring push splits every 128-row chunk over the comm CTAs and keeps one flag per (chunk, comm CTA)
+    if (p.n_comm < 2 || p.n_comm > 8 || kBM % p.n_comm != 0 || p.tiles_m_seg * p.n_comm > a.max_chunks) return cudaErrorInvalidValue;
+  }
   // the pair kernel keeps reduce-scatter flags per 128 x 128 unit, the single-CTA kernel per tile
   const int rs_flag_units = a.cta_pair ? p.tiles_m_seg * ((a.N + 127) / 128) : p.tiles_m_seg * p.tiles_n;
   if (a.mode == kGemmReduceScatter && rs_flag_units > a.max_tiles) return cudaErrorInvalidValue;

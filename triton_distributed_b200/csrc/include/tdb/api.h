@@ -110,6 +110,7 @@ struct GemmFp8Args {
   TensorMap tmap_a;         // e4m3 as bytes: [d2][rows][K], box [128 x 128], 128-byte swizzle
   TensorMap tmap_b;         // [1][N][K], box [128 x 128]
   TensorMap tmap_a_local;   // all-gather: local shard [1][seg_rows][K]
+  TensorMap tmap_peer_c[kMaxRanksHost];   // reduce-scatter: per owner rank, its slots [2*world][rows][N] bf16, box [128 x 64]
   int num_ctas;
   int seg_rows, max_seg_rows, n_comm_ctas;
   const void* a_local;          // all-gather: local e4m3 shard [seg_rows, K]

@@ -34,6 +34,8 @@ class Engine:
         self.graph = None
         self.last_decode_ms: Optional[float] = None
         self.last_profile: Optional[str] = None
+        self.keep_logits = False          # True: serve() keeps the fp32 logits of every generated position in step_logits
+        self.step_logits: list = []
         # Sampling state: one generator with the SAME seed on every rank (the process-wide generator is seeded per
         # rank), and rank 0's pick is broadcast, so all ranks feed the same token into the next step.
         self._sample_gen = torch.Generator(device=self.rt.device)
@@ -131,6 +133,7 @@ class Engine:
         self.kv_cache.inc_offset(S)
         nxt = self._sample(logits)
         out = [nxt]
+        self.step_logits = [logits.float().clone()] if self.keep_logits else []
         # switch backend
         self._ensure_ctx(max(B, 1))
         self.model.set_fwd(self.backend)
@@ -148,6 +151,8 @@ class Engine:
             else:
                 self._decode_step()
             self.kv_cache.inc_offset(1)
+            if self.keep_logits:
+                self.step_logits.append(self._logits.float().clone())
             nxt = self._sample(self._logits)
             self._ids.copy_(nxt.reshape(B, 1))
             out.append(nxt.clone())

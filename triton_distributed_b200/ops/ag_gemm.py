@@ -64,7 +64,7 @@ def create_ag_gemm_context(tensor_A: Optional[torch.Tensor] = None, tensor_B: Op
                            num_local_ranks: int = 8, BLOCK_M: int = 128, BLOCK_N: int = 256, BLOCK_K: int = 64,
                            stages: int = 3, ag_intranode_stream=None, ag_internode_stream=None,
                            for_correctness: bool = False, K: Optional[int] = None, dtype: Optional[torch.dtype] = None,
-                           n_comm_ctas: int = 0, use_multimem: bool = False) -> AllGatherGEMMTensorParallelContext:
+                           n_comm_ctas: int = 0, use_multimem: Optional[bool] = None) -> AllGatherGEMMTensorParallelContext:
     """Allocate the symmetric workspace and flags (collective call: every rank, same arguments).
 
     ``max_M`` is the gathered row count (``world * rows_per_rank``).  Stream / tile arguments of the
@@ -83,12 +83,18 @@ def create_ag_gemm_context(tensor_A: Optional[torch.Tensor] = None, tensor_B: Op
         raise ValueError("create_ag_gemm_context needs tensor_A or (max_M, K)")
     dtype = dtype or torch.bfloat16
     max_M = (max_M + num_ranks - 1) // num_ranks * num_ranks
+    if use_multimem is None:
+        # From four ranks on the NVLS push wins: every byte leaves the GPU once instead of W - 1 times, so four comm
+        # CTAs carry the whole all-gather; between two ranks there is nothing to replicate.
+        import os
+        use_multimem = num_ranks >= 4 and os.environ.get("TDB200_AG_MULTIMEM", "1") != "0"
     ctx = AllGatherGEMMTensorParallelContext(rt=rt, rank=rank, num_ranks=num_ranks, max_M=max_M, K=K, dtype=dtype,
                                              BLOCK_N=BLOCK_N if BLOCK_N in (128, 256) else 256,
                                              n_comm_ctas=n_comm_ctas, use_multimem=use_multimem,
                                              for_correctness=for_correctness)
     if rt.is_cuda and num_ranks > 1:
-        ctx.max_chunks = (ctx.max_seg_rows + BLOCK_M - 1) // BLOCK_M
+        # flag words per source: one per 128-row chunk for the unicast push, one per (chunk, comm CTA <= 8) for NVLS
+        ctx.max_chunks = 8 * ((ctx.max_seg_rows + BLOCK_M - 1) // BLOCK_M)
         ctx.workspace = rt.symm_tensor((2, max_M, K), dtype, zero=False)
         ctx.flags = rt.symm_tensor((2, num_ranks, ctx.max_chunks), torch.int32)
         ctx.ctx_dev = new_ctx_dev(rt)
@@ -97,7 +103,8 @@ def create_ag_gemm_context(tensor_A: Optional[torch.Tensor] = None, tensor_B: Op
     return ctx
 
 
-PUSH_GBS_PER_CTA = 45.0     # measured: one bulk-TMA comm CTA moves about 45 GB/s (local memory -> shared -> peer)
+PUSH_GBS_PER_CTA = 22.0     # effective rate of one bulk-TMA comm CTA while the GEMM runs (ten of them starved the
+                            # eight-rank GEMM for a third of its time, twenty did not)
 LINK_GBS = 770.0            # measured peer-copy bandwidth per direction
 PAIR_TILE_TFLOPS = 20.5     # measured: one CTA pair sustains about 20.5 TFLOP/s on 256 x 256 tiles
 
@@ -182,12 +189,16 @@ def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelCo
         out = torch.empty((m * W, N), dtype=a.dtype, device=a.device)
     n_sms = ctx.num_ctas or sm_count(a.device)
     pair = use_cta_pair(ctx.kernel_form, m, N, out)
-    n_comm = ctx.n_comm_ctas or pick_comm_ctas(m, N, W, ctx.BLOCK_N, n_sms, pair, K)
-    n_comm = max(1, min(n_comm, n_sms - 1))
-    if pair and n_comm % 2:
-        n_comm += 1
+    mc = bool(ctx.use_multimem and rt.has_multicast)
+    if pair and mc:
+        n_comm = ctx.n_comm_ctas if ctx.n_comm_ctas in (2, 4, 8) else 4
+    else:
+        n_comm = ctx.n_comm_ctas or pick_comm_ctas(m, N, W, ctx.BLOCK_N, n_sms, pair, K)
+        n_comm = max(1, min(n_comm, n_sms - 1))
+        if pair and n_comm % 2:
+            n_comm += 1
     lib.ag_gemm_bf16(rt.heap, a, b, out, ctx.workspace, ctx.flags, ctx.ctx_dev, ctx.max_seg_rows, ctx.max_chunks,
-                     n_comm, 512 if pair else ctx.BLOCK_N, n_sms, bool(ctx.use_multimem and rt.has_multicast),
+                     n_comm, 512 if pair else ctx.BLOCK_N, n_sms, mc,
                      rt.config.wait_timeout_s, ctx.stats)
     ctx.calls += 1
     return out
