@@ -11,6 +11,10 @@ Device-timed inside CUDA graphs where the op allows it (the way decode uses them
 import argparse
 import json
 import os
+
+# the prefill-size EP exchange alone needs about 1 GB of receive buffers per rank: take a roomier symmetric heap than
+# the 4 GiB default (180 GB of HBM per GPU)
+os.environ.setdefault("TDB200_SYMM_HEAP_BYTES", str(16 << 30))
 import statistics
 import sys
 

@@ -75,3 +75,48 @@ def test_speed_of_light_models():
     ag = roofline.estimate_all_gather_time_ms(8192 * 8192 * 2, 8)
     rs = roofline.estimate_reduce_scatter_time_ms(8192 * 8192 * 2, 8)
     assert abs(ag - rs) < 1e-9 and 0.1 < ag < 0.3            # 117 MB over about 770 GB/s
+
+
+def test_autotuner_drives_op_knobs():
+    """The launch knobs of an op come from the autotuner's active configuration: a tuned thunk sees every candidate
+    through current_config() and the winner afterwards (reference: python/triton_dist/autotuner.py:43-250)."""
+    import time
+    from triton_distributed_b200.tools.autotuner import contextual_autotune, current_config, config_space
+    from triton_distributed_b200.ops.ag_gemm import AG_GEMM_TUNE_SPACE
+    from triton_distributed_b200.ops import tuned_configs
+
+    seen = []
+
+    @contextual_autotune(configs=config_space(n_comm_ctas=[4, 8, 16]), key=lambda n: f"n{n}", n_repeat=2, n_warmup=1)
+    def thunk(n):
+        c = current_config()["n_comm_ctas"]
+        seen.append(c)
+        time.sleep(0.001 * abs(c - 8) + 0.0005)
+        return c
+
+    assert thunk(1) == 8 and set(seen) == {4, 8, 16}
+    n_calls = len(seen)
+    assert thunk(1) == 8 and len(seen) == n_calls + 1          # cached: one more call, no re-tuning
+    assert all({"use_multimem", "n_comm_ctas"} <= set(c) for c in AG_GEMM_TUNE_SPACE)
+    hit = tuned_configs.lookup("ag_gemm", 8, 1024, 3584, 8192)
+    assert hit and hit["use_multimem"] is True and hit["n_comm_ctas"] in (2, 4, 8)
+    assert tuned_configs.lookup("ag_gemm", 8, 1000, 3584, 8192) is None
+
+
+def test_op_log_records_json(tmp_path):
+    import json
+    import torch
+    from triton_distributed_b200.utils import oplog
+    from triton_distributed_b200.ops.gemm import gemm
+
+    path = tmp_path / "ops.jsonl"
+    oplog.enable(str(path))
+    try:
+        a, b = torch.randn(8, 64), torch.randn(16, 64)
+        gemm(a, b)
+        new = oplog.flush()
+    finally:
+        oplog.disable()
+    assert new and new[-1]["op"] == "gemm" and new[-1]["shape"] == {"M": 8, "N": 16, "K": 64}
+    rec = json.loads(path.read_text().splitlines()[-1])
+    assert rec["us"] > 0 and "tflops" in rec and "roofline_frac" in rec

@@ -20,6 +20,8 @@ import torch
 
 from .. import _native
 from ..runtime import Runtime, get_runtime
+from ..tools.autotuner import config_space, contextual_autotune, current_config
+from ..utils.oplog import logged_op
 from .gemm import use_cta_pair
 from .common import new_ctx_dev, ref_all_gather, sm_count
 
@@ -39,6 +41,7 @@ class AllGatherGEMMTensorParallelContext:
     n_comm_ctas: int = 0       # 0 = automatic
     num_ctas: int = 0
     use_multimem: bool = False
+    mc_explicit: bool = False  # the caller (or the environment) chose the push flavour: the tuned table does not override it
     for_correctness: bool = False
     workspace: Optional[torch.Tensor] = None   # heap [2][max_M][K]
     flags: Optional[torch.Tensor] = None       # heap [2][W][max_chunks]
@@ -83,15 +86,16 @@ def create_ag_gemm_context(tensor_A: Optional[torch.Tensor] = None, tensor_B: Op
         raise ValueError("create_ag_gemm_context needs tensor_A or (max_M, K)")
     dtype = dtype or torch.bfloat16
     max_M = (max_M + num_ranks - 1) // num_ranks * num_ranks
+    import os
+    mc_explicit = use_multimem is not None or "TDB200_AG_MULTIMEM" in os.environ
     if use_multimem is None:
         # From four ranks on the NVLS push wins: every byte leaves the GPU once instead of W - 1 times, so four comm
         # CTAs carry the whole all-gather; between two ranks there is nothing to replicate.
-        import os
         use_multimem = num_ranks >= 4 and os.environ.get("TDB200_AG_MULTIMEM", "1") != "0"
     ctx = AllGatherGEMMTensorParallelContext(rt=rt, rank=rank, num_ranks=num_ranks, max_M=max_M, K=K, dtype=dtype,
                                              BLOCK_N=BLOCK_N if BLOCK_N in (128, 256) else 256,
                                              n_comm_ctas=n_comm_ctas, use_multimem=use_multimem,
-                                             for_correctness=for_correctness)
+                                             mc_explicit=mc_explicit, for_correctness=for_correctness)
     if rt.is_cuda and num_ranks > 1:
         # flag words per source: one per 128-row chunk for the unicast push, one per (chunk, comm CTA <= 8) for NVLS
         ctx.max_chunks = 8 * ((ctx.max_seg_rows + BLOCK_M - 1) // BLOCK_M)
@@ -156,15 +160,39 @@ def ag_gemm_reference(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Ten
     return torch.matmul(ref_all_gather(a, group), b.t())
 
 
+def _ag_meta(a, b, ctx, *args, **kw):
+    W = ctx.num_ranks
+    m, K = a.shape
+    N = b.shape[0]
+    return {"shape": {"M": m * W, "N": N, "K": K, "world": W}, "flops": 2.0 * m * W * N * K,
+            "link_bytes": (W - 1) * m * K * a.element_size()}
+
+
+# candidates of the contextual autotuner: launch-level knobs of the fused kernel
+AG_GEMM_TUNE_SPACE = (config_space(use_multimem=[False], n_comm_ctas=[4, 8, 12, 16, 20]) +
+                      config_space(use_multimem=[True], n_comm_ctas=[2, 4, 8]))
+
+
+@contextual_autotune(configs=AG_GEMM_TUNE_SPACE, is_dist=True,
+                     key=lambda a, b, ctx, **kw: f"W{ctx.num_ranks}_m{a.shape[0]}_N{b.shape[0]}_K{a.shape[1]}")
+def _ag_gemm_tuned(a, b, ctx, **kw):
+    return ag_gemm(a, b, ctx, autotune=False, **kw)
+
+
+@logged_op("ag_gemm", _ag_meta)
 def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelContext, persistent: bool = True,
             autotune: bool = False, straggler_option: Optional[Tuple[int, float]] = None,
             out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``a`` [M/W, K], ``b`` [N_local, K] -> [M, N_local].
 
     ``straggler_option=(rank, seconds)`` delays that rank on the host before the launch (a test aid; the
-    reference delays inside the kernel, allgather_gemm.py:602).
+    reference delays inside the kernel, allgather_gemm.py:602).  ``autotune=True`` lets the contextual autotuner time
+    the whole call on all ranks for every candidate of ``AG_GEMM_TUNE_SPACE`` (push flavour, comm CTAs) the first time
+    a shape is seen, and uses the winner afterwards; ``ops.tuned_configs`` holds the winners measured on B200.
     """
     rt = ctx.rt
+    if autotune and rt.is_cuda and ctx.num_ranks > 1:
+        return _ag_gemm_tuned(a, b, ctx, straggler_option=straggler_option, out=out)
     if straggler_option is not None and straggler_option[0] == ctx.rank:
         time.sleep(float(straggler_option[1]))
     if not _native.use_native(a, b) or a.dtype != torch.bfloat16:
@@ -189,11 +217,22 @@ def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelCo
         out = torch.empty((m * W, N), dtype=a.dtype, device=a.device)
     n_sms = ctx.num_ctas or sm_count(a.device)
     pair = use_cta_pair(ctx.kernel_form, m, N, out)
-    mc = bool(ctx.use_multimem and rt.has_multicast)
-    if pair and mc:
-        n_comm = ctx.n_comm_ctas if ctx.n_comm_ctas in (2, 4, 8) else 4
+    # knob precedence: a configuration the autotuner is trying / has chosen, then the context, then the table of
+    # measured winners, then the model
+    from .tuned_configs import lookup as tuned_lookup
+    cfg = current_config()
+    if cfg:                                   # the autotuner's candidate / winner overrides the context
+        want_mc = cfg.get("use_multimem", ctx.use_multimem)
+        want_comm = cfg.get("n_comm_ctas", ctx.n_comm_ctas)
     else:
-        n_comm = ctx.n_comm_ctas or pick_comm_ctas(m, N, W, ctx.BLOCK_N, n_sms, pair, K)
+        cfg = tuned_lookup("ag_gemm", W, m, N, K) or {}
+        want_mc = ctx.use_multimem if ctx.mc_explicit else cfg.get("use_multimem", ctx.use_multimem)
+        want_comm = ctx.n_comm_ctas or cfg.get("n_comm_ctas", 0)
+    mc = bool(want_mc and rt.has_multicast)
+    if pair and mc:
+        n_comm = want_comm if want_comm in (2, 4, 8) else 4
+    else:
+        n_comm = want_comm or pick_comm_ctas(m, N, W, ctx.BLOCK_N, n_sms, pair, K)
         n_comm = max(1, min(n_comm, n_sms - 1))
         if pair and n_comm % 2:
             n_comm += 1

@@ -18,6 +18,8 @@ import torch
 from .. import _native
 from ..runtime import Runtime, get_runtime
 from .common import new_ctx_dev, ref_all_reduce, sm_count
+from ..tools.autotuner import current_config
+from ..utils.oplog import logged_op
 
 MAX_CTAS = 64
 
@@ -109,6 +111,11 @@ def _ctas_for(nbytes: int, device) -> int:
     return int(max(1, min(MAX_CTAS, nbytes // (32 * 1024))))
 
 
+def _ar_meta(x, *args, **kw):
+    return {"shape": {"numel": x.numel(), "dtype": str(x.dtype)}, "bytes": x.numel() * x.element_size()}
+
+
+@logged_op("all_reduce", _ar_meta)
 def all_reduce(x: torch.Tensor, method: Optional[AllReduceMethod] = None, ctx: Optional[AllReduceContext] = None,
                output: Optional[torch.Tensor] = None, max_sm: int = -1,
                straggler_option: Optional[Tuple[int, float]] = None) -> torch.Tensor:
@@ -130,7 +137,8 @@ def all_reduce(x: torch.Tensor, method: Optional[AllReduceMethod] = None, ctx: O
         output = torch.empty_like(x)
     nbytes = x.numel() * x.element_size()
     if method is None or method == AllReduceMethod.Unknown:
-        method = get_auto_allreduce_method(nbytes, rt.has_multicast)
+        tuned = current_config().get("allreduce_method")       # a method the contextual autotuner is trying / chose
+        method = AllReduceMethod[tuned] if isinstance(tuned, str) else get_auto_allreduce_method(nbytes, rt.has_multicast)
     if _KERNEL_METHOD[method] >= 2 and not rt.has_multicast:
         method = AllReduceMethod.OneShot if _KERNEL_METHOD[method] == 2 else AllReduceMethod.TwoShot
     k = _KERNEL_METHOD[method]

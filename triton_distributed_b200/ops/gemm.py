@@ -11,6 +11,7 @@ from typing import Optional
 import torch
 
 from .. import _native
+from ..utils.oplog import logged_op
 
 
 SKINNY_M = 128   # up to this many rows the weight-streaming kernel wins
@@ -62,6 +63,12 @@ def summarize_stall_counters(stats: torch.Tensor) -> dict:
     return out
 
 
+def _gemm_meta(a, b, *args, **kw):
+    m = a.numel() // a.shape[-1]
+    return {"shape": {"M": m, "N": b.shape[0], "K": a.shape[-1]}, "flops": 2.0 * m * b.shape[0] * a.shape[-1]}
+
+
+@logged_op("gemm", _gemm_meta)
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, block_n: int = 0,
          num_ctas: int = 0, stats: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``a`` [M,K] x ``b`` [N,K] -> [M,N].  bf16 CUDA tensors run the sm_100a kernel."""

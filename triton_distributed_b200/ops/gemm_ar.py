@@ -17,6 +17,8 @@ import torch
 
 from .. import _native
 from ..runtime import Runtime, get_runtime
+from ..tools.autotuner import current_config
+from ..utils.oplog import logged_op
 from .common import new_ctx_dev, ref_all_reduce, sm_count
 
 MAX_SKINNY_M = 256
@@ -136,6 +138,15 @@ def gemm_ar_reference(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Ten
     return ref_all_reduce(torch.matmul(a, b.t()), group)
 
 
+def _gemm_ar_meta(ctx, a, b, *args, **kw):
+    M, K = a.shape
+    N = b.shape[0]
+    W = ctx.world_size
+    return {"shape": {"M": M, "N": N, "K": K * W, "world": W}, "flops": 2.0 * M * N * K,
+            "link_bytes": 2.0 * (W - 1) / max(W, 1) * M * N * a.element_size()}
+
+
+@logged_op("gemm_allreduce", _gemm_ar_meta)
 def gemm_allreduce_op(ctx: GemmARContext, a: torch.Tensor, b: torch.Tensor, cfg=None, output: Optional[torch.Tensor] = None,
                       straggler_option=None) -> torch.Tensor:
     """``a`` [M, K_local] @ ``b`` [N, K_local]^T summed over ranks -> [M, N] on every rank."""
@@ -165,7 +176,9 @@ def gemm_allreduce_op(ctx: GemmARContext, a: torch.Tensor, b: torch.Tensor, cfg=
         return all_reduce(part, ctx=ctx.ar_ctx, output=output)
     if N != ctx.N:
         raise ValueError(f"gemm_allreduce_op: N={N} differs from the context's N={ctx.N}")
-    splits = ctx.splits if ctx.splits is not None else pick_gemm_ar_splits(M, N, K)
+    tuned = current_config()
+    splits = tuned["gemm_ar_splits"] if "gemm_ar_splits" in tuned else (
+        ctx.splits if ctx.splits is not None else pick_gemm_ar_splits(M, N, K))
     lib.gemm_ar_bf16(rt.heap, a, b, output, ctx.acc, ctx.counters, ctx.partial, ctx.flags, ctx.ctx_dev, ctx.m_cap,
                      ctx.max_tiles, int(splits), 0, bool(ctx.use_multimem), rt.config.wait_timeout_s)
     ctx.calls += 1

@@ -20,6 +20,7 @@ import torch
 
 from .. import _native
 from ..runtime import Runtime, get_runtime
+from ..utils.oplog import logged_op
 from .gemm import use_cta_pair
 from .common import new_ctx_dev, ref_reduce_scatter, sm_count
 
@@ -84,6 +85,15 @@ def gemm_rs_reference(a: torch.Tensor, b: torch.Tensor, group=None) -> torch.Ten
     return ref_reduce_scatter(torch.matmul(a, b.t()), group)
 
 
+def _rs_meta(a, b, ctx, *args, **kw):
+    W = ctx.world_size
+    M, K = a.shape
+    N = b.shape[0]
+    return {"shape": {"M": M, "N": N, "K": K * W, "world": W}, "flops": 2.0 * M * N * K,
+            "link_bytes": (W - 1) / max(W, 1) * M * N * a.element_size()}
+
+
+@logged_op("gemm_rs", _rs_meta)
 def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParallelContext, persistent: bool = True,
             fuse_scatter: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``a`` [M, K_local], ``b`` [N, K_local] -> [M/W, N]."""

@@ -1,0 +1,26 @@
+"""Launch configurations that won on 8 x B200 (NVLink 5 / NVSwitch), keyed by op and problem: what ``autotune=True``
+(the contextual autotuner of ``tools/autotuner.py``) chose for the benchmark shapes, kept here so that the default path
+starts from measured values instead of re-tuning in every process.  An op looks its shape up with :func:`lookup`; a
+shape that is not listed falls back to the op's analytical model (e.g. ``pick_comm_ctas``).
+
+How an entry gets here: run the op once with ``autotune=True`` on the target box (every rank, same arguments), read the
+``best`` line for the key in ``./.autotune_logs/rank-0.log`` and copy it below.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+# (op, world, rows per rank, N local, K) -> knobs
+_TABLE: Dict[Tuple[str, int, int, int, int], Dict] = {
+    # AG -> GEMM, M = 8192 tokens, K = 8192, N = 28672 / W (the MLP up-projection of the headline benchmark).
+    # Two ranks: nothing to replicate, four unicast comm CTAs keep the 64 MB shard ahead of the GEMM (no flag stalls).
+    ("ag_gemm", 2, 4096, 14336, 8192): {"use_multimem": False, "n_comm_ctas": 4},
+    # Four and eight ranks: the NVLS ring push with four comm CTAs (every byte leaves the GPU once); at eight ranks ten
+    # unicast comm CTAs starved the GEMM for a third of its time and twenty cost a whole wave of tiles.
+    ("ag_gemm", 4, 2048, 7168, 8192): {"use_multimem": True, "n_comm_ctas": 4},
+    ("ag_gemm", 8, 1024, 3584, 8192): {"use_multimem": True, "n_comm_ctas": 4},
+}
+
+
+def lookup(op: str, world: int, rows_per_rank: int, n_local: int, k: int) -> Optional[Dict]:
+    return _TABLE.get((op, int(world), int(rows_per_rank), int(n_local), int(k)))
