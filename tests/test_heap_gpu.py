@@ -72,6 +72,31 @@ def test_bounded_wait_reports_and_context_survives(rt):
     rt.check_status()
 
 
+def test_debug_translation_reports_bad_ranges(rt):
+    """The checked put (what TDB200_DEBUG=1 enables in every put / get / signal): a rank outside the world or a range that
+    leaves the heap is reported as status 4 and nothing is written; a valid put goes through."""
+    from triton_distributed_b200 import CommTimeoutError, _native
+
+    lib = _native.load(True)
+    dst = rt.symm_tensor((64,), torch.int32)
+    src = torch.arange(64, dtype=torch.int32, device="cuda")
+    lib.bounds_probe(rt.heap, dst, src, 256, rt.rank)
+    rt.check_status()
+    assert torch.equal(dst, src)
+    dst.zero_()
+    lib.bounds_probe(rt.heap, dst, src, 256, rt.world_size + 3)          # no such rank
+    with pytest.raises(CommTimeoutError) as ei:
+        rt.check_status()
+    assert ei.value.record["code"] == 4 and ei.value.record["where"] == 101 and ei.value.record["peer"] == rt.world_size + 3
+    outside = torch.zeros(64, dtype=torch.int32, device="cuda")           # ordinary device memory, not a heap object
+    lib.bounds_probe(rt.heap, outside, src, 256, rt.rank)
+    with pytest.raises(CommTimeoutError) as ei:
+        rt.check_status()
+    assert ei.value.record["code"] == 4
+    assert int(dst.abs().sum()) == 0 and int(outside.abs().sum()) == 0
+    rt.check_status()
+
+
 def test_abort_word_stops_a_wait(rt):
     from triton_distributed_b200 import CommTimeoutError, _native
 

@@ -108,6 +108,16 @@ void timeout_probe(SymmHeap& h, at::Tensor& flag, int64_t expected, double timeo
              "launch_timeout_probe");
 }
 
+// Put `src` into the heap object `dst` of `peer` through the checked translation (what TDB200_DEBUG=1 turns on for
+// every put / get / signal): a bad destination or rank is recorded as status 4 and nothing is written.
+void bounds_probe(SymmHeap& h, at::Tensor& dst, const at::Tensor& src, int64_t nbytes, int64_t peer) {
+  TORCH_CHECK(src.is_cuda() && dst.is_cuda() && nbytes >= 0 && nbytes <= static_cast<int64_t>(src.nbytes()),
+              "bounds_probe: device tensors and nbytes <= src.nbytes() expected");
+  check_cuda(tdb::launch_bounds_probe(dst.data_ptr(), src.data_ptr(), static_cast<uint64_t>(nbytes), static_cast<int>(peer),
+                                      h.info(ns(1.0)), cur_stream()),
+             "launch_bounds_probe");
+}
+
 void p2p_copy(at::Tensor& dst, const at::Tensor& src, int64_t num_ctas, int64_t mode) {
   TORCH_CHECK(dst.is_contiguous() && src.is_contiguous(), "p2p_copy: contiguous tensors expected");
   const uint64_t bytes = static_cast<uint64_t>(src.numel()) * src.element_size();
@@ -283,6 +293,7 @@ void bind_more(py::module_& m) {
   m.def("primitives_test", &primitives_test);
   m.def("timeout_probe", &timeout_probe, py::arg("heap"), py::arg("flag"), py::arg("expected"), py::arg("timeout_s"),
         py::arg("cmp") = 1);
+  m.def("bounds_probe", &bounds_probe);
   m.def("p2p_copy", &p2p_copy);
   m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("residual") = py::none());
   m.def("silu_mul", &silu_mul);

@@ -455,6 +455,13 @@ __global__ void timeout_probe_kernel(const uint32_t* flag, uint32_t expected, in
   if (threadIdx.x == 0) wait_until(symm, flag, expected, static_cast<CmpOp>(cmp), kKernelPrimitive, 99, -1, 0);
 }
 
+// One warp-scope put with the checked translation forced on: a destination outside the heap or a peer rank outside
+// [0, world) records kBadArgument and issues no store (the check is arithmetic on the arguments, nothing is accessed).
+__global__ void bounds_probe_kernel(void* dst_local, const void* src, uint64_t bytes, int peer, SymmInfo symm) {
+  symm.debug = 1u;
+  if (threadIdx.x < 32) putmem_warp(symm, dst_local, src, bytes, peer);
+}
+
 // ---------------------------------------------------------------------------
 // Plain copy kernel between any two device-visible buffers (local or peer-mapped): the transport of the
 // pipeline-parallel CommOp and the calibration kernel for NVLink bandwidth.
@@ -618,6 +625,12 @@ cudaError_t launch_p2p_copy(void* dst, const void* src, uint64_t bytes, int num_
 cudaError_t launch_primitives_test(int32_t* data, int32_t* scratch, uint32_t* sig, uint32_t* bar_flags, int n,
                                    uint32_t epoch, const SymmInfoHost& symm, cudaStream_t stream) {
   primitives_test_kernel<<<1, 256, n * 4, stream>>>(data, scratch, sig, bar_flags, n, epoch, to_dev(symm));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bounds_probe(void* dst_local, const void* src, uint64_t bytes, int peer, const SymmInfoHost& symm,
+                                cudaStream_t stream) {
+  bounds_probe_kernel<<<1, 32, 0, stream>>>(dst_local, src, bytes, peer, to_dev(symm));
   return cudaGetLastError();
 }
 

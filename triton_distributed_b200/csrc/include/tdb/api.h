@@ -21,6 +21,8 @@ struct SymmInfoHost {
   int32_t rank;
   int32_t world;
   uint64_t timeout_ns;
+  uint32_t debug;      // TDB200_DEBUG: device primitives check heap ranges and peer ranks
+  uint32_t pad_;
 };
 
 // 128-byte opaque CUtensorMap image.

@@ -61,6 +61,9 @@ cudaError_t launch_p2p_copy(void* dst, const void* src, uint64_t bytes, int num_
 
 cudaError_t launch_primitives_test(int32_t* data, int32_t* scratch, uint32_t* sig, uint32_t* bar_flags, int n,
                                    uint32_t epoch, const SymmInfoHost& symm, cudaStream_t stream);
+// Checked warp-scope put (debug translation forced on): bad ranges / ranks are reported, never accessed.
+cudaError_t launch_bounds_probe(void* dst_local, const void* src, uint64_t bytes, int peer, const SymmInfoHost& symm,
+                                cudaStream_t stream);
 cudaError_t launch_timeout_probe(const uint32_t* flag, uint32_t expected, int cmp, const SymmInfoHost& symm,
                                  cudaStream_t stream);
 

@@ -30,6 +30,8 @@ struct SymmInfo {
   int32_t rank;
   int32_t world;
   uint64_t timeout_ns;            // limit of every wait
+  uint32_t debug;                 // != 0: put / get / notify check their heap ranges and peer ranks
+  uint32_t pad_;
 };
 
 TDB_DEVICE int my_pe(const SymmInfo& s) { return s.rank; }
@@ -78,6 +80,24 @@ TDB_DEVICE bool abort_requested(const SymmInfo& s) {
   return s.status != nullptr && *reinterpret_cast<volatile int32_t*>(&s.status->abort_word) != 0;
 }
 
+// Checked translation used by the put / get / signal primitives.  With s.debug set, a peer rank outside [0, world) or
+// a range that leaves this rank's heap records kBadArgument (where = `site`, index = low bits of the offending offset)
+// and yields nullptr, and the primitive then skips the access: a wrong pointer becomes an error on the host instead
+// of a fault on a peer GPU.  Without s.debug it is symm_at.
+static __device__ __noinline__ void symm_check_failed(const SymmInfo& s, const void* local, uint64_t bytes, int peer, int site) {
+  const uint64_t off = reinterpret_cast<uint64_t>(local) - s.peer_base[s.rank];
+  report(s, kBadArgument, kKernelPrimitive, site, peer, static_cast<int>(off & 0x7fffffffu),
+         static_cast<int>(s.heap_bytes >> 20), static_cast<int>(bytes & 0x7fffffffu));
+}
+template <typename T>
+TDB_DEVICE T* symm_at_checked(const SymmInfo& s, T* local, uint64_t bytes, int peer, int site) {
+  if (s.debug != 0u && (peer < 0 || peer >= s.world || !in_heap(s, local, bytes))) {
+    symm_check_failed(s, local, bytes, peer, site);
+    return nullptr;
+  }
+  return symm_at(s, local, peer);
+}
+
 // ---------------------------------------------------------------------------
 // Signals
 // ---------------------------------------------------------------------------
@@ -87,7 +107,8 @@ enum SignalOp : int { kSignalSet = 0, kSignalAdd = 1 };
 // pointer into this rank's heap).  Call from ONE thread after the CTA's data
 // stores have been ordered by __syncthreads().
 TDB_DEVICE void notify(const SymmInfo& s, uint32_t* flag_local, int peer, uint32_t value, SignalOp op) {
-  uint32_t* dst = symm_at(s, flag_local, peer);
+  uint32_t* dst = symm_at_checked(s, flag_local, sizeof(uint32_t), peer, 100);
+  if (dst == nullptr) return;
   if (op == kSignalSet) {
     st_release_sys(dst, value);
   } else {
@@ -168,29 +189,25 @@ TDB_DEVICE void copy_bytes_strided(char* dst, const char* src, uint64_t bytes, i
 
 // putmem: copy `bytes` from local memory `src` to the heap object `dst_local` on `peer`.
 TDB_DEVICE void putmem_block(const SymmInfo& s, void* dst_local, const void* src, uint64_t bytes, int peer) {
-  copy_bytes_strided(reinterpret_cast<char*>(symm_at(s, reinterpret_cast<char*>(dst_local), peer)),
-                     reinterpret_cast<const char*>(src), bytes, threadIdx.x, blockDim.x);
+  char* dst = symm_at_checked(s, reinterpret_cast<char*>(dst_local), bytes, peer, 101);
+  if (dst != nullptr) copy_bytes_strided(dst, reinterpret_cast<const char*>(src), bytes, threadIdx.x, blockDim.x);
 }
 TDB_DEVICE void putmem_warp(const SymmInfo& s, void* dst_local, const void* src, uint64_t bytes, int peer) {
-  copy_bytes_strided(reinterpret_cast<char*>(symm_at(s, reinterpret_cast<char*>(dst_local), peer)),
-                     reinterpret_cast<const char*>(src), bytes, lane_id(), 32);
+  char* dst = symm_at_checked(s, reinterpret_cast<char*>(dst_local), bytes, peer, 101);
+  if (dst != nullptr) copy_bytes_strided(dst, reinterpret_cast<const char*>(src), bytes, lane_id(), 32);
 }
 TDB_DEVICE void putmem_thread(const SymmInfo& s, void* dst_local, const void* src, uint64_t bytes, int peer) {
-  copy_bytes_strided(reinterpret_cast<char*>(symm_at(s, reinterpret_cast<char*>(dst_local), peer)),
-                     reinterpret_cast<const char*>(src), bytes, 0, 1);
+  char* dst = symm_at_checked(s, reinterpret_cast<char*>(dst_local), bytes, peer, 101);
+  if (dst != nullptr) copy_bytes_strided(dst, reinterpret_cast<const char*>(src), bytes, 0, 1);
 }
 // getmem: copy from the heap object `src_local` on `peer` into local memory `dst`.
 TDB_DEVICE void getmem_block(const SymmInfo& s, void* dst, const void* src_local, uint64_t bytes, int peer) {
-  copy_bytes_strided(reinterpret_cast<char*>(dst),
-                     reinterpret_cast<const char*>(
-                         symm_at(s, const_cast<char*>(reinterpret_cast<const char*>(src_local)), peer)),
-                     bytes, threadIdx.x, blockDim.x);
+  const char* src = symm_at_checked(s, const_cast<char*>(reinterpret_cast<const char*>(src_local)), bytes, peer, 102);
+  if (src != nullptr) copy_bytes_strided(reinterpret_cast<char*>(dst), src, bytes, threadIdx.x, blockDim.x);
 }
 TDB_DEVICE void getmem_warp(const SymmInfo& s, void* dst, const void* src_local, uint64_t bytes, int peer) {
-  copy_bytes_strided(reinterpret_cast<char*>(dst),
-                     reinterpret_cast<const char*>(
-                         symm_at(s, const_cast<char*>(reinterpret_cast<const char*>(src_local)), peer)),
-                     bytes, lane_id(), 32);
+  const char* src = symm_at_checked(s, const_cast<char*>(reinterpret_cast<const char*>(src_local)), bytes, peer, 102);
+  if (src != nullptr) copy_bytes_strided(reinterpret_cast<char*>(dst), src, bytes, lane_id(), 32);
 }
 // putmem_signal: data, then a signal that the receiver can wait for.
 TDB_DEVICE void putmem_signal_block(const SymmInfo& s, void* dst_local, const void* src, uint64_t bytes,

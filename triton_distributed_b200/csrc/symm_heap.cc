@@ -393,6 +393,11 @@ SymmInfoHost SymmHeap::info(uint64_t timeout_ns) const {
   s.rank = rank_;
   s.world = world_;
   s.timeout_ns = timeout_ns;
+  static const bool debug = [] {
+    const char* e = std::getenv("TDB200_DEBUG");
+    return e != nullptr && std::atoi(e) != 0;
+  }();
+  s.debug = debug ? 1u : 0u;
   return s;
 }
 

@@ -236,6 +236,9 @@ def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelCo
         n_comm = max(1, min(n_comm, n_sms - 1))
         if pair and n_comm % 2:
             n_comm += 1
+    if rt.config.debug:
+        from .common import poison_unused_parity
+        poison_unused_parity(ctx.workspace, ctx.calls)
     lib.ag_gemm_bf16(rt.heap, a, b, out, ctx.workspace, ctx.flags, ctx.ctx_dev, ctx.max_seg_rows, ctx.max_chunks,
                      n_comm, 512 if pair else ctx.BLOCK_N, n_sms, mc,
                      rt.config.wait_timeout_s, ctx.stats)

@@ -16,6 +16,20 @@ def new_ctx_dev(rt: Runtime) -> torch.Tensor:
     return t
 
 
+def poison_unused_parity(buf: torch.Tensor, calls: int) -> None:
+    """Debug aid (``TDB200_DEBUG=1``): ``buf`` is a double-buffered heap object ``[2, ...]`` whose half ``epoch & 1`` the
+    call with epoch ``calls + 1`` uses.  Fill the OTHER half with NaN (0xFF bytes for integer / fp8 data) before the
+    launch, in stream order.  That half was last written for the previous call, which this rank has finished, and no
+    peer can write it again before this rank's launch of the current call has pushed its data (a peer's next call
+    needs them), so the fill races with nothing; a kernel that reads a stale or wrong-parity tile then produces NaN
+    instead of plausible numbers.  Eager mode only: under CUDA-graph replay the host's call count is not the epoch."""
+    half = buf[(calls + 1) & 1 ^ 1]
+    if half.dtype.is_floating_point and half.element_size() >= 2:
+        half.fill_(float("nan"))
+    else:
+        half.view(torch.uint8).fill_(0xFF)
+
+
 def sm_count(device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 

@@ -122,6 +122,9 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParall
     if out is None:
         out = torch.empty((M // W, N), dtype=a.dtype, device=a.device)
     pair = use_cta_pair(ctx.kernel_form, M // W, N, out)
+    if rt.config.debug:
+        from .common import poison_unused_parity
+        poison_unused_parity(ctx.slots, ctx.calls)
     lib.gemm_rs_bf16(rt.heap, a, b, out, ctx.slots, ctx.flags, ctx.ctx_dev, ctx.max_seg_rows, ctx.max_tiles,
                      512 if pair else ctx.BLOCK_N, ctx.num_ctas or sm_count(a.device), rt.config.wait_timeout_s, ctx.stats)
     ctx.calls += 1
