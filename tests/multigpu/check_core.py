@@ -281,19 +281,25 @@ def check_dist_decode(rt):
     for r in range(W):
         for b in range(B):
             global_kv_lens[r, b] = max(0, min(per[b], lens_global[b] - r * per[b]))
-    for it in range(3):
-        out = layer.forward(q, k_cache, v_cache, global_kv_lens, bt)
-        torch.cuda.synchronize()
-        rt.check_status()
     # oracle: plain attention over the full KV
     kf = k_full.float().repeat_interleave(Hq // Hkv, dim=2)
     vf = v_full.float().repeat_interleave(Hq // Hkv, dim=2)
+    refs = []
     for b in range(B):
         n = lens_global[b]
         s = torch.einsum("hd,khd->hk", q[b].float(), kf[b, :n]) / (D ** 0.5)
-        ref = torch.einsum("hk,khd->hd", torch.softmax(s, -1), vf[b, :n])
-        err = (out[b].float() - ref).abs().max().item()
-        assert err < 3e-2, f"dist flash decode b={b}: err {err}"
+        refs.append(torch.einsum("hk,khd->hd", torch.softmax(s, -1), vf[b, :n]))
+    # the one-launch form (split-KV + exchange + merge in one kernel) and the two-launch form, alternating on the same
+    # staging buffers and epoch counter
+    for it in range(6):
+        layer.one_launch = it % 3 != 2
+        out = layer.forward(q, k_cache, v_cache, global_kv_lens, bt)
+        torch.cuda.synchronize()
+        rt.check_status()
+        assert layer.last_launches == (1 if layer.one_launch else 2), layer.last_launches
+        for b in range(B):
+            err = (out[b].float() - refs[b]).abs().max().item()
+            assert err < 3e-2, f"dist flash decode (launches={layer.last_launches}) it={it} b={b}: err {err}"
     log(rt, "OK distributed flash-decode")
 
 

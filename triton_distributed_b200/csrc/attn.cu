@@ -116,16 +116,10 @@ __global__ void __launch_bounds__(kAttnThreads) flash_fwd_kernel(const PrefillPa
 // Decode, split-KV.  q [B, Hq, D].  grid = (splits, Hkv * head_chunks, B).  Partials: out [B, Hq, splits, D] fp32,
 // lse [B, Hq, splits].
 // ---------------------------------------------------------------------------
-template <int D, int S>
-__global__ void __launch_bounds__(kAttnThreads) decode_splitkv_kernel(const DecodeParams p) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  pdl_wait();   // q and the cache rows of the new token come from the previous kernel
-  auto sync = [] { __syncthreads(); };
-  decode_splitkv_body<D, decltype(sync), S>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem, sync);
-  if (p.fuse_counters == nullptr) return;
-  // ---- fused combine: the last CTA to arrive for this (sequence, KV head, head chunk) merges the splits
+// The last CTA to arrive for a (sequence, KV head, head chunk) merges the splits.  Returns true for that CTA only;
+// the counter is left at zero for the next call.
+__device__ bool splits_arrive_last(const DecodeParams& p) {
   __shared__ int s_last;
-  pdl_launch_dependents();
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -135,17 +129,24 @@ __global__ void __launch_bounds__(kAttnThreads) decode_splitkv_kernel(const Deco
     if (s_last) *ctr = 0;   // every arrival of this call has been counted: leave the counter clean for the next one
   }
   __syncthreads();
-  if (!s_last) return;
+  if (!s_last) return false;
   __threadfence();
-  // Merge: the partials come from other CTAs, so they are read at L2.  First the LSEs of all heads of the chunk
-  // go to shared memory and become weights, then every thread sums four output dims of one head over the splits
-  // with several independent 16-byte loads in flight.
+  return true;
+}
+
+// Merge of the split partials of one head chunk by its last CTA: the partials come from other CTAs, so they are read
+// at L2.  First the LSEs of all heads of the chunk go to shared memory and become weights, then every thread sums four
+// output dims of one head over the splits with several independent 16-byte loads in flight and hands the normalised
+// float4 to emit(head in chunk, b * Hq + head, float4 index, values, LSE of the head over all splits).
+template <int D, typename Emit>
+__device__ void merge_chunk(const DecodeParams& p, uint8_t* smem, Emit emit) {
   const int b = blockIdx.z;
   const int hkv = blockIdx.y / p.head_chunks, hc = blockIdx.y - hkv * p.head_chunks;
   const int h_begin = hkv * p.group + hc * 16;
   const int nheads = min(p.group - hc * 16, 16);
   float* s_w = reinterpret_cast<float*>(smem);          // [nheads][splits] weights
   float* s_inv = s_w + 16 * p.splits;                   // [nheads] 1 / total
+  float* s_lse = s_inv + 16;                            // [nheads] LSE over all splits
   for (int i = threadIdx.x; i < nheads * p.splits; i += kAttnThreads) {
     const int h = i / p.splits, sp = i - h * p.splits;
     s_w[i] = __ldcg(p.part_lse + (static_cast<int64_t>(b) * p.Hq + h_begin + h) * p.splits + sp);
@@ -162,6 +163,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_splitkv_kernel(const Deco
       tot += e;
     }
     s_inv[threadIdx.x] = tot > 0.f ? 1.f / tot : 0.f;
+    s_lse[threadIdx.x] = tot > 0.f ? mx + __logf(tot) : -INFINITY;
   }
   __syncthreads();
   constexpr int kVecPerHead = D / 4;                     // float4 per head row
@@ -188,10 +190,180 @@ __global__ void __launch_bounds__(kAttnThreads) decode_splitkv_kernel(const Deco
       acc.x += w[i] * v.x; acc.y += w[i] * v.y; acc.z += w[i] * v.z; acc.w += w[i] * v.w;
     }
     const float inv = s_inv[h];
-    uint2 o;
-    o.x = pack_bf16x2(acc.x * inv, acc.y * inv);
-    o.y = pack_bf16x2(acc.z * inv, acc.w * inv);
-    *reinterpret_cast<uint2*>(p.fuse_out + bh * D + dv * 4) = o;
+    emit(h, bh, dv, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv), s_lse[h]);
+  }
+}
+
+template <int D, int S>
+__global__ void __launch_bounds__(kAttnThreads) decode_splitkv_kernel(const DecodeParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  pdl_wait();   // q and the cache rows of the new token come from the previous kernel
+  auto sync = [] { __syncthreads(); };
+  decode_splitkv_body<D, decltype(sync), S>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem, sync);
+  if (p.fuse_counters == nullptr) return;
+  // ---- fused combine
+  pdl_launch_dependents();
+  if (!splits_arrive_last(p)) return;
+  merge_chunk<D>(p, smem, [&](int, int64_t bh, int dv, float4 o, float) {
+    uint2 r;
+    r.x = pack_bf16x2(o.x, o.y);
+    r.y = pack_bf16x2(o.z, o.w);
+    *reinterpret_cast<uint2*>(p.fuse_out + bh * D + dv * 4) = r;
+  });
+}
+
+// ---------------------------------------------------------------------------
+// Distributed flash-decode in ONE launch: split-KV over the local KV shard; the last CTA of every head chunk merges the
+// local splits, pushes (out[D], LSE) of its heads as packets {value, epoch} (8 bytes each, written two at a time) into
+// slot [rank] of every rank's staging, waits until all W slots of the local staging carry this call's epoch for its
+// heads, merges them by LSE and writes the bf16 output.  A CTA only ever waits for REMOTE data, whose producers do not
+// depend on this rank, but a waiting CTA keeps its SM: the host uses this form only while the head chunks
+// (batch x KV heads x chunks) fit the SMs, so that waiting CTAs can never keep this rank's own split CTAs from running.
+// staging: heap, [2][W][B*Hq][D+1] packets; buffer parity = epoch & 1; the last CTA out advances the epoch.
+// The reference runs the same tail as separate kernels (python/triton_dist/kernels/nvidia/flash_decode.py:587-760).
+// ---------------------------------------------------------------------------
+struct DistTail {
+  uint64_t* staging;
+  int64_t staging_half;   // packets per buffer
+  int BH;
+  CtxDev* ctx;
+  SymmInfo symm;
+};
+
+__device__ __forceinline__ void st_packet2(uint64_t* dst, uint64_t a, uint64_t b) {
+  asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(dst), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ void ld_packet2(const uint64_t* src, uint64_t& a, uint64_t& b) {
+  asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
+}
+// Wait for two adjacent packets of this call; false after the time limit (status recorded).
+__device__ bool wait_packet2(const DistTail& t, const uint64_t* src, uint32_t epoch, uint64_t t0, int slot, int index,
+                             float& v0, float& v1) {
+  uint64_t a, b;
+  uint32_t spins = 0;
+  while (true) {
+    ld_packet2(src, a, b);
+    if (static_cast<uint32_t>(a >> 32) == epoch && static_cast<uint32_t>(b >> 32) == epoch) break;
+    if ((++spins & 255u) == 0u && (abort_requested(t.symm) || globaltimer_ns() - t0 > t.symm.timeout_ns)) {
+      report(t.symm, kTimeoutFlag, kKernelFlashDecode, 2, slot, index, (int)epoch, (int)(a >> 32));
+      return false;
+    }
+  }
+  v0 = __uint_as_float(static_cast<uint32_t>(a));
+  v1 = __uint_as_float(static_cast<uint32_t>(b));
+  return true;
+}
+__device__ bool wait_packet1(const DistTail& t, const uint64_t* src, uint32_t epoch, uint64_t t0, int slot, int index,
+                             float& v) {
+  uint64_t a;
+  uint32_t spins = 0;
+  while (true) {
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(a) : "l"(src) : "memory");
+    if (static_cast<uint32_t>(a >> 32) == epoch) break;
+    if ((++spins & 255u) == 0u && (abort_requested(t.symm) || globaltimer_ns() - t0 > t.symm.timeout_ns)) {
+      report(t.symm, kTimeoutFlag, kKernelFlashDecode, 3, slot, index, (int)epoch, (int)(a >> 32));
+      return false;
+    }
+  }
+  v = __uint_as_float(static_cast<uint32_t>(a));
+  return true;
+}
+
+template <int D, int S>
+__global__ void __launch_bounds__(kAttnThreads) decode_splitkv_dist_kernel(const DecodeParams p, const DistTail t) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  pdl_wait();
+  auto sync = [] { __syncthreads(); };
+  decode_splitkv_body<D, decltype(sync), S>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem, sync);
+  pdl_launch_dependents();
+  if (splits_arrive_last(p)) {
+    // The epoch cannot advance before this CTA has counted itself out below.
+    const uint32_t epoch = ld_volatile(&t.ctx->epoch);
+    const int W = t.symm.world, rank = t.symm.rank;
+    uint64_t* st = t.staging + (epoch & 1) * t.staging_half;
+    // A row of D + 1 packets starts on an 8-byte boundary only (D + 1 is odd), so whether its packet pairs can be
+    // written with 16-byte stores depends on the row: decided from the address, which symm_at does not change mod 16.
+    const int64_t slot_stride = static_cast<int64_t>(t.BH) * (D + 1);
+    const uint64_t tag = static_cast<uint64_t>(epoch) << 32;
+    merge_chunk<D>(p, smem, [&](int, int64_t bh, int dv, float4 o, float lse) {
+      uint64_t* mine = st + rank * slot_stride + bh * (D + 1);
+      const bool even = (reinterpret_cast<uint64_t>(mine) & 15u) == 0;
+      const uint64_t p0 = tag | __float_as_uint(o.x), p1 = tag | __float_as_uint(o.y);
+      const uint64_t p2 = tag | __float_as_uint(o.z), p3 = tag | __float_as_uint(o.w);
+      for (int j = 0; j < W; ++j) {
+        uint64_t* dst = symm_at(t.symm, mine, (rank + j) % W) + dv * 4;
+        if (even) {
+          st_packet2(dst, p0, p1);
+          st_packet2(dst + 2, p2, p3);
+        } else {
+          asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(p0) : "memory");
+          st_packet2(dst + 1, p1, p2);
+          asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + 3), "l"(p3) : "memory");
+        }
+        if (dv == 0) {
+          const uint64_t pl = tag | __float_as_uint(lse);
+          asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + D), "l"(pl) : "memory");
+        }
+      }
+    });
+    // ---- receive: every thread owns four dims of one head per pass, as in the merge
+    constexpr int kVecPerHead = D / 4;
+    constexpr int kHeadsPerPass = kAttnThreads / kVecPerHead;
+    const int b = blockIdx.z;
+    const int hkv = blockIdx.y / p.head_chunks, hc = blockIdx.y - hkv * p.head_chunks;
+    const int h_begin = hkv * p.group + hc * 16;
+    const int nheads = min(p.group - hc * 16, 16);
+    const int dv = threadIdx.x % kVecPerHead, sub = threadIdx.x / kVecPerHead;
+    const uint64_t t0 = globaltimer_ns();
+    for (int h = sub; h < nheads; h += kHeadsPerPass) {
+      const int64_t bh = static_cast<int64_t>(b) * p.Hq + h_begin + h;
+      float lse_s[kMaxRanks];
+      float mx = -INFINITY;
+      bool ok = true;
+      for (int s = 0; s < W && ok; ++s) {
+        ok = wait_packet1(t, st + s * slot_stride + bh * (D + 1) + D, epoch, t0, s, static_cast<int>(bh), lse_s[s]);
+        if (ok) mx = fmaxf(mx, lse_s[s]);
+      }
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      float tot = 0.f;
+      for (int s = 0; s < W && ok; ++s) {
+        const uint64_t* row = st + s * slot_stride + bh * (D + 1);
+        const uint64_t* src = row + dv * 4;
+        float v0, v1, v2, v3;
+        if ((reinterpret_cast<uint64_t>(row) & 15u) == 0) {
+          ok = wait_packet2(t, src, epoch, t0, s, static_cast<int>(bh), v0, v1) &&
+               wait_packet2(t, src + 2, epoch, t0, s, static_cast<int>(bh), v2, v3);
+        } else {
+          ok = wait_packet1(t, src, epoch, t0, s, static_cast<int>(bh), v0) &&
+               wait_packet2(t, src + 1, epoch, t0, s, static_cast<int>(bh), v1, v2) &&
+               wait_packet1(t, src + 3, epoch, t0, s, static_cast<int>(bh), v3);
+        }
+        if (!ok) break;
+        const float wgt = (mx == -INFINITY) ? 0.f : __expf(lse_s[s] - mx);
+        tot += wgt;
+        acc.x += wgt * v0; acc.y += wgt * v1; acc.z += wgt * v2; acc.w += wgt * v3;
+      }
+      if (ok) {
+        const float inv = tot > 0.f ? 1.f / tot : 0.f;
+        uint2 r;
+        r.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+        r.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(p.fuse_out + bh * D + dv * 4) = r;
+      }
+    }
+  }
+  // every CTA counts itself out; the last one advances the call epoch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
+    const uint32_t prev = atomicAdd(&t.ctx->done, 1u);
+    if (prev == total - 1) {
+      const uint32_t epoch = ld_volatile(&t.ctx->epoch);
+      t.ctx->done = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(&t.ctx->epoch) = epoch + 1;
+    }
   }
 }
 
@@ -356,7 +528,9 @@ int decode_workspace_floats(int batch, int num_q_heads, int head_dim, int splits
   return batch * num_q_heads * splits * (head_dim + 1);
 }
 
-cudaError_t launch_decode_splitkv(const DecodeArgs& a, cudaStream_t stream) {
+namespace {
+// Shared by the local and the one-launch distributed form.  `tail` == nullptr: local.
+cudaError_t launch_splitkv_impl(const DecodeArgs& a, const DistTail* tail, cudaStream_t stream) {
   if (a.head_dim != 64 && a.head_dim != 128) return cudaErrorInvalidValue;
   if (a.num_q_heads % a.kv.num_kv_heads != 0 || a.splits < 1) return cudaErrorInvalidValue;
   if (a.batch == 0) return cudaSuccess;
@@ -380,6 +554,22 @@ cudaError_t launch_decode_splitkv(const DecodeArgs& a, cudaStream_t stream) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const bool deep = static_cast<int64_t>(grid.x) * grid.y * grid.z <= sms;
+  if (tail != nullptr) {
+    // the merge tail keeps 16 * splits + 32 floats in shared memory; waiting chunk CTAs must leave SMs for the rest
+    if (p.fuse_counters == nullptr || static_cast<int64_t>(grid.y) * grid.z > sms) return cudaErrorInvalidValue;
+    auto launch = [&](auto kernel, int smem, SmemOptIn* set) -> cudaError_t {
+      cudaError_t e = ensure_smem(kernel, smem, set);
+      if (e != cudaSuccess) return e;
+      return launch_pdl(kernel, grid, dim3(kAttnThreads), static_cast<size_t>(smem), stream, p, *tail);
+    };
+    static SmemOptIn d128_2, d128_4, d64_2, d64_4;
+    if (a.head_dim == 128) {
+      return deep ? launch(decode_splitkv_dist_kernel<128, 4>, 2 * Tiles<128>::kSmem, &d128_4)
+                  : launch(decode_splitkv_dist_kernel<128, 2>, Tiles<128>::kSmem, &d128_2);
+    }
+    return deep ? launch(decode_splitkv_dist_kernel<64, 4>, 2 * Tiles<64>::kSmem, &d64_4)
+                : launch(decode_splitkv_dist_kernel<64, 2>, Tiles<64>::kSmem, &d64_2);
+  }
   auto launch = [&](auto kernel, int smem, SmemOptIn* set) -> cudaError_t {
     cudaError_t e = ensure_smem(kernel, smem, set);
     if (e != cudaSuccess) return e;
@@ -392,6 +582,23 @@ cudaError_t launch_decode_splitkv(const DecodeArgs& a, cudaStream_t stream) {
   }
   return deep ? launch(decode_splitkv_kernel<64, 4>, 2 * Tiles<64>::kSmem, &set64_4)
               : launch(decode_splitkv_kernel<64, 2>, Tiles<64>::kSmem, &set64_2);
+}
+}  // namespace
+
+cudaError_t launch_decode_splitkv(const DecodeArgs& a, cudaStream_t stream) { return launch_splitkv_impl(a, nullptr, stream); }
+
+cudaError_t launch_dist_decode_fused(const DecodeArgs& a, void* staging, int64_t staging_half_packets, CtxDev* ctx,
+                                     const SymmInfoHost& symm, cudaStream_t stream) {
+  if (a.batch == 0) return cudaSuccess;
+  DistTail t;
+  t.staging = reinterpret_cast<uint64_t*>(staging);
+  t.staging_half = staging_half_packets;
+  t.BH = a.batch * a.num_q_heads;
+  t.ctx = ctx;
+  static_assert(sizeof(SymmInfo) == sizeof(SymmInfoHost), "SymmInfo mirrors must match");
+  memcpy(&t.symm, &symm, sizeof(SymmInfo));
+  if (static_cast<int64_t>(symm.world) * t.BH * (a.head_dim + 1) > staging_half_packets) return cudaErrorInvalidValue;
+  return launch_splitkv_impl(a, &t, stream);
 }
 
 cudaError_t launch_decode_combine(const DecodeArgs& a, void* out_bf16, float* out_lse, float* out_f32,

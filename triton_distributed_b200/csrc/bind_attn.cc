@@ -121,18 +121,39 @@ void decode_attn(const at::Tensor& q, const at::Tensor& k_cache, const at::Tenso
              "launch_decode_combine");
 }
 
-// Distributed flash-decode: local split-KV, then the fused combine + cross-rank exchange + LSE merge.
-void dist_decode_attn(SymmHeap& h, const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
-                      const at::Tensor& block_table, const at::Tensor& kv_lens, at::Tensor& workspace, int64_t splits,
-                      double scale, double softcap, at::Tensor& out, at::Tensor& staging, at::Tensor& ctx,
-                      double timeout_s) {
+// Distributed flash-decode.  With `counters` (int32, batch x KV heads x head chunks, zero) and a problem whose head
+// chunks fit the SMs: ONE launch (split-KV, local merge, packet exchange, cross-rank merge).  Otherwise split-KV and
+// the exchange + merge kernel.  Returns the number of launches.
+int64_t dist_decode_attn(SymmHeap& h, const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
+                         const at::Tensor& block_table, const at::Tensor& kv_lens, at::Tensor& workspace, int64_t splits,
+                         double scale, double softcap, at::Tensor& out, at::Tensor& staging, at::Tensor& ctx,
+                         double timeout_s, c10::optional<at::Tensor> counters) {
   c10::cuda::CUDAGuard guard(q.device());
   tdb::DecodeArgs a = decode_args(q, k_cache, v_cache, block_table, kv_lens, workspace, splits, scale, softcap);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous(), "dist_decode_attn: out must be contiguous bf16");
+  const int64_t half = staging.numel() * staging.element_size() / 16;
+  const auto info = h.info(static_cast<uint64_t>(timeout_s * 1e9));
+  if (counters.has_value()) {
+    const int64_t group = a.num_q_heads / k_cache.size(2);
+    const int64_t chunks = static_cast<int64_t>(a.batch) * k_cache.size(2) * ((group + 15) / 16);
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (chunks <= sms && splits <= 64) {
+      TORCH_CHECK(counters->scalar_type() == at::kInt && counters->numel() >= chunks, "dist_decode_attn: counters too small");
+      a.fuse_counters = reinterpret_cast<uint32_t*>(counters->data_ptr());
+      a.fuse_out = out.data_ptr();
+      check_cuda(tdb::launch_dist_decode_fused(a, staging.data_ptr(), half, reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr()),
+                                               info, cur_stream()),
+                 "launch_dist_decode_fused");
+      return 1;
+    }
+  }
   check_cuda(tdb::launch_decode_splitkv(a, cur_stream()), "launch_decode_splitkv");
-  check_cuda(tdb::launch_dist_combine(a, out.data_ptr(), staging.data_ptr(), staging.numel() * staging.element_size() / 16,
-                                      reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr()),
-                                      h.info(static_cast<uint64_t>(timeout_s * 1e9)), cur_stream()),
+  check_cuda(tdb::launch_dist_combine(a, out.data_ptr(), staging.data_ptr(), half,
+                                      reinterpret_cast<tdb::CtxDev*>(ctx.data_ptr()), info, cur_stream()),
              "launch_dist_combine");
+  return 2;
 }
 
 }  // namespace
@@ -140,6 +161,9 @@ void dist_decode_attn(SymmHeap& h, const at::Tensor& q, const at::Tensor& k_cach
 void bind_attn(py::module_& m) {
   m.def("flash_fwd", &flash_fwd);
   m.def("decode_attn", &decode_attn);
-  m.def("dist_decode_attn", &dist_decode_attn);
+  m.def("dist_decode_attn", &dist_decode_attn, py::arg("heap"), py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
+        py::arg("block_table"), py::arg("kv_lens"), py::arg("workspace"), py::arg("splits"), py::arg("scale"),
+        py::arg("softcap"), py::arg("out"), py::arg("staging"), py::arg("ctx"), py::arg("timeout_s"),
+        py::arg("counters") = py::none());
   m.def("decode_workspace_floats", &tdb::decode_workspace_floats);
 }

@@ -51,4 +51,9 @@ cudaError_t launch_decode_combine(const DecodeArgs& a, void* out_bf16, float* ou
 cudaError_t launch_dist_combine(const DecodeArgs& a, void* out_bf16, void* staging, int64_t staging_half_packets,
                                 CtxDev* ctx, const SymmInfoHost& symm, cudaStream_t stream);
 
+// The whole distributed flash-decode step in one launch (a.fuse_counters and a.fuse_out must be set): usable while
+// batch x KV heads x head chunks <= SM count, cudaErrorInvalidValue otherwise.
+cudaError_t launch_dist_decode_fused(const DecodeArgs& a, void* staging, int64_t staging_half_packets, CtxDev* ctx,
+                                     const SymmInfoHost& symm, cudaStream_t stream);
+
 }  // namespace tdb

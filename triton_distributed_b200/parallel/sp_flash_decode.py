@@ -1,9 +1,12 @@
 """Distributed flash-decode layer: KV sharded over ranks, one query token per sequence.
 
 API of the reference: ``SpGQAFlashDecodeAttention`` (python/triton_dist/layers/nvidia/sp_flash_decode_layer.py:44-185).
-Each rank runs split-KV attention over its KV shard; one more launch merges the local splits, exchanges the
-per-rank (out, LSE) as low-latency packets with in-band flags and merges the W partials (``csrc/attn.cu``
-``dist_combine_kernel``) - the reference needs a separate LL all-gather kernel plus a combine kernel.
+Each rank runs split-KV attention over its KV shard.  While the head chunks (batch x KV heads x ceil(group / 16)) fit
+the SMs the whole step is ONE launch (``csrc/attn.cu`` ``decode_splitkv_dist_kernel``): the last split CTA of a head
+chunk merges the local splits, pushes (out, LSE) to every rank as 8-byte packets with the call epoch in band, waits for
+the W packets of its heads and merges them by LSE.  Larger problems use split-KV plus one exchange-and-merge launch
+(``dist_combine_kernel``).  The reference runs split-KV, a combine, an LL all-gather and a second combine
+(python/triton_dist/kernels/nvidia/flash_decode.py:587-760, sp_flash_decode_layer.py:120-185).
 """
 from __future__ import annotations
 
@@ -35,10 +38,15 @@ class SpGQAFlashDecodeAttention:
         self.staging = None
         self.ctx_dev = None
         self.workspace = None
+        self.counters = None
+        self.one_launch = True      # False forces the two-launch form (benchmarks compare the two)
+        self.last_launches = 0
         if self.rt.is_cuda and num_ranks > 1:
             packets = num_ranks * max_allowed_batch * num_q_heads * (q_head_dim + 1)
             self.staging = self.rt.symm_tensor((2, packets, 2), torch.int32)   # 8-byte packets
             self.ctx_dev = new_ctx_dev(self.rt)
+            chunks = max_allowed_batch * num_kv_heads * ((num_q_heads // num_kv_heads + 15) // 16)
+            self.counters = torch.zeros(chunks, dtype=torch.int32, device=self.rt.device)
             torch.cuda.synchronize()
             self.rt.host_barrier()
 
@@ -69,9 +77,10 @@ class SpGQAFlashDecodeAttention:
             lib.decode_attn(q.contiguous(), k_cache, v_cache, block_table, local_lens, self.workspace, splits,
                             float(self.scale), float(self.soft_cap), out, None, None, None)
             return out
-        lib.dist_decode_attn(self.rt.heap, q.contiguous(), k_cache, v_cache, block_table, local_lens, self.workspace,
-                             splits, float(self.scale), float(self.soft_cap), out, self.staging, self.ctx_dev,
-                             self.rt.config.wait_timeout_s)
+        self.last_launches = lib.dist_decode_attn(
+            self.rt.heap, q.contiguous(), k_cache, v_cache, block_table, local_lens, self.workspace, splits,
+            float(self.scale), float(self.soft_cap), out, self.staging, self.ctx_dev, self.rt.config.wait_timeout_s,
+            self.counters if self.one_launch else None)
         return out
 
     __call__ = forward
