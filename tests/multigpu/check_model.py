@@ -92,7 +92,7 @@ def check_megakernel(rt, cfg):
         for c in caches:
             model.inference(prompt, pos, c)
             c.inc_offset(21)
-        mega = Qwen3Model(model, caches[1], Bm)
+        mega = Qwen3Model(model, caches[1], Bm, prefetch=(Bm == 16))
         tok = prompt[:, :1].contiguous()
         for step in range(4):
             ref_l = model.inference(tok, caches[0].kv_offset.to(torch.int64).unsqueeze(1), caches[0])
@@ -107,6 +107,39 @@ def check_megakernel(rt, cfg):
         rt.host_barrier()
     if rt.rank == 0:
         print("megakernel matches the layer-wise decode on", W, "ranks", flush=True)
+    check_mega_aux_tasks(rt)
+
+
+def check_mega_aux_tasks(rt):
+    """Stand-alone all-reduce, rank-barrier and prefetch tasks of the megakernel across ranks, with and without NVLS."""
+    import torch.distributed as dist
+    from triton_distributed_b200.mega import ModelBuilder
+
+    W, dev = rt.world_size, rt.device
+    B, K, N = 7, 256, 2048 + 128
+    g = torch.Generator(device=dev).manual_seed(11 + rt.rank)
+    x = torch.randn(B, K, device=dev, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    for use_mc in (True, False):
+        part = torch.zeros(B, N, device=dev, dtype=torch.bfloat16)
+        out = torch.zeros(B, N, device=dev, dtype=torch.bfloat16)
+        b = ModelBuilder(B, use_multimem=use_mc)
+        b.make_prefetch(w)
+        b.make_linear(x, w, part)                       # local partial product, no fused all-reduce
+        b.make_barrier_all_intra_node()
+        b.make_allreduce(part, out, chunk_cols=512)
+        b.compile()
+        for it in range(3):
+            b.run()
+            torch.cuda.synchronize()
+            rt.check_status()
+            ref = part.float().clone()
+            dist.all_reduce(ref, group=rt.group)
+            err = (out.float() - ref).abs().max().item()
+            assert err < 2e-2 * ref.abs().max().item() + 1e-3, f"mega all-reduce task (nvls={use_mc}) it={it}: {err}"
+        rt.host_barrier()
+    if rt.rank == 0:
+        print("megakernel all-reduce / barrier / prefetch tasks OK on", W, "ranks", flush=True)
 
 
 if __name__ == "__main__":

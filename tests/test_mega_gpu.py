@@ -29,7 +29,7 @@ def test_megakernel_matches_layerwise_decode(rt, batch):
     for c in caches:
         model.inference(prompt, pos, c)
         c.inc_offset(9)
-    mega = Qwen3Model(model, caches[1], batch, enable_profiling=(batch == 3))
+    mega = Qwen3Model(model, caches[1], batch, enable_profiling=(batch == 3), prefetch=(batch in (1, 20)))
     tok = torch.randint(0, 1000, (batch, 1), device=rt.device)
     for step in range(3):
         ref = model.inference(tok, caches[0].kv_offset.to(torch.int64).unsqueeze(1), caches[0])
@@ -47,3 +47,34 @@ def test_megakernel_matches_layerwise_decode(rt, batch):
         act = mega.builder.get_sm_activity()
         assert len(act) > 0 and all(0 <= v <= 1.0001 for v in act.values())
         assert sum(mega.builder.tasks_per_sm()) > 0
+
+
+def test_builder_prefetch_barrier_allreduce_lm_head_tasks(rt, tmp_path):
+    """The auxiliary task types on their own: L2 prefetch (no visible effect, must not disturb anything), rank barrier,
+    stand-alone all-reduce (one rank: the sum is the input) and the LM-head linear, against PyTorch."""
+    from triton_distributed_b200.mega import ModelBuilder
+
+    B, K, N = 5, 512, 1024 + 256
+    dev = rt.device
+    g = torch.Generator(device=dev).manual_seed(3)
+    x = torch.randn(B, K, device=dev, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    big = torch.randn(3 * 1024 * 1024 + 8, device=dev, generator=g).to(torch.bfloat16)    # 6 MB + a ragged tail
+    logits = torch.zeros(B, N, device=dev, dtype=torch.bfloat16)
+    summed = torch.zeros(B, N, device=dev, dtype=torch.bfloat16)
+    b = ModelBuilder(B, enable_profiling=True)
+    st_p = b.make_prefetch(big)
+    st_l = b.make_lm_head(x, w, logits)
+    st_b = b.make_barrier_all_intra_node()
+    st_a = b.make_allreduce(logits, summed, chunk_cols=512)
+    assert len({st_p, st_l, st_b, st_a}) == 4
+    b.compile()
+    for _ in range(2):
+        b.run()
+        torch.cuda.synchronize()
+        rt.check_status()
+    ref = (x.float() @ w.float().t())
+    torch.testing.assert_close(logits.float(), ref, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(summed.float() / rt.world_size, logits.float(), rtol=1e-2, atol=1e-2)
+    names = {e["name"] for e in b.dump_trace(str(tmp_path / "trace.json"))["traceEvents"]}
+    assert {"prefetch_l2", "barrier_all", "all_reduce", "linear"} <= names, names

@@ -240,12 +240,169 @@ __global__ void ep_gather_rows_kernel(const uint8_t* __restrict__ recv_x_base, c
 }
 
 // ---------------------------------------------------------------------------
+// Receive side in one launch: from the per-(local expert, source) counts alone, lay the received rows out for the
+// grouped GEMM (rows sorted by local expert, every expert padded to 128 rows), de-quantising fp8 rows on the way.
+// The receive areas are already grouped by (expert, source), so the place of every row follows from a prefix sum over
+// at most epr * W counts that every CTA recomputes in shared memory; nothing scans the receive capacity.
+// One warp moves one row.  Block 0 also writes the layout tensors (sorted_ids are receive-row indices, -1 = padding).
+// ---------------------------------------------------------------------------
+constexpr int kFinishMaxBlocks = 2048;    // epr * W
+constexpr int kFinishMaxExperts = 256;    // epr
+
+struct FinishParams {
+  const uint8_t* recv_x;
+  const float* recv_scale;
+  const int32_t* recv_count;
+  const int32_t* base_self;    // packed layout: first receive row of every (expert, source) block; null = fixed stride
+  int epr, W, max_tokens, H, quant;
+  int64_t rows_per_parity;
+  const CtxDev* dctx;
+  __nv_bfloat16* x_sorted;     // [cap, H]
+  int32_t* sorted_ids;         // [cap]
+  int32_t* tile_expert;        // [cap / 128]
+  int32_t* offsets;            // [epr + 1]
+  int32_t* counts;             // [epr]
+  int32_t* meta;               // {padded rows, tiles}
+  int64_t cap;                 // multiple of 128
+};
+
+__global__ void __launch_bounds__(kEpThreads) ep_finish_kernel(const FinishParams p) {
+  __shared__ int s_cnt[kFinishMaxBlocks];        // tokens of (le, src)
+  __shared__ int s_in[kFinishMaxBlocks];         // rows of the same expert from earlier sources
+  __shared__ int s_tot[kFinishMaxExperts];       // tokens of the expert
+  __shared__ int s_off[kFinishMaxExperts + 1];   // padded first row of the expert
+  const int par = last_parity(p.dctx);
+  const int epr = p.epr, W = p.W, nblk = epr * W;
+  const int32_t* rc = p.recv_count + par * nblk;
+  for (int i = threadIdx.x; i < nblk; i += kEpThreads) {
+    int c = rc[i];
+    s_cnt[i] = c < 0 ? 0 : c;
+  }
+  __syncthreads();
+  for (int le = threadIdx.x; le < epr; le += kEpThreads) {
+    int acc = 0;
+    for (int sr = 0; sr < W; ++sr) {
+      s_in[le * W + sr] = acc;
+      acc += s_cnt[le * W + sr];
+    }
+    s_tot[le] = acc;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int64_t acc = 0;
+    for (int le = 0; le < epr; ++le) {
+      s_off[le] = static_cast<int>(acc);
+      int64_t nxt = acc + (static_cast<int64_t>(s_tot[le]) + 127) / 128 * 128;
+      if (nxt > p.cap) {          // cannot happen with a capacity of min(receive rows, W * tokens * k) + epr * 127 rows;
+        s_tot[le] = 0;            // an expert that would not fit is dropped rather than written out of bounds
+        nxt = acc;
+      }
+      acc = nxt;
+    }
+    s_off[epr] = static_cast<int>(acc);
+  }
+  __syncthreads();
+  const int R = s_off[epr];
+  if (blockIdx.x == 0) {
+    for (int le = threadIdx.x; le < epr; le += kEpThreads) {
+      p.offsets[le] = s_off[le];
+      p.counts[le] = s_tot[le];
+    }
+    if (threadIdx.x == 0) {
+      p.offsets[epr] = R;
+      p.meta[0] = R;
+      p.meta[1] = R / 128;
+    }
+    const int max_tiles = static_cast<int>(p.cap / 128);
+    for (int t = threadIdx.x; t < max_tiles; t += kEpThreads) {
+      int ex = -1;
+      if (t * 128 < R) {
+        int lo = 0, hi = epr - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (s_off[mid] <= t * 128) lo = mid; else hi = mid - 1;
+        }
+        ex = lo;
+      }
+      p.tile_expert[t] = ex;
+    }
+  }
+  const int row_bytes = p.quant ? p.H : 2 * p.H;
+  const int nsc = p.H / kQuantBlock;
+  const uint8_t* recv_x = p.recv_x + par * p.rows_per_parity * row_bytes;
+  const float* recv_scale = p.recv_scale + par * p.rows_per_parity * nsc;
+  const int warps = kEpThreads / 32, lane = threadIdx.x & 31;
+  for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
+    int lo = 0, hi = epr - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_off[mid] <= r) lo = mid; else hi = mid - 1;
+    }
+    // several experts may share a start row (empty ones): the last of them is the one with rows
+    const int le = lo;
+    const int j = r - s_off[le];
+    uint4* dst = reinterpret_cast<uint4*>(p.x_sorted + static_cast<int64_t>(r) * p.H);
+    if (j >= s_tot[le]) {
+      if (lane == 0) p.sorted_ids[r] = -1;
+      for (int i = lane; i < (p.H >> 3); i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    int sr = 0;
+    while (sr + 1 < W && s_in[le * W + sr + 1] <= j) ++sr;
+    const int i_in = j - s_in[le * W + sr];
+    const int64_t id = p.base_self ? static_cast<int64_t>(p.base_self[le * W + sr]) + i_in
+                                   : (static_cast<int64_t>(le) * W + sr) * p.max_tokens + i_in;
+    if (lane == 0) p.sorted_ids[r] = static_cast<int32_t>(id);
+    if (!p.quant) {
+      const uint4* src = reinterpret_cast<const uint4*>(recv_x + id * row_bytes);
+      int i = lane;
+      for (; i + 96 < (p.H >> 3); i += 128) {
+        const uint4 v0 = src[i], v1 = src[i + 32], v2 = src[i + 64], v3 = src[i + 96];
+        dst[i] = v0; dst[i + 32] = v1; dst[i + 64] = v2; dst[i + 96] = v3;
+      }
+      for (; i < (p.H >> 3); i += 32) dst[i] = src[i];
+      continue;
+    }
+    // fp8 row: a lane turns 16 values (one 16-byte load, inside one 128-value scale block) into two 16-byte stores
+    const uint4* q = reinterpret_cast<const uint4*>(recv_x + id * row_bytes);
+    const float* sc = recv_scale + id * nsc;
+    for (int i0 = 0; i0 < (p.H >> 4); i0 += 128) {
+      uint4 w[4];
+      float scl[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * 32 + lane;
+        const bool in = i < (p.H >> 4);
+        w[u] = in ? q[i] : make_uint4(0u, 0u, 0u, 0u);
+        scl[u] = in ? sc[i >> 3] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * 32 + lane;
+        if (i >= (p.H >> 4)) break;
+        const uint32_t ws[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+        uint32_t o[8];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          o[2 * c] = pack_bf16x2(fp8_to_float(ws[c] & 0xff) * scl[u], fp8_to_float((ws[c] >> 8) & 0xff) * scl[u]);
+          o[2 * c + 1] = pack_bf16x2(fp8_to_float((ws[c] >> 16) & 0xff) * scl[u], fp8_to_float(ws[c] >> 24) * scl[u]);
+        }
+        dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Combine: y_sorted rows (expert outputs, bf16) go back to the source rank of their token, into ret[pair]; when all
 // expert ranks have flagged, every CTA reduces its share of the local tokens: out[t] = sum_j w[t,j] * ret[t*k+j].
 // ---------------------------------------------------------------------------
 struct CombineParams {
   const __nv_bfloat16* y;        // [rows_sorted, H] expert outputs in the sorted layout
-  const int32_t* pos_of;         // [recv rows] sorted row of every receive row (-1: no token)
+  const int32_t* pos_of;         // [recv rows] sorted row of every receive row (-1: no token); unused with sorted_ids
+  const int32_t* sorted_ids;     // optional [sorted rows] receive row of every sorted row (-1: padding): the send loop
+  const int32_t* sort_meta;      //   then walks the sort_meta[0] sorted rows instead of the whole receive capacity
   const int32_t* recv_meta;      // [2][recv rows] pair index at the source (parity of the matching dispatch)
   const CtxDev* dctx;            // the dispatch context (gives that parity)
   const int32_t* base_self;      // packed layout: [epr*W] first row of block; null = fixed stride
@@ -282,17 +439,25 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const CombinePar
     if (lane == 0) chunk = atomicAdd(work, 1u);
     chunk = __shfl_sync(0xffffffffu, chunk, 0);
     const int64_t r_base = static_cast<int64_t>(chunk) * 32;
-    if (r_base >= p.recv_rows) break;
+    const int64_t domain = p.sorted_ids ? static_cast<int64_t>(p.sort_meta[0]) : p.recv_rows;
+    if (r_base >= domain) break;
     const int64_t r_mine = r_base + lane;
-    const int pos_mine = r_mine < p.recv_rows ? p.pos_of[r_mine] : -1;
-    const int pair_mine = pos_mine >= 0 ? recv_meta[r_mine] : 0;
+    int pos_mine = -1;
+    int64_t id_mine = r_mine;      // receive row
+    if (p.sorted_ids) {
+      id_mine = r_mine < domain ? p.sorted_ids[r_mine] : -1;
+      pos_mine = id_mine >= 0 ? static_cast<int>(r_mine) : -1;
+    } else if (r_mine < domain) {
+      pos_mine = p.pos_of[r_mine];
+    }
+    const int pair_mine = pos_mine >= 0 ? recv_meta[id_mine] : 0;
     uint32_t valid = __ballot_sync(0xffffffffu, pos_mine >= 0);
     while (valid) {
       const int l = __ffs(valid) - 1;
       valid &= valid - 1;
       const int pos = __shfl_sync(0xffffffffu, pos_mine, l);
       const int pair = __shfl_sync(0xffffffffu, pair_mine, l);
-      const int64_t r = r_base + l;
+      const int64_t r = __shfl_sync(0xffffffffu, id_mine, l);
       int src;
       if (p.base_self == nullptr) {
         src = static_cast<int>((r / p.max_tokens) % W);
@@ -543,11 +708,38 @@ cudaError_t launch_ep_gather_rows(const void* recv_x, const float* recv_scale, c
   return cudaGetLastError();
 }
 
+cudaError_t launch_ep_finish(const EpFinishArgs& a, cudaStream_t s) {
+  if (a.H % 128 != 0 || a.cap % 128 != 0 || a.epr < 1 || a.epr > kFinishMaxExperts || a.epr * a.W > kFinishMaxBlocks)
+    return cudaErrorInvalidValue;
+  FinishParams p;
+  p.recv_x = reinterpret_cast<const uint8_t*>(a.recv_x);
+  p.recv_scale = a.recv_scale;
+  p.recv_count = a.recv_count;
+  p.base_self = a.base_self;
+  p.epr = a.epr; p.W = a.W; p.max_tokens = a.max_tokens; p.H = a.H; p.quant = a.quant;
+  p.rows_per_parity = a.rows_per_parity;
+  p.dctx = a.dispatch_ctx;
+  p.x_sorted = reinterpret_cast<__nv_bfloat16*>(a.x_sorted);
+  p.sorted_ids = a.sorted_ids;
+  p.tile_expert = a.tile_expert;
+  p.offsets = a.offsets;
+  p.counts = a.counts;
+  p.meta = a.meta;
+  p.cap = a.cap;
+  const int ctas = a.num_ctas > 0 ? a.num_ctas : 64;
+  ep_finish_kernel<<<ctas, kEpThreads, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_ep_combine(const EpCombineArgs& a, cudaStream_t s) {
   if (a.H % 8 != 0) return cudaErrorInvalidValue;
+  if (a.sorted_ids == nullptr && a.pos_of == nullptr) return cudaErrorInvalidValue;
+  if (a.sorted_ids != nullptr && a.sort_meta == nullptr) return cudaErrorInvalidValue;
   CombineParams p;
   p.y = reinterpret_cast<const __nv_bfloat16*>(a.y);
   p.pos_of = a.pos_of;
+  p.sorted_ids = a.sorted_ids;
+  p.sort_meta = a.sort_meta;
   p.recv_meta = a.recv_meta;
   p.dctx = a.dispatch_ctx;
   p.base_self = a.base_self;

@@ -32,9 +32,32 @@ cudaError_t launch_ep_gather_rows(const void* recv_x, const float* recv_scale, c
                                   void* out, int64_t rows_cap, int H, int quant, int64_t rows_per_parity,
                                   const CtxDev* dispatch_ctx, cudaStream_t s);
 
+// Receive side of a dispatch in one launch: grouped-GEMM layout (rows sorted by local expert, 128-row padding) built
+// from the per-(expert, source) counts, fp8 rows de-quantised on the way.  sorted_ids hold receive-row indices.
+struct EpFinishArgs {
+  const void* recv_x;
+  const float* recv_scale;
+  const int32_t* recv_count;  // heap [2][epr][W]
+  const int32_t* base_self;   // packed layout [epr * W], or null for the fixed-stride layout
+  int epr, W, max_tokens, H, quant;
+  int64_t rows_per_parity;
+  const CtxDev* dispatch_ctx;
+  void* x_sorted;             // bf16 [cap, H]
+  int32_t* sorted_ids;        // [cap]
+  int32_t* tile_expert;       // [cap / 128]
+  int32_t* offsets;           // [epr + 1]
+  int32_t* counts;            // [epr]
+  int32_t* meta;              // [2]
+  int64_t cap;                // multiple of 128
+  int num_ctas;
+};
+cudaError_t launch_ep_finish(const EpFinishArgs& a, cudaStream_t s);
+
 struct EpCombineArgs {
   const void* y;              // bf16 [sorted rows, H]
-  const int32_t* pos_of;      // [recv rows]
+  const int32_t* pos_of;      // [recv rows]; may be null when sorted_ids is given
+  const int32_t* sorted_ids = nullptr;   // [sorted rows] receive row per sorted row (-1 padding) + sort_meta {rows, tiles}:
+  const int32_t* sort_meta = nullptr;    //   the send loop walks the sorted rows instead of the receive capacity
   const int32_t* recv_meta;   // heap [2][recv rows]
   const CtxDev* dispatch_ctx;
   const int32_t* base_self;   // [E/W * W] packed layout, or null

@@ -16,6 +16,9 @@ enum MegaTaskType : int32_t {
   kTaskAttnSplit = 4,    // a0 = sequence, a1 = KV split, a2 = kv head * head chunks + chunk
   kTaskAttnCombine = 5,  // a0 = sequence
   kTaskSiluMul = 6,      // a0 = row
+  kTaskPrefetch = 7,     // a0 = chunk of the byte range that is requested into L2 (cp.async.bulk.prefetch.L2)
+  kTaskBarrier = 8,      // one task: barrier over all ranks (epoch flags in the heap)
+  kTaskAllReduce = 9,    // a0 = column chunk of a stand-alone all-reduce of a [batch, N] bf16 tensor
 };
 
 struct MegaTask {

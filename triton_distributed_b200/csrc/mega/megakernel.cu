@@ -225,6 +225,100 @@ TDB_DEVICE void task_attn_combine(const MegaOp& op, int b, int h0, int batch) {
   }
 }
 
+// L2 prefetch of chunk `chunk` of a byte range (the weights of an operator that runs later): the requests are
+// asynchronous, the task ends as soon as they are issued.  op.p[0] = base (16-byte aligned), op.i[0..1] = total bytes
+// (low / high word), op.i[2] = bytes per chunk (multiple of 2048).
+// Reference: mega_triton_kernel/kernels/prefetch.py:31-56.
+TDB_DEVICE void task_prefetch(const MegaOp& op, int chunk) {
+  const uint64_t total = (static_cast<uint64_t>(static_cast<uint32_t>(op.i[1])) << 32) | static_cast<uint32_t>(op.i[0]);
+  const uint64_t per = static_cast<uint32_t>(op.i[2]);
+  const uint64_t b0 = static_cast<uint64_t>(chunk) * per;
+  const uint64_t b1 = b0 + per < total ? b0 + per : total;
+  const char* base = reinterpret_cast<const char*>(op.p[0]);
+  constexpr uint32_t kPiece = 2048;
+  for (uint64_t b = b0 + static_cast<uint64_t>(threadIdx.x) * kPiece; b < b1; b += static_cast<uint64_t>(kThreads) * kPiece) {
+    const uint64_t left = b1 - b;
+    const uint32_t n = static_cast<uint32_t>(left < kPiece ? (left & ~15ull) : kPiece);
+    if (n > 0) prefetch_l2(base + b, n);
+  }
+}
+
+// Stand-alone all-reduce of columns [chunk * cc, ...) of a [batch, N] bf16 tensor (sum over ranks), for partial sums
+// that were not produced by a linear task with the fused all-reduce.
+//   op.p: 0 x (local), 1 partial (heap; push: [W][batch][N], NVLS: [batch][N]), 2 flags (heap [W][chunks]), 3 out
+//   op.i: 0 N, 1 ld_x, 2 ld_out, 3 columns per chunk (multiple of 8), 4 chunks
+// Push: the chunk goes into slot [rank] of every rank's partial buffer, then the call epoch into flag [rank][chunk] of
+// every rank; when all W flags of this rank carry the epoch the W slots are summed.  NVLS: the chunk is stored locally
+// and summed across ranks by multimem.ld_reduce.  Reference: mega_triton_kernel/kernels/allreduce.py:35-65.
+TDB_DEVICE bool task_allreduce(const KP& p, const MegaOp& op, int chunk, uint32_t epoch, volatile int* s_ok) {
+  const int W = p.symm.world, rank = p.symm.rank;
+  const int N = op.i[0], cc = op.i[3], chunks = op.i[4];
+  const int64_t ld_x = op.i[1], ld_out = op.i[2];
+  const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(op.p[0]);
+  __nv_bfloat16* partial = reinterpret_cast<__nv_bfloat16*>(op.p[1]);
+  uint32_t* flags = reinterpret_cast<uint32_t*>(op.p[2]);
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(op.p[3]);
+  const int c0 = chunk * cc, c1 = min(N, c0 + cc);
+  const int vec_per_row = (c1 - c0) / 8;
+  const int nvec = p.batch * vec_per_row;
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    const int m = v / vec_per_row, col = c0 + (v - m * vec_per_row) * 8;
+    const uint4 u = ld_v4(x + static_cast<int64_t>(m) * ld_x + col);
+    if (p.use_mc) {
+      st_v4(partial + static_cast<int64_t>(m) * N + col, u);
+    } else {
+      __nv_bfloat16* mine = partial + (static_cast<int64_t>(rank) * p.batch + m) * N + col;
+      for (int j = 0; j < W; ++j) st_v4(symm_at(p.symm, mine, (rank + j) % W), u);
+    }
+  }
+  if (threadIdx.x == 0) *s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < W) {
+    fence_acq_rel_sys();
+    st_release_sys(symm_at(p.symm, flags + static_cast<int64_t>(rank) * chunks + chunk, (rank + threadIdx.x) % W), epoch);
+    if (!wait_until(p.symm, flags + static_cast<int64_t>(threadIdx.x) * chunks + chunk, epoch, kCmpGe, kKernelMega, 60,
+                    threadIdx.x, chunk))
+      *s_ok = 0;
+  }
+  __syncthreads();
+  if (*s_ok == 0) return false;
+  for (int v = threadIdx.x; v < nvec; v += kThreads) {
+    const int m = v / vec_per_row, col = c0 + (v - m * vec_per_row) * 8;
+    uint4 o;
+    if (p.use_mc) {
+      o = multimem_ld_reduce_bf16x8(mc_ptr(p.symm, partial + static_cast<int64_t>(m) * N + col));
+    } else {
+      float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int sr = 0; sr < W; ++sr) {
+        const uint4 u = ld_relaxed_sys_v4(partial + (static_cast<int64_t>(sr) * p.batch + m) * N + col);
+        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+        a[0] += f0.x; a[1] += f0.y; a[2] += f1.x; a[3] += f1.y; a[4] += f2.x; a[5] += f2.y; a[6] += f3.x; a[7] += f3.y;
+      }
+      o.x = pack_bf16x2(a[0], a[1]); o.y = pack_bf16x2(a[2], a[3]); o.z = pack_bf16x2(a[4], a[5]); o.w = pack_bf16x2(a[6], a[7]);
+    }
+    st_v4(out + static_cast<int64_t>(m) * ld_out + col, o);
+  }
+  return true;
+}
+
+// Spin (bounded) until scoreboard slot tk.dep_idx has reached tk.dep_need.  One thread.
+TDB_DEVICE bool wait_dependency(const KP& p, const MegaTask& tk, int ti) {
+  if (tk.dep_idx < 0) return true;
+  const uint32_t* sb = reinterpret_cast<const uint32_t*>(p.scoreboard + tk.dep_idx);
+  uint32_t v = ld_acquire_gpu(sb);
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(v) < tk.dep_need) {
+    // the abort word lives in host memory: look at it (and at the clock) rarely, a read over PCIe is slow
+    if ((++spins & 4095u) == 0u && (abort_requested(p.symm) || globaltimer_ns() - t0 > p.symm.timeout_ns)) {
+      report(p.symm, kTimeoutFlag, kKernelMega, 1, tk.type, ti, tk.dep_need, (int)v);
+      return false;
+    }
+    v = ld_acquire_gpu(sb);
+  }
+  return true;
+}
+
 template <int MPAD>
 __global__ void __launch_bounds__(kThreads, 1) mega_kernel(const KP p) {
   using L = Layout<MPAD>;
@@ -275,20 +369,10 @@ __global__ void __launch_bounds__(kThreads, 1) mega_kernel(const KP p) {
     const MegaTask tk = p.tasks[ti];
     // ---- dependencies
     bool ok = true;
-    if (threadIdx.x == 0 && tk.dep_idx >= 0) {
-      const uint32_t* sb = reinterpret_cast<const uint32_t*>(p.scoreboard + tk.dep_idx);
-      uint32_t v = ld_acquire_gpu(sb);
-      const uint64_t t0 = globaltimer_ns();
-      uint32_t spins = 0;
-      while (static_cast<int32_t>(v) < tk.dep_need) {
-        // the abort word lives in host memory: look at it (and at the clock) rarely, a read over PCIe is slow
-        if ((++spins & 4095u) == 0u && (abort_requested(p.symm) || globaltimer_ns() - t0 > p.symm.timeout_ns)) {
-          report(p.symm, kTimeoutFlag, kKernelMega, 1, tk.type, ti, tk.dep_need, (int)v);
-          ok = false;
-          break;
-        }
-        v = ld_acquire_gpu(sb);
-      }
+    // A linear task checks its dependency in the producer lane, after the first weight tiles (which depend on nothing)
+    // have been requested; every other task type waits here.
+    if (threadIdx.x == 0 && tk.type != kTaskLinear) {
+      ok = wait_dependency(p, tk, ti);
       // data written through the generic proxy by other SMs may be read by TMA below
       fence_proxy_async();
     }
@@ -322,6 +406,28 @@ __global__ void __launch_bounds__(kThreads, 1) mega_kernel(const KP p) {
       case kTaskAttnCombine:
         task_attn_combine(op, tk.a0, tk.a1, p.batch);
         break;
+      case kTaskPrefetch:
+        task_prefetch(op, tk.a0);
+        break;
+      case kTaskBarrier:
+        // op.p[0] = heap flags [W] of this barrier; the call epoch is the value, so nothing is ever reset
+        if (W > 1 && !rank_barrier_block(p.symm, reinterpret_cast<uint32_t*>(op.p[0]), epoch, kKernelMega, 50)) *abort_flag = 1;
+        break;
+      case kTaskAllReduce:
+        if (W > 1) {
+          if (!task_allreduce(p, op, tk.a0, epoch, s_wok)) *abort_flag = 1;
+        } else {
+          // one rank: the sum is the input
+          const int N = op.i[0], cc = op.i[3];
+          const int c0 = tk.a0 * cc, c1 = min(N, c0 + cc);
+          const int vec_per_row = (c1 - c0) / 8;
+          for (int v = threadIdx.x; v < p.batch * vec_per_row; v += kThreads) {
+            const int m = v / vec_per_row, col = c0 + (v - m * vec_per_row) * 8;
+            st_v4(reinterpret_cast<__nv_bfloat16*>(op.p[3]) + static_cast<int64_t>(m) * op.i[2] + col,
+                  ld_v4(reinterpret_cast<const __nv_bfloat16*>(op.p[0]) + static_cast<int64_t>(m) * op.i[1] + col));
+          }
+        }
+        break;
       case kTaskLinear: {
         // op.i: 0 N, 1 K, 2 splits, 3 tmap_w, 4 tmap_x, 5 ld_out, 6 all_reduce, 7 tiles_n, 8 max_tiles(flags stride)
         // op.p: 0 out, 1 partial (heap, this op's ping-pong buffer), 2 flags (heap [W][max_tiles])
@@ -336,7 +442,36 @@ __global__ void __launch_bounds__(kThreads, 1) mega_kernel(const KP p) {
         const bool direct = (splits == 1 && !ar);
         if (warp == 0) {
           if (lane == 0) {
-            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+            // The weight tiles depend on nothing: the first stages are requested before the dependency (which only
+            // the activation tile has) is checked, so the DRAM latency of the weights overlaps the wait.
+            const int n_pre = min(kb1 - kb0, kStages);
+            int issued = 0;
+            bool pok = true;
+            for (int j = 0; j < n_pre; ++j) {
+              const uint32_t itj = it + j;
+              const int s = itj % kStages;
+              const uint32_t ph = (itj / kStages) & 1;
+              if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kMbarTimeoutNs)) {
+                report(p.symm, kTimeoutMbarrier, kKernelMega, 10, -1, s, (int)ph, ti);
+                *abort_flag = 1;
+                pok = false;
+                break;
+              }
+              mbar_arrive_expect_tx(&full_bar[s], L::kWBytes + L::kXBytesRaw);
+              tma_load_2d(smem + s * L::kStageBytes, tmap_w, &full_bar[s], (kb0 + j) * kBK, nt * kTN);
+              issued = j + 1;
+            }
+            if (!wait_dependency(p, tk, ti)) {
+              *abort_flag = 1;   // the activation loads below still run (the memory is valid) so that the barriers of
+              pok = false;       // the requested stages complete; the MMA lane sees the flag and skips the tile
+            }
+            fence_proxy_async();
+            for (int j = 0; j < issued; ++j) {
+              const int s = (it + j) % kStages;
+              tma_load_2d(smem + s * L::kStageBytes + L::kWBytes, tmap_x, &full_bar[s], (kb0 + j) * kBK, 0);
+            }
+            it += issued;
+            for (int kb = kb0 + issued; kb < kb1 && pok; ++kb, ++it) {
               const int s = it % kStages;
               const uint32_t ph = (it / kStages) & 1;
               if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kMbarTimeoutNs)) {

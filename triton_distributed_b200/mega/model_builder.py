@@ -18,8 +18,16 @@ from ..runtime import get_runtime
 from ..tools import profiler as prof_tools
 
 T_RMSNORM, T_LINEAR, T_ROPE_KV, T_ATTN_SPLIT, T_ATTN_COMBINE, T_SILU_MUL = 1, 2, 3, 4, 5, 6
+T_PREFETCH, T_BARRIER, T_ALLREDUCE = 7, 8, 9
 TASK_NAMES = {1: "rms_norm", 2: "linear", 3: "qk_norm_rope_kv", 4: "flash_decode_split", 5: "flash_decode_combine",
-              6: "silu_mul"}
+              6: "silu_mul", 7: "prefetch_l2", 8: "barrier_all", 9: "all_reduce"}
+PREFETCH_CHUNK_BYTES = 384 * 1024     # one pass of the CTA: 192 threads x 2 KB requests
+
+
+def _i32(v: int) -> int:
+    """The 32-bit pattern ``v`` as the signed value an int32 field holds."""
+    v &= 0xFFFFFFFF
+    return v - (1 << 32) if v & 0x80000000 else v
 
 
 class _LoggingScheduler:
@@ -65,6 +73,8 @@ class ModelBuilder:
         self._producer: Dict[int, int] = {}       # data_ptr -> stage that wrote it last
         self._keep: List[torch.Tensor] = []
         self._ar_ops: List[dict] = []
+        self._bar_ops: List[int] = []
+        self._fused_ar_stages = set()
         self._max_n = 0
         self._max_tiles = 0
         self._last_stage = -1
@@ -124,20 +134,61 @@ class ModelBuilder:
         if ar:
             self._ar_ops.append({"op": op, "N": N, "tiles": tiles, "out": out, "ints": ints})
         st = self.sched.add_stage(T_LINEAR, op, tiles, splits, 1, self._dep(x))
+        if all_reduce:
+            self._fused_ar_stages.add(st)
         self._wrote(st, out)
         return st
 
     make_qkv_proj = make_o_proj = make_fc1 = make_fc2 = make_linear
 
-    def make_allreduce(self, x: torch.Tensor):
-        """All-reduces are fused into the producing ``make_linear(..., all_reduce=True)``."""
-        return self._last_stage
+    def make_lm_head(self, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> int:
+        """Logits of the local vocabulary shard: a linear stage without all-reduce."""
+        return self.make_linear(x, weight, out, all_reduce=False)
 
-    def make_barrier_all_intra_node(self):
-        return self._last_stage
+    def make_allreduce(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, chunk_cols: int = 1024) -> int:
+        """Sum ``x`` [B, N] over the ranks.  A tensor produced by ``make_linear(..., all_reduce=True)`` is already
+        summed (the all-reduce ran inside those tasks): nothing is scheduled for it.  Otherwise stand-alone all-reduce
+        tasks, one per ``chunk_cols`` columns, write ``out`` (default: in place).  All-reduces alternate between two
+        staging buffers: between two of them that share a buffer (every second one, and the same one of the next launch)
+        there must be another all-reduce or a ``make_barrier_all_intra_node``, as in the reference's barrier + all-reduce
+        pairs, so that no rank overwrites a buffer a slower rank is still summing."""
+        st = self._producer.get(x.data_ptr(), -1)
+        if st >= 0 and st in self._fused_ar_stages:
+            return st
+        out = x if out is None else out
+        N = x.shape[-1]
+        if N % 8 or chunk_cols % 8:
+            raise ValueError("make_allreduce: N and chunk_cols must be multiples of 8")
+        chunks = (N + chunk_cols - 1) // chunk_cols
+        self._max_tiles = max(self._max_tiles, chunks)
+        ints = [N, x.stride(0), out.stride(0), chunk_cols, chunks]
+        op = self.sched.add_op([self._ptr(x), 0, 0, self._ptr(out)], ints, [])
+        if self.world_size > 1:
+            self._ar_ops.append({"op": op, "N": N, "tiles": chunks, "out": out, "ints": ints, "standalone": True})
+        stage = self.sched.add_stage(T_ALLREDUCE, op, chunks, 1, 1, self._dep(x))
+        self._wrote(stage, out)
+        return stage
 
-    def make_prefetch(self, *a, **k):
-        return self._last_stage
+    def make_barrier_all_intra_node(self) -> int:
+        """One task that holds its SM until every rank has reached it (epoch flags in the heap, nothing to reset).  Stages
+        scheduled after it depend on it only if they are given its stage through a tensor written by it; the reference
+        uses it around its all-reduce task (model_builder.py:467-486), which the flag protocol here does not need."""
+        op = self.sched.add_op([0], [], [])
+        self._bar_ops.append(op)
+        stage = self.sched.add_stage(T_BARRIER, op, 1, 1, 1, self._last_stage)
+        self._last_stage = stage
+        return stage
+
+    def make_prefetch(self, weight: torch.Tensor, after: Optional[torch.Tensor] = None) -> int:
+        """Request ``weight`` into L2 ahead of the operator that will stream it (cp.async.bulk.prefetch.L2, asynchronous).
+        ``after``: a tensor whose producing stage must be complete before the requests are issued (so that they do not
+        compete with the operator that is running now); None = as soon as an SM reaches the task."""
+        total = weight.numel() * weight.element_size()
+        if not weight.is_contiguous() or weight.data_ptr() % 16:
+            raise ValueError("make_prefetch: contiguous, 16-byte aligned tensor expected")
+        chunks = max(1, (total + PREFETCH_CHUNK_BYTES - 1) // PREFETCH_CHUNK_BYTES)
+        op = self.sched.add_op([self._ptr(weight)], [_i32(total & 0xFFFFFFFF), _i32(total >> 32), PREFETCH_CHUNK_BYTES], [])
+        return self.sched.add_stage(T_PREFETCH, op, chunks, 1, 1, self._dep(after) if after is not None else -1)
 
     def make_qk_norm_rope_update_kvcache(self, qkv: torch.Tensor, q_norm_w, k_norm_w, q_out: torch.Tensor,
                                          k_cache: torch.Tensor, v_cache: torch.Tensor, kv_offset: torch.Tensor,
@@ -196,6 +247,8 @@ class ModelBuilder:
             self.ar_flags = rt.symm_tensor((len(self._ar_ops), self.world_size, self._max_tiles), torch.int32)
             # the op records were added before the buffers existed: rebuild the scheduler's op table entries
             # (pointers 1 and 2 of every all-reduce op) through a second scheduler with identical stages
+        if self._bar_ops:
+            self.bar_flags = rt.symm_tensor((len(self._bar_ops), max(self.world_size, 8)), torch.int32)
         sched2 = self.lib.MegaScheduler()
         self._rebuild(sched2)
         self.sched = sched2
@@ -216,7 +269,7 @@ class ModelBuilder:
 
     def _rebuild(self, sched2):
         """Re-emit ops and stages into a fresh scheduler, now with the all-reduce buffers' addresses."""
-        ar_index = {o["op"]: i for i, o in enumerate(self._ar_ops)}
+        ar_index = {o["op"]: i for i, o in enumerate(self._ar_ops) if self.world_size > 1}
         self._replay_ops(sched2, ar_index)
 
     # ops / stages are recorded twice: once while building (to learn sizes) and once here with final pointers.  To keep
@@ -229,7 +282,9 @@ class ModelBuilder:
                 if idx in ar_index:
                     i = ar_index[idx]
                     buf = self.partial[i & 1]
-                    ptrs = [ptrs[0], buf.data_ptr(), self.ar_flags[i].data_ptr()]
+                    ptrs = [ptrs[0], buf.data_ptr(), self.ar_flags[i].data_ptr()] + list(ptrs[3:])
+                elif idx in self._bar_ops:
+                    ptrs = [self.bar_flags[self._bar_ops.index(idx)].data_ptr()]
                 sched2.add_op(ptrs, ints, floats)
             else:
                 _, ty, op, n0, n1, n2, dep = rec

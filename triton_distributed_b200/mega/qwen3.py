@@ -18,7 +18,9 @@ from .model_builder import ModelBuilder
 
 class Qwen3Model:
     def __init__(self, model: DenseLLM, kv_cache: KV_Cache, batch: int, lm_head_inside: bool = True,
-                 enable_profiling: bool = False, policy: str = "round_robin"):
+                 enable_profiling: bool = False, policy: str = "round_robin", prefetch: bool = False):
+        """``prefetch``: schedule L2 prefetch tasks for the weights of the operator after next wherever the step would
+        otherwise leave HBM idle (during the attention of short contexts and the two all-reduces of a layer)."""
         self.model, self.kv_cache, self.batch = model, kv_cache, batch
         a = model.arch
         W = model.world_size
@@ -46,17 +48,23 @@ class Qwen3Model:
             b.make_qkv_proj(self.n_out, l.attn.wqkv, self.qkv)
             b.make_qk_norm_rope_update_kvcache(self.qkv, l.attn.q_norm_w, l.attn.k_norm_w, self.q, k_cache, v_cache,
                                                kv_cache.kv_offset, Hq, Hkv, D, l.attn.eps, l.attn.rope_theta)
+            if prefetch:
+                b.make_prefetch(l.attn.wo, after=self.qkv)
             b.make_flash_decode(self.q, k_cache, v_cache, self.kv_lens, self.attn_out.view(B, Hq, D), Hq, Hkv, D, l.attn.scale)
+            if prefetch:
+                b.make_prefetch(l.mlp.gate_up_proj, after=self.attn_out)
             b.make_o_proj(self.attn_out, l.attn.wo, self.o_out, all_reduce=True)
             b.make_rms_norm(self.o_out, l.post_norm_w, self.n_out, l.eps, residual=self.resid)
             b.make_fc1(self.n_out, l.mlp.gate_up_proj, self.gate_up)
             b.make_silu_mul_up(self.gate_up, self.act)
+            if prefetch and li + 1 < len(model.layers):
+                b.make_prefetch(model.layers[li + 1].attn.wqkv, after=self.act)
             b.make_fc2(self.act, l.mlp.down_proj, self.down_out, all_reduce=True)
             prev_out = self.down_out
         b.make_rms_norm(prev_out, model.final_norm_w, self.final, a.rms_norm_eps, residual=self.resid)
         self.lm_head_inside = lm_head_inside
         if lm_head_inside:
-            b.make_linear(self.final, model.lm_head, self.logits)
+            b.make_lm_head(self.final, model.lm_head, self.logits)
         b.compile()
 
     @torch.no_grad()

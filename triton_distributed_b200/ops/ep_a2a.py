@@ -189,12 +189,15 @@ def ep_dispatch(ctx: AllToAllContext, x: torch.Tensor, topk_ids: torch.Tensor) -
     lib.ep_dispatch(rt.heap, x.contiguous(), ids, E, ctx.quant, ctx.max_m, ctx.recv_x, ctx.recv_scale, ctx.recv_meta,
                     ctx.recv_count, ctx.flags, ctx.rows_per_parity, base, ctx.cursor, ctx.sent_row, ctx.dctx,
                     _ctas_for_rows(ids.numel()), rt.config.wait_timeout_s)
-    # receive rows -> local expert per row -> sorted, padded layout
-    row_expert = torch.empty(ctx.rows_per_parity, dtype=torch.int32, device=x.device)
-    lib.ep_recv_ids(ctx.recv_count, base_self, row_expert, epr, W, ctx.max_m, ctx.dctx)
-    srt = sort_topk_ids_align_block_size(row_expert.reshape(-1, 1), epr)
-    xs = lib.ep_gather_rows(ctx.recv_x, ctx.recv_scale, srt.sorted_ids, srt.meta, ctx.hidden, ctx.quant, ctx.rows_per_parity,
-                            ctx.dctx)
+    # Receive side, one launch: the receive areas are grouped by (expert, source) already, so the grouped-GEMM layout
+    # (rows sorted by local expert, 128-row padding) follows from the epr x W counts; fp8 rows are de-quantised while
+    # they are moved.  sorted_ids index receive rows; nothing scans the receive capacity.
+    cap = min(ctx.rows_per_parity, W * ctx.max_m * max(ctx.topk, ids.shape[1])) + epr * 127
+    cap = (cap + 127) // 128 * 128
+    xs, sid, tile_expert, offsets, meta, counts = lib.ep_finish(
+        ctx.recv_x, ctx.recv_scale, ctx.recv_count, base_self, epr, W, ctx.max_m, ctx.hidden, ctx.quant, ctx.rows_per_parity,
+        ctx.dctx, cap, _ctas_for_rows(min(cap, W * ids.numel())))
+    srt = MoESort(sid, None, tile_expert, offsets, meta, counts, 1)
     return EpRecv(xs, srt, ctx.rows_per_parity, ids, counts=ctx.recv_count)
 
 
@@ -208,7 +211,8 @@ def ep_combine(ctx: AllToAllContext, y_sorted: torch.Tensor, recv: EpRecv, topk_
     w = topk_w.float().contiguous() if topk_w is not None else None
     return lib.ep_combine(rt.heap, y_sorted.contiguous(), recv.sort.pos_of, ctx.recv_meta, ctx.dctx, base_self, ctx.max_m,
                           ctx.rows_per_parity, ctx.ret, ctx.ret_flags, recv.topk_ids, w, ctx.num_tot_experts, ctx.cctx,
-                          _ctas_for_rows(recv.topk_ids.numel()), rt.config.wait_timeout_s)
+                          _ctas_for_rows(recv.topk_ids.numel()), rt.config.wait_timeout_s,
+                          recv.sort.sorted_ids, recv.sort.meta)
 
 
 def fast_all_to_all(ctx: AllToAllContext, send_tensor: torch.Tensor, send_split_cumsum: torch.Tensor,
