@@ -1,4 +1,5 @@
-"""Gated delta rule forward: device time of the CUDA kernel for the reference's test shapes (H heads, K = V = 128,
+"""Gated delta rule forward: device time of the chunk-parallel tensor-core kernels and of the token-recurrent kernel for
+the reference's test shapes (H heads, K = V = 128,
 one sequence of T tokens; python/triton_dist/test/nvidia/test_gdn.py:78-88)."""
 import argparse
 import json
@@ -28,10 +29,14 @@ def main():
         beta = torch.rand(1, T, H, device="cuda").to(torch.bfloat16)
         g = F.logsigmoid(torch.rand(1, T, H, device="cuda"))
         cu = torch.tensor([0, T], dtype=torch.int32, device="cuda")
-        ts = device_time_ms(lambda: ops.chunk_gated_delta_rule_fwd(q, k, v, g, beta, K ** -0.5, None, False, cu), 10, 3)
-        ms = statistics.median(ts)
-        print(json.dumps({"op": "gdn_fwd", "T": T, "H": H, "ms": round(ms, 4),
-                          "us_per_token": round(ms * 1e3 / T, 4)}), flush=True)
+        rec = {"op": "gdn_fwd", "T": T, "H": H}
+        for impl in ("chunk", "recurrent"):
+            ts = device_time_ms(lambda: ops.chunk_gated_delta_rule_fwd(q, k, v, g, beta, K ** -0.5, None, False, cu, impl=impl), 10, 3)
+            ms = statistics.median(ts)
+            rec[f"{impl}_ms"] = round(ms, 4)
+            rec[f"{impl}_us_per_token"] = round(ms * 1e3 / T, 4)
+        rec["chunk_speedup"] = round(rec["recurrent_ms"] / rec["chunk_ms"], 2)
+        print(json.dumps(rec), flush=True)
 
 
 if __name__ == "__main__":

@@ -300,6 +300,13 @@ def check_dist_decode(rt):
         for b in range(B):
             err = (out[b].float() - refs[b]).abs().max().item()
             assert err < 3e-2, f"dist flash decode (launches={layer.last_launches}) it={it} b={b}: err {err}"
+    layer.one_launch = None          # automatic choice
+    out = layer.forward(q, k_cache, v_cache, global_kv_lens, bt)
+    torch.cuda.synchronize()
+    rt.check_status()
+    assert layer.last_launches in (1, 2)
+    for b in range(B):
+        assert (out[b].float() - refs[b]).abs().max().item() < 3e-2
     log(rt, "OK distributed flash-decode")
 
 

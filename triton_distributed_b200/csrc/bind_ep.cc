@@ -68,7 +68,8 @@ at::Tensor ep_gather_rows(const at::Tensor& recv_x, const at::Tensor& recv_scale
   return out;
 }
 
-// Returns (x_sorted [cap, H] bf16, sorted_ids [cap], tile_expert [cap/128], offsets [epr+1], meta [2], counts [epr]).
+// Returns (x_sorted [cap, H] bf16, sorted_ids [cap], tile_expert [cap/128], offsets [epr+1], meta [2], counts [epr],
+// real_rows [cap + 1]).
 std::vector<at::Tensor> ep_finish(const at::Tensor& recv_x, const at::Tensor& recv_scale, const at::Tensor& recv_count,
                                   c10::optional<at::Tensor> base_self, int64_t epr, int64_t W, int64_t max_tokens, int64_t H,
                                   bool quant, int64_t rows_per_parity, const at::Tensor& dispatch_ctx, int64_t cap,
@@ -82,6 +83,7 @@ std::vector<at::Tensor> ep_finish(const at::Tensor& recv_x, const at::Tensor& re
   at::Tensor offsets = at::empty({epr + 1}, i32o);
   at::Tensor meta = at::empty({2}, i32o);
   at::Tensor counts = at::empty({epr}, i32o);
+  at::Tensor real_rows = at::empty({cap + 1}, i32o);
   tdb::EpFinishArgs a;
   a.recv_x = recv_x.data_ptr();
   a.recv_scale = recv_scale.data_ptr<float>();
@@ -96,17 +98,19 @@ std::vector<at::Tensor> ep_finish(const at::Tensor& recv_x, const at::Tensor& re
   a.offsets = i32(offsets);
   a.counts = i32(counts);
   a.meta = i32(meta);
+  a.real_rows = i32(real_rows);
   a.cap = cap;
   a.num_ctas = num_ctas;
   check_cuda(tdb::launch_ep_finish(a, cur_stream()), "launch_ep_finish");
-  return {xs, sorted_ids, tile_expert, offsets, meta, counts};
+  return {xs, sorted_ids, tile_expert, offsets, meta, counts, real_rows};
 }
 
 at::Tensor ep_combine(SymmHeap& h, const at::Tensor& y, c10::optional<at::Tensor> pos_of, const at::Tensor& recv_meta,
                       const at::Tensor& dispatch_ctx, c10::optional<at::Tensor> base_self, int64_t max_tokens,
                       int64_t recv_rows, at::Tensor& ret, at::Tensor& flags, const at::Tensor& topk_ids,
                       c10::optional<at::Tensor> topk_w, int64_t E, at::Tensor& ctx, int64_t num_ctas, double timeout_s,
-                      c10::optional<at::Tensor> sorted_ids, c10::optional<at::Tensor> sort_meta) {
+                      c10::optional<at::Tensor> sorted_ids, c10::optional<at::Tensor> sort_meta,
+                      c10::optional<at::Tensor> real_rows) {
   TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.is_contiguous(), "ep_combine: y bf16 [rows,H]");
   c10::cuda::CUDAGuard guard(y.device());
   const int64_t T = topk_ids.size(0), k = topk_ids.size(1), H = y.size(1);
@@ -118,6 +122,11 @@ at::Tensor ep_combine(SymmHeap& h, const at::Tensor& y, c10::optional<at::Tensor
     TORCH_CHECK(sort_meta.has_value(), "ep_combine: sorted_ids needs sort_meta");
     a.sorted_ids = i32(*sorted_ids);
     a.sort_meta = i32(*sort_meta);
+    if (real_rows.has_value()) {
+      TORCH_CHECK(real_rows->numel() == sorted_ids->numel() + 1, "ep_combine: real_rows must have one entry more than sorted_ids");
+      a.real_rows = i32(*real_rows);
+      a.real_cap = sorted_ids->numel();
+    }
   }
   a.recv_meta = i32(recv_meta);
   a.dispatch_ctx = ctxp(dispatch_ctx);
@@ -183,7 +192,8 @@ void bind_ep(py::module_& m) {
   m.def("ep_combine", &ep_combine, py::arg("heap"), py::arg("y"), py::arg("pos_of"), py::arg("recv_meta"),
         py::arg("dispatch_ctx"), py::arg("base_self"), py::arg("max_tokens"), py::arg("recv_rows"), py::arg("ret"),
         py::arg("flags"), py::arg("topk_ids"), py::arg("topk_w"), py::arg("E"), py::arg("ctx"), py::arg("num_ctas"),
-        py::arg("timeout_s"), py::arg("sorted_ids") = py::none(), py::arg("sort_meta") = py::none());
+        py::arg("timeout_s"), py::arg("sorted_ids") = py::none(), py::arg("sort_meta") = py::none(),
+        py::arg("real_rows") = py::none());
   m.def("a2a_single", &a2a_single);
   m.def("fp8_quant", &fp8_quant);
   m.def("fp8_dequant", &fp8_dequant);

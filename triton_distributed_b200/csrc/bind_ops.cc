@@ -273,6 +273,59 @@ std::tuple<at::Tensor, at::Tensor> gdn_fwd(const at::Tensor& q, const at::Tensor
   return {o, ht};
 }
 
+// Chunk-parallel gated delta rule forward.  chunk_seq / chunk_t0 int32 [NC], seq_chunk0 int32 [N + 1] (device).
+// Returns (o bf16 [T, H, V], g_cumsum fp32 [T, H], A fp32 [T, H, 64] or empty, final_state fp32 [N, H, K, V] or empty).
+std::vector<at::Tensor> gdn_chunk_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& g,
+                                      const at::Tensor& beta, double scale, const c10::optional<at::Tensor>& h0,
+                                      bool output_final_state, const at::Tensor& cu_seqlens, const at::Tensor& chunk_seq,
+                                      const at::Tensor& chunk_t0, const at::Tensor& seq_chunk0, bool return_a) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
+                  v.scalar_type() == at::kBFloat16 && beta.scalar_type() == at::kBFloat16 && g.scalar_type() == at::kFloat,
+              "gdn_chunk_fwd: q, k, v, beta bf16 and g fp32 expected");
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && g.is_contiguous() &&
+                  beta.is_contiguous(), "gdn_chunk_fwd: contiguous [T, H, *] tensors expected");
+  for (const at::Tensor* t : {&cu_seqlens, &chunk_seq, &chunk_t0, &seq_chunk0})
+    TORCH_CHECK(t->scalar_type() == at::kInt && t->is_cuda() && t->is_contiguous(), "gdn_chunk_fwd: int32 device index tensors");
+  const int64_t T = q.size(0), H = q.size(1), K = q.size(2), V = v.size(2);
+  TORCH_CHECK(K == 128 && V % 64 == 0 && V >= 64 && V <= 256, "gdn_chunk_fwd: K = 128 and V in {64, 128, 192, 256}");
+  TORCH_CHECK(k.size(0) == T && v.size(0) == T && g.numel() == T * H && beta.numel() == T * H, "gdn_chunk_fwd: shape mismatch");
+  const int64_t N = cu_seqlens.numel() - 1, NC = chunk_seq.numel();
+  TORCH_CHECK(N >= 1 && chunk_t0.numel() == NC && seq_chunk0.numel() == N + 1, "gdn_chunk_fwd: chunk tables do not match");
+  c10::cuda::CUDAGuard guard(q.device());
+  auto f32 = q.options().dtype(at::kFloat);
+  at::Tensor o = at::empty({T, H, V}, q.options());
+  at::Tensor gc = at::empty({T, H}, f32);
+  at::Tensor A = return_a ? at::empty({T, H, 64}, f32) : at::empty({0}, f32);
+  at::Tensor ht = output_final_state ? at::empty({N, H, K, V}, f32) : at::empty({0}, f32);
+  at::Tensor w = at::empty({NC, H, 64, K}, q.options());
+  at::Tensor u = at::empty({NC, H, 64, V}, q.options());
+  at::Tensor vn = at::empty({NC, H, 64, V}, q.options());
+  at::Tensor hs = at::empty({NC, H, K, V}, q.options());
+  tdb::GdnChunkArgs a;
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
+  a.g = g.data_ptr<float>();
+  a.beta = beta.data_ptr();
+  a.cu_seqlens = cu_seqlens.data_ptr<int32_t>();
+  a.chunk_seq = chunk_seq.data_ptr<int32_t>();
+  a.chunk_t0 = chunk_t0.data_ptr<int32_t>();
+  a.seq_chunk0 = seq_chunk0.data_ptr<int32_t>();
+  a.g_cumsum = gc.data_ptr<float>();
+  a.a_out = return_a ? A.data_ptr<float>() : nullptr;
+  a.w = w.data_ptr(); a.u = u.data_ptr(); a.v_new = vn.data_ptr(); a.h_chunks = hs.data_ptr();
+  a.initial_state = nullptr;
+  if (h0.has_value()) {
+    TORCH_CHECK(h0->scalar_type() == at::kFloat && h0->is_contiguous() && h0->numel() == N * H * K * V,
+                "gdn_chunk_fwd: initial_state fp32 [N, H, K, V]");
+    a.initial_state = h0->data_ptr<float>();
+  }
+  a.final_state = output_final_state ? ht.data_ptr<float>() : nullptr;
+  a.o = o.data_ptr();
+  a.num_seqs = N; a.num_chunks = NC; a.H = H; a.K = K; a.V = V;
+  a.scale = static_cast<float>(scale);
+  if (T > 0) check_cuda(tdb::launch_gdn_chunk_fwd(a, cur_stream()), "launch_gdn_chunk_fwd");
+  return {o, gc, A, ht};
+}
+
 }  // namespace
 
 
@@ -303,4 +356,5 @@ void bind_more(py::module_& m) {
   m.def("argmax", &argmax);
   m.def("abs_sum", &abs_sum);
   m.def("gdn_fwd", &gdn_fwd);
+  m.def("gdn_chunk_fwd", &gdn_chunk_fwd);
 }

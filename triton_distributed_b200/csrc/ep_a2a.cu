@@ -244,7 +244,8 @@ __global__ void ep_gather_rows_kernel(const uint8_t* __restrict__ recv_x_base, c
 // grouped GEMM (rows sorted by local expert, every expert padded to 128 rows), de-quantising fp8 rows on the way.
 // The receive areas are already grouped by (expert, source), so the place of every row follows from a prefix sum over
 // at most epr * W counts that every CTA recomputes in shared memory; nothing scans the receive capacity.
-// One warp moves one row.  Block 0 also writes the layout tensors (sorted_ids are receive-row indices, -1 = padding).
+// One warp moves one row.  Block 0 also writes the layout tensors (sorted_ids are receive-row indices, -1 = padding;
+// padding rows of x_sorted are left as they are).
 // ---------------------------------------------------------------------------
 constexpr int kFinishMaxBlocks = 2048;    // epr * W
 constexpr int kFinishMaxExperts = 256;    // epr
@@ -263,10 +264,12 @@ struct FinishParams {
   int32_t* offsets;            // [epr + 1]
   int32_t* counts;             // [epr]
   int32_t* meta;               // {padded rows, tiles}
+  int32_t* real_rows;          // [cap + 1]: the sorted rows that carry a token, packed, and their number in the last slot
   int64_t cap;                 // multiple of 128
 };
 
 __global__ void __launch_bounds__(kEpThreads) ep_finish_kernel(const FinishParams p) {
+  __shared__ int s_real[kFinishMaxExperts];      // tokens of the experts before this one
   __shared__ int s_cnt[kFinishMaxBlocks];        // tokens of (le, src)
   __shared__ int s_in[kFinishMaxBlocks];         // rows of the same expert from earlier sources
   __shared__ int s_tot[kFinishMaxExperts];       // tokens of the expert
@@ -290,6 +293,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_finish_kernel(const FinishParam
   __syncthreads();
   if (threadIdx.x == 0) {
     int64_t acc = 0;
+    int real = 0;
     for (int le = 0; le < epr; ++le) {
       s_off[le] = static_cast<int>(acc);
       int64_t nxt = acc + (static_cast<int64_t>(s_tot[le]) + 127) / 128 * 128;
@@ -297,9 +301,12 @@ __global__ void __launch_bounds__(kEpThreads) ep_finish_kernel(const FinishParam
         s_tot[le] = 0;            // an expert that would not fit is dropped rather than written out of bounds
         nxt = acc;
       }
+      s_real[le] = real;
+      real += s_tot[le];
       acc = nxt;
     }
     s_off[epr] = static_cast<int>(acc);
+    if (blockIdx.x == 0) p.real_rows[p.cap] = real;
   }
   __syncthreads();
   const int R = s_off[epr];
@@ -343,8 +350,10 @@ __global__ void __launch_bounds__(kEpThreads) ep_finish_kernel(const FinishParam
     const int j = r - s_off[le];
     uint4* dst = reinterpret_cast<uint4*>(p.x_sorted + static_cast<int64_t>(r) * p.H);
     if (j >= s_tot[le]) {
+      // Padding row of a partly filled tile: marked, not cleared.  A GEMM row depends on its own input row only and
+      // nothing reads the output rows of padding, so clearing up to 127 rows per expert would be wasted traffic
+      // (with many experts per rank far more bytes than the tokens themselves).
       if (lane == 0) p.sorted_ids[r] = -1;
-      for (int i = lane; i < (p.H >> 3); i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
       continue;
     }
     int sr = 0;
@@ -352,7 +361,10 @@ __global__ void __launch_bounds__(kEpThreads) ep_finish_kernel(const FinishParam
     const int i_in = j - s_in[le * W + sr];
     const int64_t id = p.base_self ? static_cast<int64_t>(p.base_self[le * W + sr]) + i_in
                                    : (static_cast<int64_t>(le) * W + sr) * p.max_tokens + i_in;
-    if (lane == 0) p.sorted_ids[r] = static_cast<int32_t>(id);
+    if (lane == 0) {
+      p.sorted_ids[r] = static_cast<int32_t>(id);
+      p.real_rows[s_real[le] + j] = r;
+    }
     if (!p.quant) {
       const uint4* src = reinterpret_cast<const uint4*>(recv_x + id * row_bytes);
       int i = lane;
@@ -403,6 +415,8 @@ struct CombineParams {
   const int32_t* pos_of;         // [recv rows] sorted row of every receive row (-1: no token); unused with sorted_ids
   const int32_t* sorted_ids;     // optional [sorted rows] receive row of every sorted row (-1: padding): the send loop
   const int32_t* sort_meta;      //   then walks the sort_meta[0] sorted rows instead of the whole receive capacity
+  const int32_t* real_rows;      // optional (with sorted_ids) [cap + 1]: packed list of the sorted rows that carry a token,
+  int64_t real_cap;              //   count in slot [real_cap]: one warp per listed row, no scan at all
   const int32_t* recv_meta;      // [2][recv rows] pair index at the source (parity of the matching dispatch)
   const CtxDev* dctx;            // the dispatch context (gives that parity)
   const int32_t* base_self;      // packed layout: [epr*W] first row of block; null = fixed stride
@@ -434,6 +448,41 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const CombinePar
   const int blocks = p.epr * W;
   uint32_t* work = &p.ctx->pad[0];
   const int nvec = p.H >> 3;
+  // copy of one expert-output row to its token's owner, several 16-byte loads in flight
+  auto send_row = [&](int pos, int pair, int64_t r) {
+    int src;
+    if (p.base_self == nullptr) {
+      src = static_cast<int>((r / p.max_tokens) % W);
+    } else {
+      int lo = 0, hi = blocks - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (p.base_self[mid] <= r) lo = mid; else hi = mid - 1;
+      }
+      src = lo % W;
+    }
+    const uint4* sp = reinterpret_cast<const uint4*>(p.y + static_cast<int64_t>(pos) * p.H);
+    uint4* d = reinterpret_cast<uint4*>(symm_at(p.symm, ret + static_cast<int64_t>(pair) * p.H, src));
+    int i = lane;
+    for (; i + 96 < nvec; i += 128) {
+      const uint4 v0 = sp[i], v1 = sp[i + 32], v2 = sp[i + 64], v3 = sp[i + 96];
+      st_v4(d + i, v0);
+      st_v4(d + i + 32, v1);
+      st_v4(d + i + 64, v2);
+      st_v4(d + i + 96, v3);
+    }
+    for (; i < nvec; i += 32) st_v4(d + i, sp[i]);
+  };
+  if (p.real_rows != nullptr) {
+    // the receive side listed the rows that carry a token: one warp per row, rows spread evenly over all warps (the
+    // rows of an expert are adjacent, so chunked scanning would leave the few warps that hit them with all the work)
+    const int n_real = p.real_rows[p.real_cap];
+    for (int j = blockIdx.x * warps + (threadIdx.x >> 5); j < n_real; j += gridDim.x * warps) {
+      const int pos = p.real_rows[j];
+      const int64_t r = p.sorted_ids[pos];
+      if (r >= 0) send_row(pos, recv_meta[r], r);
+    }
+  } else {
   while (true) {
     uint32_t chunk = 0;
     if (lane == 0) chunk = atomicAdd(work, 1u);
@@ -458,29 +507,9 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const CombinePar
       const int pos = __shfl_sync(0xffffffffu, pos_mine, l);
       const int pair = __shfl_sync(0xffffffffu, pair_mine, l);
       const int64_t r = __shfl_sync(0xffffffffu, id_mine, l);
-      int src;
-      if (p.base_self == nullptr) {
-        src = static_cast<int>((r / p.max_tokens) % W);
-      } else {
-        int lo = 0, hi = blocks - 1;
-        while (lo < hi) {
-          const int mid = (lo + hi + 1) >> 1;
-          if (p.base_self[mid] <= r) lo = mid; else hi = mid - 1;
-        }
-        src = lo % W;
-      }
-      const uint4* sp = reinterpret_cast<const uint4*>(p.y + static_cast<int64_t>(pos) * p.H);
-      uint4* d = reinterpret_cast<uint4*>(symm_at(p.symm, ret + static_cast<int64_t>(pair) * p.H, src));
-      int i = lane;
-      for (; i + 96 < nvec; i += 128) {
-        const uint4 v0 = sp[i], v1 = sp[i + 32], v2 = sp[i + 64], v3 = sp[i + 96];
-        st_v4(d + i, v0);
-        st_v4(d + i + 32, v1);
-        st_v4(d + i + 64, v2);
-        st_v4(d + i + 96, v3);
-      }
-      for (; i < nvec; i += 32) st_v4(d + i, sp[i]);
+      send_row(pos, pair, r);
     }
+  }
   }
   __shared__ int s_last;
   __shared__ int s_ok;
@@ -725,6 +754,7 @@ cudaError_t launch_ep_finish(const EpFinishArgs& a, cudaStream_t s) {
   p.offsets = a.offsets;
   p.counts = a.counts;
   p.meta = a.meta;
+  p.real_rows = a.real_rows;
   p.cap = a.cap;
   const int ctas = a.num_ctas > 0 ? a.num_ctas : 64;
   ep_finish_kernel<<<ctas, kEpThreads, 0, s>>>(p);
@@ -740,6 +770,8 @@ cudaError_t launch_ep_combine(const EpCombineArgs& a, cudaStream_t s) {
   p.pos_of = a.pos_of;
   p.sorted_ids = a.sorted_ids;
   p.sort_meta = a.sort_meta;
+  p.real_rows = a.sorted_ids != nullptr ? a.real_rows : nullptr;
+  p.real_cap = a.real_cap;
   p.recv_meta = a.recv_meta;
   p.dctx = a.dispatch_ctx;
   p.base_self = a.base_self;

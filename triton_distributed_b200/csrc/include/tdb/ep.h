@@ -48,6 +48,7 @@ struct EpFinishArgs {
   int32_t* offsets;           // [epr + 1]
   int32_t* counts;            // [epr]
   int32_t* meta;              // [2]
+  int32_t* real_rows;         // [cap + 1] packed list of the sorted rows that carry a token; [cap] = their number
   int64_t cap;                // multiple of 128
   int num_ctas;
 };
@@ -58,6 +59,8 @@ struct EpCombineArgs {
   const int32_t* pos_of;      // [recv rows]; may be null when sorted_ids is given
   const int32_t* sorted_ids = nullptr;   // [sorted rows] receive row per sorted row (-1 padding) + sort_meta {rows, tiles}:
   const int32_t* sort_meta = nullptr;    //   the send loop walks the sorted rows instead of the receive capacity
+  const int32_t* real_rows = nullptr;    // optional, with sorted_ids: EpFinishArgs::real_rows of the matching dispatch
+  int64_t real_cap = 0;                  //   and its cap: one warp per token row, nothing is scanned
   const int32_t* recv_meta;   // heap [2][recv rows]
   const CtxDev* dispatch_ctx;
   const int32_t* base_self;   // [E/W * W] packed layout, or null

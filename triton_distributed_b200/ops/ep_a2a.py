@@ -74,6 +74,7 @@ class EpRecv:
     recv_rows: int
     topk_ids: torch.Tensor          # the local routing that was dispatched (for combine)
     counts: Optional[torch.Tensor] = None   # [epr][W] tokens per (local expert, source)
+    real_rows: Optional[torch.Tensor] = None   # packed list of the sorted rows that carry a token (+ their number)
     # CPU emulation only
     cpu_state: object = None
 
@@ -167,7 +168,7 @@ def _cpu_combine(ctx: AllToAllContext, y_sorted, recv: EpRecv, topk_w):
 def _ctas_for_rows(rows: int) -> int:
     """One warp moves one row at a time and a row is a handful of memory round trips, so the kernels are latency-bound
     until many warps work: 64 CTAs (512 warps) for a decode step, up to four per SM for prefill-sized batches."""
-    return int(min(592, max(64, rows // 16)))
+    return int(min(592, max(64, rows // 8)))
 
 
 # ------------------------------------------------------------------ public ops
@@ -194,11 +195,11 @@ def ep_dispatch(ctx: AllToAllContext, x: torch.Tensor, topk_ids: torch.Tensor) -
     # they are moved.  sorted_ids index receive rows; nothing scans the receive capacity.
     cap = min(ctx.rows_per_parity, W * ctx.max_m * max(ctx.topk, ids.shape[1])) + epr * 127
     cap = (cap + 127) // 128 * 128
-    xs, sid, tile_expert, offsets, meta, counts = lib.ep_finish(
+    xs, sid, tile_expert, offsets, meta, counts, real_rows = lib.ep_finish(
         ctx.recv_x, ctx.recv_scale, ctx.recv_count, base_self, epr, W, ctx.max_m, ctx.hidden, ctx.quant, ctx.rows_per_parity,
         ctx.dctx, cap, _ctas_for_rows(min(cap, W * ids.numel())))
     srt = MoESort(sid, None, tile_expert, offsets, meta, counts, 1)
-    return EpRecv(xs, srt, ctx.rows_per_parity, ids, counts=ctx.recv_count)
+    return EpRecv(xs, srt, ctx.rows_per_parity, ids, counts=ctx.recv_count, real_rows=real_rows)
 
 
 def ep_combine(ctx: AllToAllContext, y_sorted: torch.Tensor, recv: EpRecv, topk_w: Optional[torch.Tensor]) -> torch.Tensor:
@@ -212,7 +213,7 @@ def ep_combine(ctx: AllToAllContext, y_sorted: torch.Tensor, recv: EpRecv, topk_
     return lib.ep_combine(rt.heap, y_sorted.contiguous(), recv.sort.pos_of, ctx.recv_meta, ctx.dctx, base_self, ctx.max_m,
                           ctx.rows_per_parity, ctx.ret, ctx.ret_flags, recv.topk_ids, w, ctx.num_tot_experts, ctx.cctx,
                           _ctas_for_rows(recv.topk_ids.numel()), rt.config.wait_timeout_s,
-                          recv.sort.sorted_ids, recv.sort.meta)
+                          recv.sort.sorted_ids, recv.sort.meta, recv.real_rows)
 
 
 def fast_all_to_all(ctx: AllToAllContext, send_tensor: torch.Tensor, send_split_cumsum: torch.Tensor,

@@ -7,10 +7,11 @@ cu_seqlens)`` -> ``(g_cumsum, o, A, final_state)`` (python/triton_dist/kernels/n
 Per head the state ``S`` [K, V] follows ``S <- exp(g_t) S;  v' = beta_t (v_t - S^T k_t);  S <- S + k_t v'^T;
 o_t = scale S^T q_t``.  Three implementations of the same function live here:
 
-* ``csrc/gdn.cu``: one CUDA kernel that walks the tokens with the state in registers (bf16 CUDA tensors, K = 128);
-* ``gated_delta_rule_chunked``: the chunk-parallel WY form the reference uses (triangular solve per 64-token chunk,
-  sequential pass over chunk states, output pass), written with batched PyTorch ops - the CPU path, and the source
-  of the per-chunk ``A`` matrices when a caller asks for them;
+* ``csrc/gdn_chunk.cu``: the chunk-parallel WY form the reference uses (triangular solve per 64-token chunk,
+  sequential pass over chunk states, output pass) as three CUDA kernels with tensor-core products - the default for
+  bf16 CUDA tensors with K = 128 and V a multiple of 64, also the source of the per-chunk ``A`` matrices;
+* ``csrc/gdn.cu``: one CUDA kernel that walks the tokens with the state in registers (``impl="recurrent"``; other V);
+* ``gated_delta_rule_chunked``: the same chunked form with batched PyTorch ops - the CPU path;
 * ``gated_delta_rule_recurrent``: the token loop in fp32, the oracle of the tests.
 """
 from __future__ import annotations
@@ -111,16 +112,30 @@ def gated_delta_rule_chunked(q, k, v, g, beta, scale, initial_state=None, cu_seq
 def chunk_gated_delta_rule_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
                                scale: float, initial_state: Optional[torch.Tensor] = None,
                                output_final_state: bool = False, cu_seqlens: Optional[torch.Tensor] = None,
-                               return_A: bool = False) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+                               return_A: bool = False, impl: str = "auto") -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Forward of the gated delta rule.  Returns ``(g_cumsum, o, A, final_state)``: the chunk-local cumulative log
     decay, the outputs in the dtype of ``v``, the per-chunk WY matrices (only with ``return_A``; otherwise None) and the
-    final state fp32 [N, H, K, V] (with ``output_final_state``)."""
+    final state fp32 [N, H, K, V] (with ``output_final_state``).  ``impl``: "auto" (chunk-parallel CUDA kernels where they
+    apply, else the token-recurrent kernel, else PyTorch), "chunk" or "recurrent"."""
     _, T, H, K = q.shape
     V = v.shape[-1]
     if cu_seqlens is None:
         cu_seqlens = torch.tensor([0, T], dtype=torch.int32, device=q.device)
-    native = (_native.use_native(q, k, v) and q.dtype == torch.bfloat16 and K == 128 and V % 32 == 0 and not return_A)
-    if not native:
+    native = _native.use_native(q, k, v) and q.dtype == torch.bfloat16 and K == 128
+    chunk_ok = native and V % 64 == 0 and 64 <= V <= 256 and impl in ("auto", "chunk")
+    recurrent_ok = native and V % 32 == 0 and not return_A and impl in ("auto", "recurrent")
+    if impl == "chunk" and not chunk_ok or impl == "recurrent" and not recurrent_ok:
+        raise ValueError(f"chunk_gated_delta_rule_fwd: impl={impl!r} does not support these tensors")
+    if chunk_ok:
+        lib = _native.load(True)
+        cu = cu_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
+        chunk_seq, chunk_t0, seq_chunk0 = _chunk_tables(cu_seqlens, q.device)
+        o, gc, A, ht = lib.gdn_chunk_fwd(q[0].contiguous(), k[0].contiguous(), v[0].contiguous(), g[0].float().contiguous(),
+                                         beta[0].to(torch.bfloat16).contiguous(), float(scale),
+                                         initial_state.float().contiguous() if initial_state is not None else None,
+                                         bool(output_final_state), cu, chunk_seq, chunk_t0, seq_chunk0, bool(return_A))
+        return gc.unsqueeze(0), o.unsqueeze(0), (A.unsqueeze(0) if return_A else None), (ht if output_final_state else None)
+    if not recurrent_ok:
         gc, o, A, ht = gated_delta_rule_chunked(q, k, v, g, beta, scale, initial_state, cu_seqlens)
         return gc, o.to(v.dtype), (A if return_A else None), (ht if output_final_state else None)
     lib = _native.load(True)
@@ -132,6 +147,19 @@ def chunk_gated_delta_rule_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     # chunk-local cumulative decay, cheap enough in torch: cumsum over T minus the value at each chunk start
     gc = _chunk_local_cumsum(g[0].float(), cu_seqlens)
     return gc.unsqueeze(0), o.unsqueeze(0), None, (ht if output_final_state else None)
+
+
+def _chunk_tables(cu_seqlens: torch.Tensor, device, chunk: int = CHUNK):
+    """Per chunk: its sequence and first token; per sequence: its first chunk (int32 device tensors)."""
+    cu = cu_seqlens.tolist()
+    seq_of, t0_of, first = [], [], [0]
+    for s in range(len(cu) - 1):
+        for t in range(cu[s], cu[s + 1], chunk):
+            seq_of.append(s)
+            t0_of.append(t)
+        first.append(len(seq_of))
+    mk = lambda x: torch.tensor(x, dtype=torch.int32, device=device)   # noqa: E731
+    return mk(seq_of), mk(t0_of), mk(first)
 
 
 def _chunk_local_cumsum(g: torch.Tensor, cu_seqlens: torch.Tensor, chunk: int = CHUNK) -> torch.Tensor:

@@ -21,6 +21,9 @@ from ..ops.common import new_ctx_dev, ref_all_gather
 from ..runtime import get_runtime
 
 
+ONE_LAUNCH_MAX_SPLITS = 16
+
+
 class SpGQAFlashDecodeAttention:
     def __init__(self, rank: int, node: int, num_ranks: int, num_nodes: int, num_q_heads: int, num_kv_heads: int,
                  q_head_dim: int, v_head_dim: int, page_size: int = 1, scale: Optional[float] = None,
@@ -39,7 +42,10 @@ class SpGQAFlashDecodeAttention:
         self.ctx_dev = None
         self.workspace = None
         self.counters = None
-        self.one_launch = True      # False forces the two-launch form (benchmarks compare the two)
+        # None: one launch while the local KV is cut into at most ONE_LAUNCH_MAX_SPLITS splits.  Beyond that the merge of
+        # the splits by a single CTA per KV head costs more than the second launch saves (bs 1, 16 k KV per rank, 45
+        # splits, two B200: 39 us in one launch, 34 us in two).  True / False force a form.
+        self.one_launch: Optional[bool] = None
         self.last_launches = 0
         if self.rt.is_cuda and num_ranks > 1:
             packets = num_ranks * max_allowed_batch * num_q_heads * (q_head_dim + 1)
@@ -80,7 +86,7 @@ class SpGQAFlashDecodeAttention:
         self.last_launches = lib.dist_decode_attn(
             self.rt.heap, q.contiguous(), k_cache, v_cache, block_table, local_lens, self.workspace, splits,
             float(self.scale), float(self.soft_cap), out, self.staging, self.ctx_dev, self.rt.config.wait_timeout_s,
-            self.counters if self.one_launch else None)
+            self.counters if (self.one_launch if self.one_launch is not None else splits <= ONE_LAUNCH_MAX_SPLITS) else None)
         return out
 
     __call__ = forward
