@@ -20,7 +20,7 @@ uint64_t ns(double s) { return static_cast<uint64_t>(s * 1e9); }
 void ep_dispatch(SymmHeap& h, const at::Tensor& x, const at::Tensor& topk_ids, int64_t E, bool quant, int64_t max_tokens,
                  at::Tensor& recv_x, at::Tensor& recv_scale, at::Tensor& recv_meta, at::Tensor& recv_count,
                  at::Tensor& flags, int64_t rows_per_parity, c10::optional<at::Tensor> base, at::Tensor& cursor,
-                 at::Tensor& sent_row, at::Tensor& ctx, int64_t num_ctas, double timeout_s) {
+                 at::Tensor& sent_row, at::Tensor& ctx, int64_t num_ctas, double timeout_s, int64_t parts) {
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(), "ep_dispatch: x bf16 [T,H]");
   TORCH_CHECK(topk_ids.scalar_type() == at::kInt && topk_ids.dim() == 2 && topk_ids.is_contiguous(), "ep_dispatch: int32 ids [T,k]");
   TORCH_CHECK(x.size(0) <= max_tokens, "ep_dispatch: more tokens than the context was created for");
@@ -41,6 +41,7 @@ void ep_dispatch(SymmHeap& h, const at::Tensor& x, const at::Tensor& topk_ids, i
   a.cursor = i32(cursor);
   a.sent_row = i32(sent_row);
   a.num_ctas = num_ctas;
+  a.parts = parts;
   a.ctx = ctxp(ctx);
   a.symm = h.info(ns(timeout_s));
   check_cuda(tdb::launch_ep_dispatch(a, cur_stream()), "launch_ep_dispatch");
@@ -73,7 +74,7 @@ at::Tensor ep_gather_rows(const at::Tensor& recv_x, const at::Tensor& recv_scale
 std::vector<at::Tensor> ep_finish(const at::Tensor& recv_x, const at::Tensor& recv_scale, const at::Tensor& recv_count,
                                   c10::optional<at::Tensor> base_self, int64_t epr, int64_t W, int64_t max_tokens, int64_t H,
                                   bool quant, int64_t rows_per_parity, const at::Tensor& dispatch_ctx, int64_t cap,
-                                  int64_t num_ctas) {
+                                  int64_t num_ctas, int64_t parts) {
   c10::cuda::CUDAGuard guard(recv_x.device());
   TORCH_CHECK(cap > 0 && cap % 128 == 0, "ep_finish: cap must be a positive multiple of 128");
   auto i32o = recv_x.options().dtype(at::kInt);
@@ -101,6 +102,7 @@ std::vector<at::Tensor> ep_finish(const at::Tensor& recv_x, const at::Tensor& re
   a.real_rows = i32(real_rows);
   a.cap = cap;
   a.num_ctas = num_ctas;
+  a.parts = parts;
   check_cuda(tdb::launch_ep_finish(a, cur_stream()), "launch_ep_finish");
   return {xs, sorted_ids, tile_expert, offsets, meta, counts, real_rows};
 }
@@ -110,7 +112,7 @@ at::Tensor ep_combine(SymmHeap& h, const at::Tensor& y, c10::optional<at::Tensor
                       int64_t recv_rows, at::Tensor& ret, at::Tensor& flags, const at::Tensor& topk_ids,
                       c10::optional<at::Tensor> topk_w, int64_t E, at::Tensor& ctx, int64_t num_ctas, double timeout_s,
                       c10::optional<at::Tensor> sorted_ids, c10::optional<at::Tensor> sort_meta,
-                      c10::optional<at::Tensor> real_rows) {
+                      c10::optional<at::Tensor> real_rows, int64_t parts) {
   TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.dim() == 2 && y.is_contiguous(), "ep_combine: y bf16 [rows,H]");
   c10::cuda::CUDAGuard guard(y.device());
   const int64_t T = topk_ids.size(0), k = topk_ids.size(1), H = y.size(1);
@@ -145,6 +147,7 @@ at::Tensor ep_combine(SymmHeap& h, const at::Tensor& y, c10::optional<at::Tensor
   a.out = out.data_ptr();
   a.T = T; a.H = H; a.k = k; a.E = E;
   a.num_ctas = num_ctas;
+  a.parts = parts;
   a.ctx = ctxp(ctx);
   a.symm = h.info(ns(timeout_s));
   TORCH_CHECK(a.ret_half >= static_cast<uint64_t>(T) * k * H, "ep_combine: return buffer too small");
@@ -183,17 +186,22 @@ at::Tensor fp8_dequant(const at::Tensor& q, const at::Tensor& s) {
 }  // namespace
 
 void bind_ep(py::module_& m) {
-  m.def("ep_dispatch", &ep_dispatch);
+  m.def("ep_dispatch", &ep_dispatch, py::arg("heap"), py::arg("x"), py::arg("topk_ids"), py::arg("E"), py::arg("quant"),
+        py::arg("max_tokens"), py::arg("recv_x"), py::arg("recv_scale"), py::arg("recv_meta"), py::arg("recv_count"),
+        py::arg("flags"), py::arg("rows_per_parity"), py::arg("base"), py::arg("cursor"), py::arg("sent_row"), py::arg("ctx"),
+        py::arg("num_ctas"), py::arg("timeout_s"), py::arg("parts") = 1);
   m.def("ep_count", &ep_count);
   m.def("ep_layout", &ep_layout);
   m.def("ep_recv_ids", &ep_recv_ids);
   m.def("ep_gather_rows", &ep_gather_rows);
-  m.def("ep_finish", &ep_finish);
+  m.def("ep_finish", &ep_finish, py::arg("recv_x"), py::arg("recv_scale"), py::arg("recv_count"), py::arg("base_self"),
+        py::arg("epr"), py::arg("W"), py::arg("max_tokens"), py::arg("H"), py::arg("quant"), py::arg("rows_per_parity"),
+        py::arg("dispatch_ctx"), py::arg("cap"), py::arg("num_ctas"), py::arg("parts") = 1);
   m.def("ep_combine", &ep_combine, py::arg("heap"), py::arg("y"), py::arg("pos_of"), py::arg("recv_meta"),
         py::arg("dispatch_ctx"), py::arg("base_self"), py::arg("max_tokens"), py::arg("recv_rows"), py::arg("ret"),
         py::arg("flags"), py::arg("topk_ids"), py::arg("topk_w"), py::arg("E"), py::arg("ctx"), py::arg("num_ctas"),
         py::arg("timeout_s"), py::arg("sorted_ids") = py::none(), py::arg("sort_meta") = py::none(),
-        py::arg("real_rows") = py::none());
+        py::arg("real_rows") = py::none(), py::arg("parts") = 1);
   m.def("a2a_single", &a2a_single);
   m.def("fp8_quant", &fp8_quant);
   m.def("fp8_dequant", &fp8_dequant);

@@ -36,12 +36,13 @@ TDB_DEVICE float fp8_to_float(uint32_t byte) {
 }
 
 // One warp quantises one bf16 row of H elements (H % 128 == 0) into fp8 + H/128 scales and writes both.
-TDB_DEVICE void warp_quant_row(const __nv_bfloat16* src, uint8_t* dst_q, float* dst_s, int H) {
+// (blocks [b_begin, b_end) of the row when several warps share it)
+TDB_DEVICE void warp_quant_row(const __nv_bfloat16* src, uint8_t* dst_q, float* dst_s, int H, int b_begin = 0, int b_end = -1) {
   const int lane = lane_id();
-  const int nb = H / kQuantBlock;
+  const int nb = b_end < 0 ? H / kQuantBlock : b_end;
   // eight 128-value blocks per step: their loads are in flight together (a block per iteration would pay one memory
   // round trip per block, 56 in a row for a 7168-wide token)
-  for (int b0 = 0; b0 < nb; b0 += 8) {
+  for (int b0 = b_begin; b0 < nb; b0 += 8) {
     uint2 u[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -79,6 +80,7 @@ struct DispatchParams {
   CtxDev* ctx;
   SymmInfo symm;
   int wait_recv;                 // the last CTA also waits for all sources' flags
+  int parts;                     // warps per row: 1, 2, 4 or 8
 };
 
 __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const DispatchParams p) {
@@ -93,29 +95,47 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const DispatchP
   float* rs = p.recv_scale + par * p.rows_per_parity * nsc;
   int32_t* rm = p.recv_meta + par * p.rows_per_parity;
   const int64_t pairs = static_cast<int64_t>(p.T) * p.k;
-  for (int64_t pr = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); pr < pairs;
-       pr += static_cast<int64_t>(gridDim.x) * warps) {
-    const int e = p.topk_ids[pr];
-    if (e < 0 || e >= p.E) {
-      if (lane == 0) p.sent_row[pr] = -1;
-      continue;
+  // `parts` warps share a row (a row is a chain of dependent memory round trips: with few rows more warps per row cut
+  // the latency).  The slot of a row comes from one atomic on the LOCAL cursor of its expert, taken by the row's first
+  // warp and handed to the others through shared memory.
+  __shared__ int64_t s_row[kEpThreads / 32];
+  const int parts = p.parts, rpc = warps / parts;
+  const int grp = (threadIdx.x >> 5) / parts, part = (threadIdx.x >> 5) % parts;
+  const int nblk = p.H / kQuantBlock;
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * rpc; base < pairs; base += static_cast<int64_t>(gridDim.x) * rpc) {
+    const int64_t pr = base + grp;
+    int e = -1;
+    if (pr < pairs) {
+      e = p.topk_ids[pr];
+      if (e < 0 || e >= p.E) e = -1;
     }
-    const int dst = e / p.epr, le = e - dst * p.epr;
-    int idx = 0;
-    if (lane == 0) idx = atomicAdd(p.cursor + e, 1);
-    idx = __shfl_sync(0xffffffffu, idx, 0);
-    const int64_t base = p.base ? p.base[(static_cast<int64_t>(dst) * p.epr + le) * W + rank]
-                                : (static_cast<int64_t>(le) * W + rank) * p.max_tokens;
-    const int64_t row = base + idx;
-    if (lane == 0) p.sent_row[pr] = static_cast<int32_t>(row);
-    const __nv_bfloat16* src = p.x + (pr / p.k) * p.H;
-    uint8_t* drow = symm_at(p.symm, rx + row * row_bytes, dst);
-    if (p.quant) {
-      warp_quant_row(src, drow, symm_at(p.symm, rs + row * nsc, dst), p.H);
-    } else {
-      for (int i = lane; i < (p.H >> 3); i += 32) st_v4(drow + i * 16, ld_nc_v4(src + i * 8));
+    if (part == 0 && lane == 0 && pr < pairs) {
+      int64_t row = -1;
+      if (e >= 0) {
+        const int dst = e / p.epr, le = e - dst * p.epr;
+        const int idx = atomicAdd(p.cursor + e, 1);
+        const int64_t b = p.base ? p.base[(static_cast<int64_t>(dst) * p.epr + le) * W + rank]
+                                 : (static_cast<int64_t>(le) * W + rank) * p.max_tokens;
+        row = b + idx;
+      }
+      p.sent_row[pr] = static_cast<int32_t>(row);
+      s_row[grp] = row;
     }
-    if (lane == 0) *symm_at(p.symm, rm + row, dst) = static_cast<int32_t>(pr);
+    __syncthreads();
+    if (e >= 0) {
+      const int dst = e / p.epr;
+      const int64_t row = s_row[grp];
+      const __nv_bfloat16* src = p.x + (pr / p.k) * p.H;
+      uint8_t* drow = symm_at(p.symm, rx + row * row_bytes, dst);
+      if (p.quant) {
+        warp_quant_row(src, drow, symm_at(p.symm, rs + row * nsc, dst), p.H, part * nblk / parts, (part + 1) * nblk / parts);
+      } else {
+        const int nv = p.H >> 3;
+        for (int i = part * nv / parts + lane; i < (part + 1) * nv / parts; i += 32) st_v4(drow + i * 16, ld_nc_v4(src + i * 8));
+      }
+      if (part == 0 && lane == 0) *symm_at(p.symm, rm + row, dst) = static_cast<int32_t>(pr);
+    }
+    __syncthreads();   // s_row is rewritten by the next iteration
   }
   // ---- completion: the last CTA of the grid publishes counts and flags
   __shared__ int s_last;
@@ -266,6 +286,7 @@ struct FinishParams {
   int32_t* meta;               // {padded rows, tiles}
   int32_t* real_rows;          // [cap + 1]: the sorted rows that carry a token, packed, and their number in the last slot
   int64_t cap;                 // multiple of 128
+  int parts;                   // warps per token row
 };
 
 __global__ void __launch_bounds__(kEpThreads) ep_finish_kernel(const FinishParams p) {
@@ -339,59 +360,73 @@ __global__ void __launch_bounds__(kEpThreads) ep_finish_kernel(const FinishParam
   const uint8_t* recv_x = p.recv_x + par * p.rows_per_parity * row_bytes;
   const float* recv_scale = p.recv_scale + par * p.rows_per_parity * nsc;
   const int warps = kEpThreads / 32, lane = threadIdx.x & 31;
-  for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
+  // padding rows of partly filled tiles: marked, not cleared.  A GEMM row depends on its own input row only and nothing
+  // reads the output rows of padding, so clearing up to 127 rows per expert would be wasted traffic (with many
+  // experts per rank far more bytes than the tokens themselves).
+  for (int r = blockIdx.x * kEpThreads + threadIdx.x; r < R; r += gridDim.x * kEpThreads) {
     int lo = 0, hi = epr - 1;
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
       if (s_off[mid] <= r) lo = mid; else hi = mid - 1;
     }
-    // several experts may share a start row (empty ones): the last of them is the one with rows
-    const int le = lo;
-    const int j = r - s_off[le];
-    uint4* dst = reinterpret_cast<uint4*>(p.x_sorted + static_cast<int64_t>(r) * p.H);
-    if (j >= s_tot[le]) {
-      // Padding row of a partly filled tile: marked, not cleared.  A GEMM row depends on its own input row only and
-      // nothing reads the output rows of padding, so clearing up to 127 rows per expert would be wasted traffic
-      // (with many experts per rank far more bytes than the tokens themselves).
-      if (lane == 0) p.sorted_ids[r] = -1;
-      continue;
+    if (r - s_off[lo] >= s_tot[lo]) p.sorted_ids[r] = -1;
+  }
+  // token rows: the j-th token row overall (experts in order, sources in order inside an expert) is handled by `parts`
+  // warps; indexing by token row rather than by sorted row spreads the rows evenly over the warps (the token rows of an
+  // expert are adjacent and 128-row aligned, a stride over sorted rows would give a few warps all of them)
+  const int n_real = s_real[epr - 1] + s_tot[epr - 1];
+  const int parts = p.parts;
+  for (int wj = blockIdx.x * warps + (threadIdx.x >> 5); wj < n_real * parts; wj += gridDim.x * warps) {
+    const int j = wj / parts, part = wj - j * parts;
+    int lo = 0, hi = epr - 1;
+    while (lo < hi) {      // last expert whose first token row is <= j: the one that owns row j (empty ones share starts)
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_real[mid] <= j) lo = mid; else hi = mid - 1;
     }
+    const int le = lo;
+    const int jr = j - s_real[le];
+    const int r = s_off[le] + jr;
     int sr = 0;
-    while (sr + 1 < W && s_in[le * W + sr + 1] <= j) ++sr;
-    const int i_in = j - s_in[le * W + sr];
+    while (sr + 1 < W && s_in[le * W + sr + 1] <= jr) ++sr;
+    const int i_in = jr - s_in[le * W + sr];
     const int64_t id = p.base_self ? static_cast<int64_t>(p.base_self[le * W + sr]) + i_in
                                    : (static_cast<int64_t>(le) * W + sr) * p.max_tokens + i_in;
-    if (lane == 0) {
+    uint4* dst = reinterpret_cast<uint4*>(p.x_sorted + static_cast<int64_t>(r) * p.H);
+    if (part == 0 && lane == 0) {
       p.sorted_ids[r] = static_cast<int32_t>(id);
-      p.real_rows[s_real[le] + j] = r;
+      p.real_rows[j] = r;
     }
     if (!p.quant) {
       const uint4* src = reinterpret_cast<const uint4*>(recv_x + id * row_bytes);
-      int i = lane;
-      for (; i + 96 < (p.H >> 3); i += 128) {
+      const int nv = p.H >> 3;
+      const int i1 = (part + 1) * nv / parts;
+      int i = part * nv / parts + lane;
+      for (; i + 96 < i1; i += 128) {
         const uint4 v0 = src[i], v1 = src[i + 32], v2 = src[i + 64], v3 = src[i + 96];
         dst[i] = v0; dst[i + 32] = v1; dst[i + 64] = v2; dst[i + 96] = v3;
       }
-      for (; i < (p.H >> 3); i += 32) dst[i] = src[i];
+      for (; i < i1; i += 32) dst[i] = src[i];
       continue;
     }
     // fp8 row: a lane turns 16 values (one 16-byte load, inside one 128-value scale block) into two 16-byte stores
     const uint4* q = reinterpret_cast<const uint4*>(recv_x + id * row_bytes);
     const float* sc = recv_scale + id * nsc;
-    for (int i0 = 0; i0 < (p.H >> 4); i0 += 128) {
+    const int nch = p.H >> 4;
+    const int c1 = (part + 1) * nch / parts;
+    for (int i0 = part * nch / parts; i0 < c1; i0 += 128) {
       uint4 w[4];
       float scl[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int i = i0 + u * 32 + lane;
-        const bool in = i < (p.H >> 4);
+        const bool in = i < c1;
         w[u] = in ? q[i] : make_uint4(0u, 0u, 0u, 0u);
         scl[u] = in ? sc[i >> 3] : 0.f;
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int i = i0 + u * 32 + lane;
-        if (i >= (p.H >> 4)) break;
+        if (i >= c1) break;
         const uint32_t ws[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
         uint32_t o[8];
 #pragma unroll
@@ -416,7 +451,8 @@ struct CombineParams {
   const int32_t* sorted_ids;     // optional [sorted rows] receive row of every sorted row (-1: padding): the send loop
   const int32_t* sort_meta;      //   then walks the sort_meta[0] sorted rows instead of the whole receive capacity
   const int32_t* real_rows;      // optional (with sorted_ids) [cap + 1]: packed list of the sorted rows that carry a token,
-  int64_t real_cap;              //   count in slot [real_cap]: one warp per listed row, no scan at all
+  int64_t real_cap;              //   count in slot [real_cap]: `parts` warps per listed row, no scan at all
+  int parts;
   const int32_t* recv_meta;      // [2][recv rows] pair index at the source (parity of the matching dispatch)
   const CtxDev* dctx;            // the dispatch context (gives that parity)
   const int32_t* base_self;      // packed layout: [epr*W] first row of block; null = fixed stride
@@ -449,7 +485,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const CombinePar
   uint32_t* work = &p.ctx->pad[0];
   const int nvec = p.H >> 3;
   // copy of one expert-output row to its token's owner, several 16-byte loads in flight
-  auto send_row = [&](int pos, int pair, int64_t r) {
+  auto send_row = [&](int pos, int pair, int64_t r, int part, int parts) {
     int src;
     if (p.base_self == nullptr) {
       src = static_cast<int>((r / p.max_tokens) % W);
@@ -463,24 +499,27 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const CombinePar
     }
     const uint4* sp = reinterpret_cast<const uint4*>(p.y + static_cast<int64_t>(pos) * p.H);
     uint4* d = reinterpret_cast<uint4*>(symm_at(p.symm, ret + static_cast<int64_t>(pair) * p.H, src));
-    int i = lane;
-    for (; i + 96 < nvec; i += 128) {
+    const int i1 = (part + 1) * nvec / parts;
+    int i = part * nvec / parts + lane;
+    for (; i + 96 < i1; i += 128) {
       const uint4 v0 = sp[i], v1 = sp[i + 32], v2 = sp[i + 64], v3 = sp[i + 96];
       st_v4(d + i, v0);
       st_v4(d + i + 32, v1);
       st_v4(d + i + 64, v2);
       st_v4(d + i + 96, v3);
     }
-    for (; i < nvec; i += 32) st_v4(d + i, sp[i]);
+    for (; i < i1; i += 32) st_v4(d + i, sp[i]);
   };
   if (p.real_rows != nullptr) {
     // the receive side listed the rows that carry a token: one warp per row, rows spread evenly over all warps (the
     // rows of an expert are adjacent, so chunked scanning would leave the few warps that hit them with all the work)
     const int n_real = p.real_rows[p.real_cap];
-    for (int j = blockIdx.x * warps + (threadIdx.x >> 5); j < n_real; j += gridDim.x * warps) {
+    const int parts = p.parts;
+    for (int wj = blockIdx.x * warps + (threadIdx.x >> 5); wj < n_real * parts; wj += gridDim.x * warps) {
+      const int j = wj / parts;
       const int pos = p.real_rows[j];
       const int64_t r = p.sorted_ids[pos];
-      if (r >= 0) send_row(pos, recv_meta[r], r);
+      if (r >= 0) send_row(pos, recv_meta[r], r, wj - j * parts, parts);
     }
   } else {
   while (true) {
@@ -507,7 +546,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const CombinePar
       const int pos = __shfl_sync(0xffffffffu, pos_mine, l);
       const int pair = __shfl_sync(0xffffffffu, pair_mine, l);
       const int64_t r = __shfl_sync(0xffffffffu, id_mine, l);
-      send_row(pos, pair, r);
+      send_row(pos, pair, r, 0, 1);
     }
   }
   }
@@ -701,6 +740,7 @@ cudaError_t launch_ep_dispatch(const EpDispatchArgs& a, cudaStream_t s) {
   p.ctx = a.ctx;
   p.symm = to_dev(a.symm);
   p.wait_recv = 1;
+  p.parts = (a.parts == 2 || a.parts == 4 || a.parts == 8) ? a.parts : 1;
   const int ctas = a.num_ctas > 0 ? a.num_ctas : 64;
   ep_dispatch_kernel<<<ctas, kEpThreads, 0, s>>>(p);
   return cudaGetLastError();
@@ -756,6 +796,7 @@ cudaError_t launch_ep_finish(const EpFinishArgs& a, cudaStream_t s) {
   p.meta = a.meta;
   p.real_rows = a.real_rows;
   p.cap = a.cap;
+  p.parts = (a.parts == 2 || a.parts == 4 || a.parts == 8) ? a.parts : 1;
   const int ctas = a.num_ctas > 0 ? a.num_ctas : 64;
   ep_finish_kernel<<<ctas, kEpThreads, 0, s>>>(p);
   return cudaGetLastError();
@@ -772,6 +813,7 @@ cudaError_t launch_ep_combine(const EpCombineArgs& a, cudaStream_t s) {
   p.sort_meta = a.sort_meta;
   p.real_rows = a.sorted_ids != nullptr ? a.real_rows : nullptr;
   p.real_cap = a.real_cap;
+  p.parts = (a.parts == 2 || a.parts == 4 || a.parts == 8) ? a.parts : 1;
   p.recv_meta = a.recv_meta;
   p.dctx = a.dispatch_ctx;
   p.base_self = a.base_self;

@@ -20,6 +20,7 @@ struct EpDispatchArgs {
   int32_t* cursor;            // local [E], zero on entry (the kernel leaves it zero)
   int32_t* sent_row;          // local [T*k]
   int num_ctas;
+  int parts = 1;              // warps that share a row (1, 2, 4, 8): more for few rows (latency), 1 for many (throughput)
   CtxDev* ctx;
   SymmInfoHost symm;
 };
@@ -51,6 +52,7 @@ struct EpFinishArgs {
   int32_t* real_rows;         // [cap + 1] packed list of the sorted rows that carry a token; [cap] = their number
   int64_t cap;                // multiple of 128
   int num_ctas;
+  int parts = 1;              // warps per token row
 };
 cudaError_t launch_ep_finish(const EpFinishArgs& a, cudaStream_t s);
 
@@ -60,7 +62,8 @@ struct EpCombineArgs {
   const int32_t* sorted_ids = nullptr;   // [sorted rows] receive row per sorted row (-1 padding) + sort_meta {rows, tiles}:
   const int32_t* sort_meta = nullptr;    //   the send loop walks the sorted rows instead of the receive capacity
   const int32_t* real_rows = nullptr;    // optional, with sorted_ids: EpFinishArgs::real_rows of the matching dispatch
-  int64_t real_cap = 0;                  //   and its cap: one warp per token row, nothing is scanned
+  int64_t real_cap = 0;                  //   and its cap: `parts` warps per token row, nothing is scanned
+  int parts = 1;
   const int32_t* recv_meta;   // heap [2][recv rows]
   const CtxDev* dispatch_ctx;
   const int32_t* base_self;   // [E/W * W] packed layout, or null

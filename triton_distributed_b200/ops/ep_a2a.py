@@ -165,10 +165,16 @@ def _cpu_combine(ctx: AllToAllContext, y_sorted, recv: EpRecv, topk_w):
     return out.to(y_sorted.dtype)
 
 
-def _ctas_for_rows(rows: int) -> int:
-    """One warp moves one row at a time and a row is a handful of memory round trips, so the kernels are latency-bound
-    until many warps work: 64 CTAs (512 warps) for a decode step, up to four per SM for prefill-sized batches."""
-    return int(min(592, max(64, rows // 8)))
+def _parts_for_rows(rows: int) -> int:
+    """Warps that share one row.  Moving a row is a chain of dependent memory round trips; a decode step has few rows,
+    so several warps per row cut the latency, while a prefill-sized batch keeps one warp per row for throughput."""
+    return 4 if rows <= 1024 else 2 if rows <= 2048 else 1
+
+
+def _ctas_for_rows(rows: int, parts: int = 1) -> int:
+    """Eight warps per CTA, ``parts`` warps per row: at least 64 CTAs for a decode step, up to four per SM for
+    prefill-sized batches."""
+    return int(min(592, max(64, rows * parts // 8)))
 
 
 # ------------------------------------------------------------------ public ops
@@ -187,9 +193,10 @@ def ep_dispatch(ctx: AllToAllContext, x: torch.Tensor, topk_ids: torch.Tensor) -
         lib.ep_layout(counts_all.contiguous(), ctx.base, epr, W, E)
         base = ctx.base
         base_self = ctx.base[ctx.rank].reshape(-1)
+    parts = _parts_for_rows(ids.numel())
     lib.ep_dispatch(rt.heap, x.contiguous(), ids, E, ctx.quant, ctx.max_m, ctx.recv_x, ctx.recv_scale, ctx.recv_meta,
                     ctx.recv_count, ctx.flags, ctx.rows_per_parity, base, ctx.cursor, ctx.sent_row, ctx.dctx,
-                    _ctas_for_rows(ids.numel()), rt.config.wait_timeout_s)
+                    _ctas_for_rows(ids.numel(), parts), rt.config.wait_timeout_s, parts)
     # Receive side, one launch: the receive areas are grouped by (expert, source) already, so the grouped-GEMM layout
     # (rows sorted by local expert, 128-row padding) follows from the epr x W counts; fp8 rows are de-quantised while
     # they are moved.  sorted_ids index receive rows; nothing scans the receive capacity.
@@ -197,7 +204,7 @@ def ep_dispatch(ctx: AllToAllContext, x: torch.Tensor, topk_ids: torch.Tensor) -
     cap = (cap + 127) // 128 * 128
     xs, sid, tile_expert, offsets, meta, counts, real_rows = lib.ep_finish(
         ctx.recv_x, ctx.recv_scale, ctx.recv_count, base_self, epr, W, ctx.max_m, ctx.hidden, ctx.quant, ctx.rows_per_parity,
-        ctx.dctx, cap, _ctas_for_rows(min(cap, W * ids.numel())))
+        ctx.dctx, cap, _ctas_for_rows(min(cap, W * ids.numel()), parts), parts)
     srt = MoESort(sid, None, tile_expert, offsets, meta, counts, 1)
     return EpRecv(xs, srt, ctx.rows_per_parity, ids, counts=ctx.recv_count, real_rows=real_rows)
 
@@ -210,10 +217,11 @@ def ep_combine(ctx: AllToAllContext, y_sorted: torch.Tensor, recv: EpRecv, topk_
     rt = ctx.rt
     base_self = ctx.base[ctx.rank].reshape(-1) if ctx.layout == "packed" else None
     w = topk_w.float().contiguous() if topk_w is not None else None
+    parts = _parts_for_rows(recv.topk_ids.numel())
     return lib.ep_combine(rt.heap, y_sorted.contiguous(), recv.sort.pos_of, ctx.recv_meta, ctx.dctx, base_self, ctx.max_m,
                           ctx.rows_per_parity, ctx.ret, ctx.ret_flags, recv.topk_ids, w, ctx.num_tot_experts, ctx.cctx,
-                          _ctas_for_rows(recv.topk_ids.numel()), rt.config.wait_timeout_s,
-                          recv.sort.sorted_ids, recv.sort.meta, recv.real_rows)
+                          _ctas_for_rows(recv.topk_ids.numel(), parts), rt.config.wait_timeout_s,
+                          recv.sort.sorted_ids, recv.sort.meta, recv.real_rows, parts)
 
 
 def fast_all_to_all(ctx: AllToAllContext, send_tensor: torch.Tensor, send_split_cumsum: torch.Tensor,
