@@ -27,7 +27,9 @@ def main():
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--steps", type=int, default=32)
-    ap.add_argument("--arms", default="torch,torch_graph,gemm_ar_graph,mega")
+    ap.add_argument("--arms", default="torch,torch_graph,gemm_ar_graph,mega",
+                    help="also: mega_prefetch (megakernel with L2 prefetch tasks), prefill (see --prefill)")
+    ap.add_argument("--prefill", type=int, default=2048, help="prompt length of the `prefill` arm (batch 1)")
     args = ap.parse_args()
     tdb.initialize_distributed(seed=0)
     rt = tdb.get_runtime()
@@ -108,14 +110,36 @@ def main():
         g = graphed("triton_dist_gemm_ar")
         emit("fused_gemm_ar_cuda_graph", timed(g.replay, reset))
         del g
-    if "mega" in arms:
-        mega = Qwen3Model(model, cache, B)
+    if "prefill" in arms:
+        # one prompt of --prefill tokens through the whole model: NCCL + cuBLAS layers against the overlapped layers
+        P = args.prefill
+        pcache = KV_Cache(a.num_hidden_layers, 1, P + 8, max(1, a.num_key_value_heads // W), a.head_dim, device=dev)
+        pids = torch.randint(0, a.vocab_size, (1, P), device=dev)
+        ppos = torch.arange(P, device=dev).unsqueeze(0)
+
+        def prefill_step():
+            pcache.kv_offset.zero_()
+            model.inference(pids, ppos, pcache)
+
+        for mode in ("torch", "triton_dist"):
+            if mode != "torch":
+                model.init_ctx_for(mode, P)
+            model.set_fwd(mode)
+            ms = timed(prefill_step, lambda: None)
+            if rt.rank == 0:
+                print(json.dumps({"arm": f"prefill_{mode}", "model": args.model, "layers": a.num_hidden_layers, "tp": W,
+                                  "tokens": P, "ms": ms}), flush=True)
+        del pcache
+    for arm_name, pre in (("mega", False), ("mega_prefetch", True)):
+        if arm_name not in arms:
+            continue
+        mega = Qwen3Model(model, cache, B, prefetch=pre)
 
         def mega_step():
             logits.copy_(mega.mega_forward(ids))
             cache.inc_offset(1)
 
-        emit("megakernel", timed(mega_step, reset))
+        emit("megakernel" + ("_prefetch" if pre else ""), timed(mega_step, reset))
         g = torch.cuda.CUDAGraph()
         reset()
         for _ in range(2):
@@ -127,7 +151,8 @@ def main():
             mega_step()
         torch.cuda.synchronize()
         rt.host_barrier()
-        emit("megakernel_cuda_graph", timed(g.replay, reset))
+        emit("megakernel" + ("_prefetch" if pre else "") + "_cuda_graph", timed(g.replay, reset))
+        del mega, g
     torch.cuda.synchronize()
     rt.host_barrier()
     sys.stdout.flush()

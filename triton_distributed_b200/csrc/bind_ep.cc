@@ -165,6 +165,19 @@ void a2a_single(SymmHeap& h, const at::Tensor& in, at::Tensor& out, const at::Te
              "launch_a2a_single");
 }
 
+void a2a_cols(SymmHeap& h, const at::Tensor& in, at::Tensor& out, int64_t s_local, at::Tensor& flags, at::Tensor& ctx,
+              int64_t parts, double timeout_s) {
+  TORCH_CHECK(in.dim() == 2 && in.stride(1) == 1 && out.dim() == 2 && out.is_contiguous() && flags.numel() >= 16,
+              "a2a_cols: in [S, C] with unit column stride, out [max s_local, W * C] contiguous, flags [2][8]");
+  c10::cuda::CUDAGuard guard(in.device());
+  const int64_t row_bytes = in.size(1) * in.element_size();
+  check_cuda(tdb::launch_a2a_cols(in.data_ptr(), in.stride(0) * in.element_size(), out.data_ptr(),
+                                  static_cast<uint64_t>(out.numel()) * out.element_size(), row_bytes, s_local,
+                                  reinterpret_cast<uint32_t*>(flags.data_ptr()), ctxp(ctx), h.info(ns(timeout_s)), parts,
+                                  cur_stream()),
+             "launch_a2a_cols");
+}
+
 std::vector<at::Tensor> fp8_quant(const at::Tensor& x) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(), "fp8_quant: bf16 [T,H]");
   c10::cuda::CUDAGuard guard(x.device());
@@ -203,6 +216,7 @@ void bind_ep(py::module_& m) {
         py::arg("timeout_s"), py::arg("sorted_ids") = py::none(), py::arg("sort_meta") = py::none(),
         py::arg("real_rows") = py::none(), py::arg("parts") = 1);
   m.def("a2a_single", &a2a_single);
+  m.def("a2a_cols", &a2a_cols);
   m.def("fp8_quant", &fp8_quant);
   m.def("fp8_dequant", &fp8_dequant);
 }

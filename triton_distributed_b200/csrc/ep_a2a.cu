@@ -682,6 +682,84 @@ __global__ void __launch_bounds__(kEpThreads) a2a_single_kernel(const A2AParams 
   }
 }
 
+// ---------------------------------------------------------------------------
+// Head-to-sequence exchange of Ulysses sequence parallelism: `in` holds all S = W * s_local positions restricted to this
+// rank's head block ([S][row_bytes], pitch in_pitch).  The rows [d * s_local, (d + 1) * s_local) go to rank d, which
+// assembles [s_local][W * row_bytes]: source rank r fills the column block [r * row_bytes, (r + 1) * row_bytes) of every
+// row.  out: heap [s_local][W * row_bytes], ONE buffer (the result is at a fixed address, so a CUDA graph that
+// captured a consumer of it stays valid).  A rank may only write into a peer's buffer when that peer has finished
+// reading the previous result, i.e. when it has entered this call: CTA 0 of every rank announces its entry first
+// thing, and every CTA waits for the announcement of its destination before it stores (a wait on a remote CTA 0,
+// which is always scheduled).  The kernel returns when the blocks of all sources have arrived.
+// flags: heap [2][W] = entry announcements, arrival flags; both carry the call epoch kept on the device.
+// Reference: kernels/nvidia/sp_ulysess_o_all2all_gemm.py:299-392 (per-tile push of the attention output).
+// ---------------------------------------------------------------------------
+struct A2AColsParams {
+  const char* in;
+  char* out;                   // heap [s_local][W * row_bytes]
+  int64_t in_pitch, row_bytes;
+  int s_local;
+  uint32_t* flags;             // heap [2][W]
+  CtxDev* ctx;
+  SymmInfo symm;
+};
+
+__global__ void __launch_bounds__(kEpThreads) a2a_cols_kernel(const A2AColsParams p) {
+  const uint32_t epoch = ld_volatile(&p.ctx->epoch);
+  const int W = p.symm.world, rank = p.symm.rank;
+  const int parts = gridDim.x / W;
+  const int dst = blockIdx.x % W, part = blockIdx.x / W;
+  __shared__ int s_go;
+  if (blockIdx.x == 0 && threadIdx.x < W)
+    st_release_sys(symm_at(p.symm, p.flags + rank, (rank + threadIdx.x) % W), epoch);
+  if (threadIdx.x == 0)
+    s_go = wait_until(p.symm, p.flags + dst, epoch, kCmpGe, kKernelA2A, 3, dst, 0) ? 1 : 0;
+  __syncthreads();
+  if (part < parts && s_go) {
+    const int64_t out_pitch = static_cast<int64_t>(W) * p.row_bytes;
+    char* obase = symm_at(p.symm, p.out, dst) + rank * p.row_bytes;
+    const char* ibase = p.in + static_cast<int64_t>(dst) * p.s_local * p.in_pitch;
+    const int nvec = static_cast<int>(p.row_bytes >> 4);
+    const int warps = kEpThreads / 32, lane = threadIdx.x & 31;
+    for (int r = part * warps + (threadIdx.x >> 5); r < p.s_local; r += parts * warps) {
+      const char* s = ibase + r * p.in_pitch;
+      char* d = obase + r * out_pitch;
+      int i = lane;
+      for (; i + 96 < nvec; i += 128) {
+        const uint4 v0 = ld_nc_v4(s + (i << 4)), v1 = ld_nc_v4(s + ((i + 32) << 4)), v2 = ld_nc_v4(s + ((i + 64) << 4)),
+                    v3 = ld_nc_v4(s + ((i + 96) << 4));
+        st_v4(d + (i << 4), v0);
+        st_v4(d + ((i + 32) << 4), v1);
+        st_v4(d + ((i + 64) << 4), v2);
+        st_v4(d + ((i + 96) << 4), v3);
+      }
+      for (; i < nvec; i += 32) st_v4(d + (i << 4), ld_nc_v4(s + (i << 4)));
+    }
+  }
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(&p.ctx->grid_bar, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x < W) {
+      __threadfence();
+      fence_acq_rel_sys();
+      st_release_sys(symm_at(p.symm, p.flags + W + rank, (rank + threadIdx.x) % W), epoch);
+      wait_until(p.symm, p.flags + W + threadIdx.x, epoch, kCmpGe, kKernelA2A, 2, threadIdx.x, 0);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      p.ctx->grid_bar = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(&p.ctx->epoch) = epoch + 1;
+    }
+  }
+}
+
 // ---- stand-alone quantisation ---------------------------------------------------------------------------------
 __global__ void fp8_quant_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ s, int64_t T,
                                  int H) {
@@ -859,6 +937,24 @@ cudaError_t launch_a2a_single(const void* in, void* out, const int32_t* splits_a
   p.symm = to_dev(symm);
   if (parts < 1) parts = 1;
   a2a_single_kernel<<<symm.world * parts, kEpThreads, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_a2a_cols(const void* in, int64_t in_pitch, void* out, uint64_t out_bytes, int64_t row_bytes, int s_local,
+                            uint32_t* flags, CtxDev* ctx, const SymmInfoHost& symm, int parts, cudaStream_t s) {
+  if (row_bytes % 16 != 0 || in_pitch % 16 != 0 || s_local < 0) return cudaErrorInvalidValue;
+  if (static_cast<uint64_t>(s_local) * symm.world * row_bytes > out_bytes) return cudaErrorInvalidValue;
+  A2AColsParams p;
+  p.in = reinterpret_cast<const char*>(in);
+  p.out = reinterpret_cast<char*>(out);
+  p.in_pitch = in_pitch;
+  p.row_bytes = row_bytes;
+  p.s_local = s_local;
+  p.flags = flags;
+  p.ctx = ctx;
+  p.symm = to_dev(symm);
+  if (parts < 1) parts = 1;
+  a2a_cols_kernel<<<symm.world * parts, kEpThreads, 0, s>>>(p);
   return cudaGetLastError();
 }
 

@@ -84,6 +84,11 @@ cudaError_t launch_ep_combine(const EpCombineArgs& a, cudaStream_t s);
 
 cudaError_t launch_a2a_single(const void* in, void* out, const int32_t* splits_all, int64_t row_bytes, uint32_t* flags,
                               CtxDev* ctx, const SymmInfoHost& symm, int parts, cudaStream_t s);
+// Ulysses head-to-sequence exchange: rows [d * s_local, ...) of `in` ([W * s_local][row_bytes], pitch in_pitch) go to
+// rank d's out [s_local][W * row_bytes] (heap, one buffer; peers are written only after they have entered the call),
+// column block [rank * row_bytes, ...).  flags: heap [2][W].  Returns when all sources' blocks have arrived.
+cudaError_t launch_a2a_cols(const void* in, int64_t in_pitch, void* out, uint64_t out_bytes, int64_t row_bytes, int s_local,
+                            uint32_t* flags, CtxDev* ctx, const SymmInfoHost& symm, int parts, cudaStream_t s);
 cudaError_t launch_fp8_quant(const void* x, void* q, float* scales, int64_t T, int H, cudaStream_t s);
 cudaError_t launch_fp8_dequant(const void* q, const float* scales, void* out, int64_t T, int H, cudaStream_t s);
 
