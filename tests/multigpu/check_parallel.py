@@ -60,7 +60,34 @@ def check_sp_attention(rt):
             err = (out.float() - ref).abs().max().item()
             assert err < 3e-2, f"sp attention zig_zag={zig} it={it}: err {err}"
         ctx.finalize()
-    log(rt, "OK SP all-gather attention (zig-zag and plain)")
+    # sequences of different lengths in one packed batch
+    for zig in (True, False):
+        n_chunks = 2 * W if zig else W
+        lens = [48 * n_chunks, 16 * n_chunks, 80 * n_chunks]
+        g = torch.Generator(device="cuda").manual_seed(9)
+        qs = [torch.randn(n, Hq, D, device="cuda", generator=g).to(torch.bfloat16) for n in lens]
+        ks = [torch.randn(n, Hkv, D, device="cuda", generator=g).to(torch.bfloat16) for n in lens]
+        vs = [torch.randn(n, Hkv, D, device="cuda", generator=g).to(torch.bfloat16) for n in lens]
+        mine = [rank, 2 * W - 1 - rank] if zig else [rank]
+
+        def shard_v(xs):
+            return torch.cat([x[ch * (n // n_chunks):(ch + 1) * (n // n_chunks)] for x, n in zip(xs, lens) for ch in mine],
+                             0).contiguous()
+
+        ctx = create_sp_ag_attention_context_intra_node(1, Hq, Hkv, sum(lens), D)
+        loc = [len(mine) * (n // n_chunks) for n in lens]
+        cu_q = torch.tensor([0] + torch.tensor(loc).cumsum(0).tolist(), dtype=torch.int32)
+        cu_k = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32)
+        out = fused_sp_ag_attn_intra_node(ctx, shard_v(qs), shard_v(ks), shard_v(vs), None, cu_q, cu_k, max(loc), max(lens),
+                                          is_causal=True, enable_zig_zag=zig)
+        torch.cuda.synchronize()
+        rt.check_status()
+        ref = torch.cat([attn_ref(qs[b], ks[b], vs[b])[ch * (n // n_chunks):(ch + 1) * (n // n_chunks)]
+                         for b, n in enumerate(lens) for ch in mine], 0)
+        err = (out.float() - ref).abs().max().item()
+        assert err < 3e-2, f"sp attention var-len zig_zag={zig}: err {err}"
+        ctx.finalize()
+    log(rt, "OK SP all-gather attention (zig-zag and plain, equal and different sequence lengths)")
 
 
 def check_ulysses(rt):

@@ -45,6 +45,27 @@ def _sp_attention(rank, world):
                                           is_causal=True, enable_zig_zag=zig)
         ref = torch.cat([_attn_ref(q[b], k[b], v[b])[ch * c:(ch + 1) * c] for b in range(B) for ch in mine], 0)
         assert (out.float() - ref).abs().max().item() < 1e-4, f"sp attention zig_zag={zig}"
+    # sequences of different lengths in one packed batch (page size = gcd of the chunk lengths)
+    lens = [96, 32, 64]
+    qs = [torch.randn(n, Hq, D, generator=g) for n in lens]
+    ks = [torch.randn(n, Hkv, D, generator=g) for n in lens]
+    vs = [torch.randn(n, Hkv, D, generator=g) for n in lens]
+    for zig in (True, False):
+        n_chunks = 2 * world if zig else world
+        mine = [rank, 2 * world - 1 - rank] if zig else [rank]
+
+        def shard(xs):
+            return torch.cat([x[ch * (n // n_chunks):(ch + 1) * (n // n_chunks)] for x, n in zip(xs, lens) for ch in mine], 0)
+
+        ctx = create_sp_ag_attention_context_intra_node(1, Hq, Hkv, sum(lens), D, input_dtype=torch.float32)
+        loc = [len(mine) * (n // n_chunks) for n in lens]
+        cu_q = torch.tensor([0] + list(torch.tensor(loc).cumsum(0)), dtype=torch.int32)
+        cu_k = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+        out = fused_sp_ag_attn_intra_node(ctx, shard(qs), shard(ks), shard(vs), None, cu_q, cu_k, max(loc), max(lens),
+                                          is_causal=True, enable_zig_zag=zig)
+        ref = torch.cat([_attn_ref(qs[b], ks[b], vs[b])[ch * (n // n_chunks):(ch + 1) * (n // n_chunks)]
+                         for b, n in enumerate(lens) for ch in mine], 0)
+        assert (out.float() - ref).abs().max().item() < 1e-4, f"sp attention var-len zig_zag={zig}"
     tdb.finalize_distributed()
 
 

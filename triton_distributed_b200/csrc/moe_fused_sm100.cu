@@ -49,7 +49,6 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kBarOffset = kStages * kStageBytes;
 constexpr int kSmemTotal = kBarOffset + (2 * kStages + 4) * 8 + 16;
 constexpr int kThreads = 320;             // warp 0 B producer, 1 MMA, 2-5 epilogue, 6-9 A gather
-constexpr int kGatherAhead = kStages - 1; // cp.async groups a gather thread keeps in flight
 
 constexpr int kPushPiece = 32 * 1024;
 constexpr int kPushSlots = 6;
@@ -101,6 +100,11 @@ TDB_DEVICE void cp_async_16(uint32_t smem_dst, const void* gsrc, bool valid) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(sz) : "memory");
 }
 TDB_DEVICE void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// One (deferred) arrival on an mbarrier that happens when all cp.async copies this thread has issued so far have
+// landed; the thread does not wait.  The barrier's count must include the arrival (.noinc).
+TDB_DEVICE void cp_async_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 template <int N>
 TDB_DEVICE void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -391,7 +395,7 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmap_b, const MoeParams p) 
   } else {
     if (threadIdx.x == 0) {
       for (int i = 0; i < kStages; ++i) {
-        mbar_init(&full_bar[i], 5);      // four gather warps + the B producer's expect_tx arrival
+        mbar_init(&full_bar[i], 129);    // 128 gather threads (deferred arrivals) + the B producer's expect_tx arrival
         mbar_init(&empty_bar[i], 1);
       }
       for (int i = 0; i < 2; ++i) {
@@ -484,6 +488,9 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmap_b, const MoeParams p) 
               report(p.symm, kTimeoutMbarrier, kKernelGroupGemm, 21, -1, s, (int)ph, w);
               break;
             }
+            // the A rows were written by cp.async of the gather threads (generic proxy), whose completion this thread
+            // has just observed through the barrier: order them before the tensor core's (async proxy) reads
+            fence_proxy_async_smem();
             tc_fence_after_sync();
             const uint32_t sa = smem_u32(smem + s * kStageBytes);
             const uint64_t adesc = make_smem_desc_sw128(sa);
@@ -574,19 +581,12 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmap_b, const MoeParams p) 
       const int g = threadIdx.x - 192;
       const int piece = g & 7;
       const int row0 = g >> 3;
+      // A thread never waits for its copies: after the eight copies of a k-block it leaves a deferred arrival on the
+      // stage's barrier (cp.async.mbarrier.arrive.noinc), which fires when they have landed.  So every free stage of the
+      // ring is in flight, and a stage is handed to the tensor core the moment its last copy lands (tying the hand-off to
+      // the issue of a later stage made every MMA wait for the completion of its predecessor).
       uint32_t it = 0;          // k-blocks issued (stage ring position)
-      uint32_t done = 0;        // k-blocks whose stage has been handed to the tensor core
       bool ok = true;
-      auto publish = [&](uint32_t upto) {
-        // the copies of k-blocks [done, upto) of this thread have landed: make them visible to the async proxy and
-        // arrive (one arrival per warp) on their stages
-        while (done < upto) {
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full_bar[done % kStages]);
-          ++done;
-        }
-      };
       for (int w = g_idx; w < num_items && ok; w += n_gemm) {
         int mt, nt, ch;
         decode(w, &mt, &nt, &ch);
@@ -634,16 +634,11 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmap_b, const MoeParams p) 
             cp_async_16(sa + r * 128 + ((piece ^ (r & 7)) << 4),
                         valid ? src[i] + static_cast<int64_t>(kcol) * 2 : reinterpret_cast<const char*>(p.x), valid);
           }
-          cp_async_commit();
-          // keep kGatherAhead groups in flight: everything older has landed
-          if (it + 1 - done > static_cast<uint32_t>(kGatherAhead)) {
-            cp_async_wait<kGatherAhead>();
-            publish(it + 1 - kGatherAhead);
-          }
+          cp_async_arrive_noinc(&full_bar[s]);
         }
       }
-      cp_async_wait<0>();
-      if (ok) publish(it);
+      cp_async_commit();
+      cp_async_wait<0>();       // nothing of this thread is in flight when the CTA winds down
     }
 
     // ------------------------------------------------------------ teardown

@@ -68,7 +68,8 @@ def fused_sp_ag_attn_intra_node(ctx: SPAllGatherAttentionContextIntraNode, q_sha
                                 cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, rank: Optional[int] = None,
                                 world_size: Optional[int] = None, is_causal: bool = True, enable_zig_zag: bool = True):
     """q/k/v_shard: [tokens_local, heads, D] packed over the batch; ``cu_seqlens_q`` gives the LOCAL token ranges per
-    sequence, ``cu_seqlens_k`` the GLOBAL lengths (each sequence length divisible by ``W`` or ``2W`` with zig-zag)."""
+    sequence, ``cu_seqlens_k`` the GLOBAL lengths (each sequence length divisible by ``W``, or ``2W`` with zig-zag;
+    the sequences may differ in length)."""
     rt = ctx.rt
     W = rt.world_size if world_size is None else world_size
     rank = rt.rank if rank is None else rank
@@ -93,40 +94,55 @@ def fused_sp_ag_attn_intra_node(ctx: SPAllGatherAttentionContextIntraNode, q_sha
     else:
         k_all, v_all, per_rank = k_shard.unsqueeze(0), v_shard.unsqueeze(0), t_local
     Hkv, D = k_shard.shape[1], k_shard.shape[2]
-    # --- paged view: page = one chunk of one sequence; all sequences must share the chunk length for one page size
+    # --- paged view of the gathered K / V.  A rank holds, packed over the batch, its chunks of every sequence (chunk r,
+    # and with zig-zag chunk 2W-1-r right behind it).  Sequences may differ in length: the page size is the largest
+    # token count that divides every chunk length (and the per-rank stride of the gathered buffer), so that every chunk
+    # is a whole number of pages and the block table can undo the zig-zag permutation without moving data.
+    import math
     lens = [cu_k[b + 1] - cu_k[b] for b in range(B)]
-    chunk = lens[0] // n_chunks
-    assert all(l == lens[0] for l in lens) and lens[0] % n_chunks == 0, \
-        "sequence lengths must be equal and divisible by the number of chunks"
-    k_pages = k_all.reshape(-1, Hkv, D)[: (W * per_rank) // chunk * chunk].reshape(-1, chunk, Hkv, D)
-    v_pages = v_all.reshape(-1, Hkv, D)[: (W * per_rank) // chunk * chunk].reshape(-1, chunk, Hkv, D)
-    pages_per_rank = per_rank // chunk
+    if any(l % n_chunks for l in lens) or any(l <= 0 for l in lens):
+        raise ValueError("sp attention: every sequence length must be a positive multiple of the number of chunks "
+                         f"({n_chunks})")
+    chunk_of = [l // n_chunks for l in lens]
     cpr = len(mine)   # chunks per rank per sequence
-    # physical page of logical chunk c of sequence b: owner rank r holds its chunks of sequence b at local pages
-    # b * cpr + (0 for chunk r, 1 for chunk 2W-1-r)
+    if sum(cpr * c for c in chunk_of) != t_local:
+        raise ValueError("sp attention: the local shard does not hold cu_seqlens_k / world tokens of every sequence")
+    page = math.gcd(*chunk_of, per_rank) if W > 1 else math.gcd(*chunk_of)
+    k_pages = k_all.reshape(-1, Hkv, D)[: (W * per_rank) // page * page].reshape(-1, page, Hkv, D)
+    v_pages = v_all.reshape(-1, Hkv, D)[: (W * per_rank) // page * page].reshape(-1, page, Hkv, D)
+    pages_per_rank = per_rank // page
+    # first local token of sequence b on any rank
+    seq_off = [0]
+    for c in chunk_of:
+        seq_off.append(seq_off[-1] + cpr * c)
     dev = q_shard.device
-    bt = torch.empty((B, n_chunks), dtype=torch.int32)
+    max_pages = max(lens) // page
+    bt = torch.zeros((B, max_pages), dtype=torch.int32)
     for b in range(B):
+        cb = chunk_of[b]
+        ppc = cb // page                      # pages per chunk
         for c in range(n_chunks):
             if enable_zig_zag:
                 owner, idx = (c, 0) if c < W else (2 * W - 1 - c, 1)
             else:
                 owner, idx = c, 0
-            bt[b, c] = owner * pages_per_rank + b * cpr + idx
+            first = owner * pages_per_rank + (seq_off[b] + idx * cb) // page
+            bt[b, c * ppc:(c + 1) * ppc] = torch.arange(first, first + ppc, dtype=torch.int32)
     # --- var-len batch with one entry per (sequence, local chunk)
     entries_q, pos0, kv_len, table_rows = [0], [], [], []
     for b in range(B):
         for i, c in enumerate(mine):
-            entries_q.append(entries_q[-1] + chunk)
-            pos0.append(c * chunk)
-            kv_len.append((c + 1) * chunk if is_causal else lens[b])
+            entries_q.append(entries_q[-1] + chunk_of[b])
+            pos0.append(c * chunk_of[b])
+            kv_len.append((c + 1) * chunk_of[b] if is_causal else lens[b])
             table_rows.append(b)
+    max_q = max(chunk_of)
     cu = torch.tensor(entries_q, dtype=torch.int32, device=dev)
     q_pos0 = torch.tensor(pos0, dtype=torch.int32, device=dev)
     kv_lens = torch.tensor(kv_len, dtype=torch.int32, device=dev)
     table = bt[table_rows].contiguous().to(dev)
     out = ops.flash_attn_varlen(q_shard.contiguous(), k_pages.contiguous() if not k_pages.is_contiguous() else k_pages,
-                                v_pages.contiguous() if not v_pages.is_contiguous() else v_pages, table, cu, kv_lens, chunk,
+                                v_pages.contiguous() if not v_pages.is_contiguous() else v_pages, table, cu, kv_lens, max_q,
                                 q_pos0=q_pos0, causal=is_causal)
     if output is not None:
         output.copy_(out)
