@@ -108,6 +108,17 @@ def bench_gemm_ar(rt, Ms, k_local=0):
             rec["kernel"] = "tcgen05 swap-AB"
             rec["splits"] = ops.gemm_ar.pick_gemm_ar_splits(M, N, K)
 
+        if M >= 32:
+            # the unfused pair of own kernels: tcgen05 GEMM (128-row tiles, lib entry, not the decode dispatch) + own all-reduce
+            part = torch.empty(M, N, device=rt.device, dtype=torch.bfloat16)
+            lib = tdb._native.load(True)
+
+            def two():
+                lib.gemm_bf16(x, w, part, 128, 0, None)
+                ops.all_reduce(part, ctx=gctx.ar_ctx, output=out)
+
+            rec["own_gemm_then_ar_us"] = round(timed(two, rt), 2)
+
         def ref():
             torch.matmul(x, wt, out=out)
             dist.all_reduce(out, group=rt.group)

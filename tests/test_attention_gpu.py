@@ -69,3 +69,30 @@ def test_prefill_causal(cfg):
     ref2 = attention_reference(q, k, v, bt, cu, kv_lens, None, False)
     out2 = flash_attn_varlen(q, k, v, bt, cu, kv_lens, max(qlens), causal=False)
     torch.testing.assert_close(out2.float(), ref2.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("impl", ["sm100", "mma"])
+@pytest.mark.parametrize("cfg", [(2, 8, 2, 16, [300, 129], [300, 500], None),
+                                 (1, 16, 8, 64, [1024], [1024], None),
+                                 (2, 4, 1, 128, [128, 200], [384, 700], [256, 100])])
+def test_prefill_both_kernels(cfg, impl):
+    """The tcgen05 prefill kernel (KV packed into dense K / V^T, S and PV in TMEM) and the mma.sync kernel against the
+    fp32 reference: ragged batches, paged caches with shuffled pages, explicit query positions (context-parallel chunks),
+    causal and not."""
+    from triton_distributed_b200.ops import attention_reference, flash_attn_varlen
+    from triton_distributed_b200.ops.attention import check_attention_errors
+
+    B, Hq, Hkv, page, qlens, kvlens, pos0 = cfg
+    D = 128
+    k, v, bt = _paged_cache(B, max(kvlens), Hkv, D, page, seed=2)
+    q = torch.randn(sum(qlens), Hq, D, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device="cuda")
+    kv_lens = torch.tensor(kvlens, dtype=torch.int32, device="cuda")
+    qp = None if pos0 is None else torch.tensor(pos0, dtype=torch.int32, device="cuda")
+    for causal in (True, False):
+        ref, ref_lse = attention_reference(q, k, v, bt, cu, kv_lens, qp, causal, None, 0.0, True)
+        out, lse = flash_attn_varlen(q, k, v, bt, cu, kv_lens, max(qlens), q_pos0=qp, causal=causal, return_lse=True, impl=impl)
+        torch.cuda.synchronize()
+        check_attention_errors()
+        torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(lse, ref_lse, rtol=1e-2, atol=1e-2)

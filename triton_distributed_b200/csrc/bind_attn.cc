@@ -73,6 +73,59 @@ at::Tensor flash_fwd(const at::Tensor& q, const at::Tensor& k_cache, const at::T
   return out;
 }
 
+// Prefill attention on the tcgen05 path (head dim 128).  Returns (out, error flag int32[1]: non-zero if a bounded wait
+// inside the kernel gave up).
+std::vector<at::Tensor> flash_fwd_sm100(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
+                                        const at::Tensor& block_table, const at::Tensor& cu_seqlens_q, const at::Tensor& kv_lens,
+                                        c10::optional<at::Tensor> q_pos0, int64_t max_q_len, int64_t max_kv_len, bool causal,
+                                        double scale, c10::optional<at::Tensor> lse) {
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && q.scalar_type() == at::kBFloat16 && q.size(2) == 128,
+              "flash_fwd_sm100: q must be contiguous bf16 [T, Hq, 128]");
+  TORCH_CHECK(k_cache.scalar_type() == at::kBFloat16 && v_cache.scalar_type() == at::kBFloat16 && k_cache.is_contiguous() &&
+                  v_cache.is_contiguous() && k_cache.size(3) == 128,
+              "flash_fwd_sm100: contiguous bf16 caches [pages, page, Hkv, 128]");
+  check_i32(cu_seqlens_q, "cu_seqlens_q");
+  check_i32(kv_lens, "kv_lens");
+  check_i32(block_table, "block_table");
+  c10::cuda::CUDAGuard guard(q.device());
+  tdb::FlashFwdSm100Args a;
+  at::Tensor out = at::empty_like(q);
+  at::Tensor err = at::zeros({1}, q.options().dtype(at::kInt));
+  a.q = q.data_ptr();
+  a.out = out.data_ptr();
+  a.lse = nullptr;
+  if (lse.has_value()) {
+    TORCH_CHECK(lse->scalar_type() == at::kFloat && lse->is_contiguous() && lse->numel() == q.size(0) * q.size(1),
+                "lse must be contiguous fp32 [Hq, T]");
+    a.lse = lse->data_ptr<float>();
+  }
+  a.cu_seqlens_q = cu_seqlens_q.data_ptr<int32_t>();
+  a.q_pos0 = nullptr;
+  if (q_pos0.has_value()) {
+    check_i32(*q_pos0, "q_pos0");
+    a.q_pos0 = q_pos0->data_ptr<int32_t>();
+  }
+  a.kv_lens = kv_lens.data_ptr<int32_t>();
+  a.kv = make_kv(k_cache, v_cache, block_table);
+  a.batch = kv_lens.numel();
+  a.max_q_len = max_q_len;
+  a.num_q_heads = q.size(1);
+  a.num_kv_heads = k_cache.size(2);
+  a.head_dim = 128;
+  a.total_q = q.size(0);
+  a.causal = causal ? 1 : 0;
+  a.scale = scale;
+  TORCH_CHECK(max_kv_len >= 1, "flash_fwd_sm100: max_kv_len must be positive");
+  a.Lp = static_cast<int>((max_kv_len + 63) / 64 * 64);
+  at::Tensor kd = at::empty({a.batch * a.num_kv_heads, a.Lp, 128}, q.options());
+  at::Tensor vt = at::empty({a.batch * a.num_kv_heads, 128, a.Lp}, q.options());
+  a.k_dense = kd.data_ptr();
+  a.vt_dense = vt.data_ptr();
+  a.error_flag = err.data_ptr<int32_t>();
+  check_cuda(tdb::launch_flash_fwd_sm100(a, cur_stream()), "launch_flash_fwd_sm100");
+  return {out, err};
+}
+
 tdb::DecodeArgs decode_args(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
                             const at::Tensor& block_table, const at::Tensor& kv_lens, at::Tensor& workspace,
                             int64_t splits, double scale, double softcap) {
@@ -160,6 +213,7 @@ int64_t dist_decode_attn(SymmHeap& h, const at::Tensor& q, const at::Tensor& k_c
 
 void bind_attn(py::module_& m) {
   m.def("flash_fwd", &flash_fwd);
+  m.def("flash_fwd_sm100", &flash_fwd_sm100);
   m.def("decode_attn", &decode_attn);
   m.def("dist_decode_attn", &dist_decode_attn, py::arg("heap"), py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
         py::arg("block_table"), py::arg("kv_lens"), py::arg("workspace"), py::arg("splits"), py::arg("scale"),

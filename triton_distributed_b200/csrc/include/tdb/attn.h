@@ -30,6 +30,29 @@ struct FlashFwdArgs {
 };
 cudaError_t launch_flash_fwd(const FlashFwdArgs& a, cudaStream_t stream);
 
+// Prefill on tcgen05 (attn_sm100.cu): head dim 128.  The launcher first packs the visible KV into dense tensors
+// (k_dense [batch * Hkv][Lp][128], vt_dense [batch * Hkv][128][Lp], both caller-provided scratch, Lp a multiple of 64 and
+// >= the longest kv_len), then runs the attention kernel.  error_flag (device int, may be null) is set if a bounded wait
+// inside the kernel gave up.
+struct FlashFwdSm100Args {
+  const void* q;
+  void* out;
+  float* lse;
+  const int32_t* cu_seqlens_q;
+  const int32_t* q_pos0;
+  const int32_t* kv_lens;
+  AttnKV kv;
+  int batch, max_q_len, num_q_heads, num_kv_heads, head_dim;
+  int64_t total_q;
+  int causal;
+  float scale;
+  int Lp;
+  void* k_dense;
+  void* vt_dense;
+  int* error_flag;
+};
+cudaError_t launch_flash_fwd_sm100(const FlashFwdSm100Args& a, cudaStream_t stream);
+
 struct DecodeArgs {
   const void* q;             // [batch, Hq, D]
   float* workspace;          // decode_workspace_floats(...) floats: partial out, then partial LSE

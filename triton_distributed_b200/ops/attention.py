@@ -10,6 +10,7 @@ cache ``[B, max_len, Hkv, D]`` is the case ``page_size = max_len`` with ``block_
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -67,17 +68,46 @@ def attention_reference(q, k_cache, v_cache, block_table, cu_seqlens_q, kv_lens,
     return out.to(q.dtype)
 
 
+SM100_PREFILL_MIN_Q = 128      # below this the 64-row mma.sync kernel has less padding and no KV packing pass
+_PENDING_ERRORS = []            # error flags of tcgen05 prefill launches that have not been looked at yet
+
+
+def check_attention_errors() -> None:
+    """Raise if a bounded wait inside a tcgen05 prefill kernel gave up since the last check (synchronises)."""
+    flags, _PENDING_ERRORS[:] = list(_PENDING_ERRORS), []
+    if any(int(f.item()) != 0 for f in flags):
+        raise RuntimeError("flash_fwd_sm100: a wait inside the kernel timed out")
+
+
 def flash_attn_varlen(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                       cu_seqlens_q: torch.Tensor, kv_lens: torch.Tensor, max_q_len: int,
                       q_pos0: Optional[torch.Tensor] = None, causal: bool = True, scale: Optional[float] = None,
-                      softcap: float = 0.0, return_lse: bool = False):
+                      softcap: float = 0.0, return_lse: bool = False, max_kv_len: Optional[int] = None,
+                      impl: str = "auto"):
     """Prefill / context attention.  ``q`` [T, Hq, D] packed; query row i of sequence b has absolute position
-    ``q_pos0[b] + i`` (default: the queries are the last ``q_len`` positions of the ``kv_lens[b]`` visible tokens)."""
+    ``q_pos0[b] + i`` (default: the queries are the last ``q_len`` positions of the ``kv_lens[b]`` visible tokens).
+
+    ``impl``: "auto" picks the tcgen05 kernel (head dim 128, no soft cap, at least ``SM100_PREFILL_MIN_Q`` query rows per
+    sequence) and otherwise the ``mma.sync`` kernel; "sm100" / "mma" force one.  ``max_kv_len`` (an upper bound of
+    ``kv_lens``) saves the tcgen05 path a device-to-host read."""
     D = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if _native.use_native(q, k_cache, v_cache) and q.dtype == torch.bfloat16 and D in (64, 128):
         lib = _native.load(True)
         lse = torch.empty((q.shape[1], q.shape[0]), dtype=torch.float32, device=q.device) if return_lse else None
+        sm100_ok = D == 128 and softcap == 0.0 and k_cache.dtype == torch.bfloat16 and os.environ.get("TDB200_ATTN_SM100", "1") != "0"
+        if impl == "sm100" and not sm100_ok:
+            raise ValueError("flash_attn_varlen: the tcgen05 kernel needs head dim 128, bf16 caches and no soft cap")
+        if impl == "sm100" or (impl == "auto" and sm100_ok and max_q_len >= SM100_PREFILL_MIN_Q):
+            if max_kv_len is None:
+                max_kv_len = int(kv_lens.max().item())
+            out, err = lib.flash_fwd_sm100(q.contiguous(), k_cache.contiguous(), v_cache.contiguous(), block_table.contiguous(),
+                                           cu_seqlens_q, kv_lens, q_pos0, int(max_q_len), max(int(max_kv_len), 1),
+                                           bool(causal), float(scale), lse)
+            _PENDING_ERRORS.append(err)
+            if len(_PENDING_ERRORS) > 64:
+                check_attention_errors()
+            return (out, lse) if return_lse else out
         out = lib.flash_fwd(q.contiguous(), k_cache, v_cache, block_table, cu_seqlens_q, kv_lens, q_pos0, int(max_q_len),
                             bool(causal), float(scale), float(softcap), lse)
         return (out, lse) if return_lse else out
