@@ -9,11 +9,14 @@
 //   flash_fwd_sm100_kernel  one CTA = 128 query rows of one head.  Warp 0 loads Q once and streams K / Vt blocks of
 //                           64 tokens by TMA (two stages); warp 1 issues tcgen05.mma: S = Q K^T (128 x 64, K = 128)
 //                           into TMEM, and after the softmax warps have written P (bf16, 128B-swizzled shared
-//                           memory) PV = P V (128 x 128, K = 64) into a second TMEM buffer; warps 2-5 (one thread
-//                           per query row) read S with tcgen05.ld, apply scale / mask / online softmax in the log2
-//                           domain, write P, then read PV and fold it into the output row kept in registers
-//                           (o = o * alpha + pv).  S of block j + 1 is issued as soon as S of block j has been read,
-//                           so the tensor core works during the exponentials.
+//                           memory) O += P V (128 x 128, K = 64), accumulated in a second TMEM buffer over all blocks;
+//                           warps 2-5 (one thread per query row) read S with tcgen05.ld, apply scale / mask / softmax
+//                           in the log2 domain and write P.  The output is NOT read back per block: the exponentials
+//                           use a reference maximum that is only raised when the row maximum has grown by more than
+//                           2^8 (P stays below 256, exact in the final division because O and the row sum share the
+//                           reference); only then the warp rescales its O rows in TMEM (tcgen05.ld / st).  S of block
+//                           j + 1 is issued as soon as S of block j has been read, so the tensor core works during the
+//                           exponentials; the output row is read once, after the last block.
 // Every wait is bounded; a timeout is recorded, the CTA stops issuing work, frees its TMEM and returns.
 //
 // Reference behaviour being matched (not its code): mega_triton_kernel/kernels/flash_attn.py:33-372 (TMA +
@@ -40,14 +43,25 @@ constexpr int kQBytes = kBM * kD * 2;        // 32 KB: two [128 x 64] swizzled h
 constexpr int kKBytes = kBN * kD * 2;        // 16 KB: two [64 x 64] halves
 constexpr int kVBytes = kD * kBN * 2;        // 16 KB: Vt block [128 d x 64 tokens]
 constexpr int kPBytes = kBM * kBN * 2;       // 16 KB
-constexpr int kStages = 2;
-constexpr int kOffK = kQBytes;
-constexpr int kOffV = kOffK + kStages * kKBytes;
-constexpr int kOffP = kOffV + kStages * kVBytes;
-constexpr int kOffBar = kOffP + kPBytes;
-constexpr int kSmem = kOffBar + 16 * 8 + 64;
+// Shared-memory layout for a ring of STAGES K / Vt blocks: Q | K ring | Vt ring | P | barriers
+template <int STAGES>
+struct Lay {
+  static constexpr int kOffK = kQBytes;
+  static constexpr int kOffV = kOffK + STAGES * kKBytes;
+  static constexpr int kOffP = kOffV + STAGES * kVBytes;
+  static constexpr int kOffBar = kOffP + kPBytes;
+  static constexpr int kSmem = kOffBar + (2 * STAGES + 8) * 8 + 64;
+};
+static_assert(2 * (Lay<2>::kSmem + 1024) <= 227 * 1024, "two CTAs of the two-stage prefill kernel must fit one SM");
+static_assert(Lay<5>::kSmem + 1024 <= 227 * 1024, "the five-stage prefill kernel must fit one SM");
 constexpr int kTmemCols = 256;     // S: columns [0, 64), PV: columns [64, 192)
 constexpr uint64_t kWaitNs = 4000000000ull;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct FwdParams {
   const __nv_bfloat16* q;
@@ -109,26 +123,36 @@ __global__ void __launch_bounds__(256) attn_pack_kv_kernel(const PackParams p) {
 // ------------------------------------------------------------------------------------------------------------------
 // Main kernel
 // ------------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 1)
+template <int kStages, int kCtasPerSm>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_vt, const FwdParams p) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
+  // Two CTAs share an SM (one runs its exponentials while the other's products are on the tensor core), which leaves no
+  // room for an alignment slack: the kernel has no static shared memory, so the dynamic window starts at offset 0 of the
+  // CTA's allocation; the 1024-byte alignment the swizzled tiles need is checked, not assumed.
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (threadIdx.x == 0 && p.error_flag != nullptr) *p.error_flag = 2;
+    return;
+  }
+  using L = Lay<kStages>;
+  constexpr int kOffK = L::kOffK, kOffV = L::kOffV, kOffP = L::kOffP;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;      // [2]
-  uint64_t* kv_empty = bars + 3;     // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* s_free = bars + 6;
-  uint64_t* p_full = bars + 7;
-  uint64_t* pv_full = bars + 8;
-  uint64_t* pv_free = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* s_full = bars + 1;
+  uint64_t* s_free = bars + 2;
+  uint64_t* p_full = bars + 3;
+  uint64_t* pv_full = bars + 4;
+  uint64_t* kv_full = bars + 5;                 // [kStages]
+  uint64_t* kv_empty = kv_full + kStages;       // [kStages]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_empty + kStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int b = blockIdx.z, head = blockIdx.y;
   const int q_begin = p.cu_seqlens_q[b], q_len = p.cu_seqlens_q[b + 1] - q_begin;
-  const int row0 = blockIdx.x * kBM;
+  // causal tiles get longer towards the end of a sequence: the long ones are scheduled first (the block scheduler hands
+  // out blockIdx.x in increasing order), so the tail of the launch consists of short tiles
+  const int row0 = (p.causal ? static_cast<int>(gridDim.x - 1 - blockIdx.x) : static_cast<int>(blockIdx.x)) * kBM;
   if (row0 >= q_len) return;                      // whole CTA, before any barrier or TMEM use
   const int kv_len = p.kv_lens[b];
   const int pos0 = p.q_pos0 ? p.q_pos0[b] : (kv_len - q_len);
@@ -149,7 +173,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     mbar_init(s_free, 128);
     mbar_init(p_full, 128);
     mbar_init(pv_full, 1);
-    mbar_init(pv_free, 128);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -216,13 +239,13 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (j + 1 < nblk) ok = issue_s(j + 1);
         if (!ok) break;
         if (!mbar_wait(p_full, j & 1, abort_flag, kWaitNs)) { ok = false; break; }
-        if (j > 0 && !mbar_wait(pv_free, (j - 1) & 1, abort_flag, kWaitNs)) { ok = false; break; }
         tc_fence_after_sync();
         const int s = j % kStages;
         const uint32_t sv = smem_u32(smem + kOffV + s * kVBytes);
 #pragma unroll
         for (int k = 0; k < kBN / kUmmaK; ++k)
-          umma_f16(tmem_pv, make_smem_desc_sw128(sp) + 2 * k, make_smem_desc_sw128(sv) + 2 * k, idesc_pv, k > 0 ? 1u : 0u);
+          umma_f16(tmem_pv, make_smem_desc_sw128(sp) + 2 * k, make_smem_desc_sw128(sv) + 2 * k, idesc_pv,
+                   (j > 0 || k > 0) ? 1u : 0u);   // O accumulates over all blocks
         umma_commit(pv_full);
         umma_commit(&kv_empty[s]);      // K (read by S of this block) and Vt of this stage are free again
       }
@@ -236,10 +259,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const int pos = pos0 + row0 + row;             // absolute position of the query
     const int lim = p.causal ? min(kv_len, pos + 1) : kv_len;   // tokens [0, lim) are visible
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
-    float o[kD];
-#pragma unroll
-    for (int i = 0; i < kD; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    constexpr float kRescaleStep = 8.f;            // log2: the reference maximum follows the row maximum in steps of 2^8
+    float m = -INFINITY, l = 0.f;                  // m: reference maximum the exponentials of this row use
     uint8_t* prow = smem + kOffP + row * 128;
     const int sw = row & 7;
     bool ok = true;
@@ -253,7 +274,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       tc_fence_before_sync();
       mbar_arrive(s_free);                          // S may be overwritten by the next block's product
       const int t0 = j * kBN;
-      float mx = m;
+      float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
         float a = __uint_as_float(s0[c]) * p.scale_log2, bq = __uint_as_float(s1[c]) * p.scale_log2;
@@ -263,8 +284,36 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         s1[c] = __float_as_uint(bq);
         mx = fmaxf(mx, fmaxf(a, bq));
       }
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
+      // raise the reference only when the row maximum has outgrown it by more than the step (or there is none yet)
+      float alpha = 1.f;
+      bool raise = false;
+      if (mx > m) {
+        if (m == -INFINITY) {
+          m = mx;                                   // nothing accumulated for this row so far (its P were all zero)
+        } else if (mx - m > kRescaleStep) {
+          alpha = ex2(m - mx);
+          m = mx;
+          raise = true;
+        }
+      }
+      const float m_use = (m == -INFINITY) ? 0.f : m;
+      // the previous block's PV must have finished: it read the P buffer that is rewritten below, and it wrote the O
+      // rows a rescale touches (issued long ago: this wait is normally already satisfied)
+      if (j > 0 && !mbar_wait(pv_full, (j - 1) & 1, abort_flag, kWaitNs)) { ok = false; break; }
+      if (__any_sync(0xffffffffu, raise)) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < kD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_pv + lane_off + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x32(tmem_pv + lane_off + c * 32, r);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+      }
       float sum = 0.f;
       // P row: 64 bf16 = eight 16-byte chunks, chunk c stored at (c ^ (row & 7)) (128-byte swizzle)
 #pragma unroll
@@ -273,30 +322,34 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int c = c8 * 8 + 2 * e;
-          const float x0 = exp2f(__uint_as_float(c < 32 ? s0[c] : s1[c - 32]) - m_use);
-          const float x1 = exp2f(__uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]) - m_use);
+          const float x0 = ex2(__uint_as_float(c < 32 ? s0[c] : s1[c - 32]) - m_use);
+          const float x1 = ex2(__uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]) - m_use);
           sum += x0 + x1;
           pk[e] = pack_bf16x2(x0, x1);
         }
         *reinterpret_cast<uint4*>(prow + ((c8 ^ sw) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       l = l * alpha + sum;
-      m = mx;
       fence_proxy_async_smem();                     // P was written through the generic proxy, the MMA reads it through the async proxy
       mbar_arrive(p_full);
-      if (!mbar_wait(pv_full, j & 1, abort_flag, kWaitNs)) { ok = false; break; }
-      tc_fence_after_sync();
+    }
+    float o[kD];
 #pragma unroll
-      for (int c = 0; c < kD / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_pv + lane_off + c * 32, r);
-        tmem_ld_wait();
-        if (c == kD / 32 - 1) {
-          tc_fence_before_sync();
-          mbar_arrive(pv_free);                     // PV may be overwritten by the next block's product
+    for (int i = 0; i < kD; ++i) o[i] = 0.f;
+    if (ok && nblk > 0) {
+      if (!mbar_wait(pv_full, (nblk - 1) & 1, abort_flag, kWaitNs)) {
+        ok = false;
+      } else {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < kD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_pv + lane_off + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(r[i]);
         }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(r[i]));
+        tc_fence_before_sync();
       }
     }
     if (!ok) *abort_flag = 1;
@@ -373,15 +426,28 @@ cudaError_t launch_flash_fwd_sm100(const FlashFwdSm100Args& a, cudaStream_t stre
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.total_q = a.total_q;
   p.error_flag = a.error_flag;
-  static SmemOptIn opt;
-  e = opt.ensure(flash_fwd_sm100_kernel, kSmem + 1024);
-  if (e != cudaSuccess) return e;
   dim3 grid((a.max_q_len + kBM - 1) / kBM, a.num_q_heads, a.batch);
   CUtensorMap mq, mk, mv;
   memcpy(&mq, tq.bytes, sizeof(mq));
   memcpy(&mk, tk.bytes, sizeof(mk));
   memcpy(&mv, tv.bytes, sizeof(mv));
-  flash_fwd_sm100_kernel<<<grid, kThreads, kSmem + 1024, stream>>>(mq, mk, mv, p);
+  // Two forms: two CTAs per SM with a two-stage KV ring (one CTA's exponentials overlap the other's products), or one
+  // CTA per SM with a five-stage ring (deeper TMA prefetch).  TDB200_ATTN_FORM selects; default = the faster measured.
+  static const int form = [] {
+    const char* e = std::getenv("TDB200_ATTN_FORM");
+    return e != nullptr ? std::atoi(e) : 2;
+  }();
+  if (form == 1) {
+    static SmemOptIn opt1;
+    e = opt1.ensure(flash_fwd_sm100_kernel<5, 1>, Lay<5>::kSmem);
+    if (e != cudaSuccess) return e;
+    flash_fwd_sm100_kernel<5, 1><<<grid, kThreads, Lay<5>::kSmem, stream>>>(mq, mk, mv, p);
+  } else {
+    static SmemOptIn opt2;
+    e = opt2.ensure(flash_fwd_sm100_kernel<2, 2>, Lay<2>::kSmem);
+    if (e != cudaSuccess) return e;
+    flash_fwd_sm100_kernel<2, 2><<<grid, kThreads, Lay<2>::kSmem, stream>>>(mq, mk, mv, p);
+  }
   return cudaGetLastError();
 }
 

@@ -75,7 +75,10 @@ _PENDING_ERRORS = []            # error flags of tcgen05 prefill launches that h
 def check_attention_errors() -> None:
     """Raise if a bounded wait inside a tcgen05 prefill kernel gave up since the last check (synchronises)."""
     flags, _PENDING_ERRORS[:] = list(_PENDING_ERRORS), []
-    if any(int(f.item()) != 0 for f in flags):
+    codes = [int(f.item()) for f in flags]
+    if any(c == 2 for c in codes):
+        raise RuntimeError("flash_fwd_sm100: the dynamic shared-memory window was not 1024-byte aligned")
+    if any(c != 0 for c in codes):
         raise RuntimeError("flash_fwd_sm100: a wait inside the kernel timed out")
 
 

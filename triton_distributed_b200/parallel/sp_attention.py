@@ -143,7 +143,7 @@ def fused_sp_ag_attn_intra_node(ctx: SPAllGatherAttentionContextIntraNode, q_sha
     table = bt[table_rows].contiguous().to(dev)
     out = ops.flash_attn_varlen(q_shard.contiguous(), k_pages.contiguous() if not k_pages.is_contiguous() else k_pages,
                                 v_pages.contiguous() if not v_pages.is_contiguous() else v_pages, table, cu, kv_lens, max_q,
-                                q_pos0=q_pos0, causal=is_causal)
+                                q_pos0=q_pos0, causal=is_causal, max_kv_len=max(kv_len))
     if output is not None:
         output.copy_(out)
         return output
