@@ -111,6 +111,7 @@ struct KParams {
   CtxDev* ctx;
   SymmInfo symm;
   uint64_t mbar_timeout_ns;     // limit of every shared-memory barrier wait
+  uint32_t epi_sleep_ns;        // pair kernel: sleep between polls of an epilogue warp waiting for its accumulator
   int split_tail;               // pair kernel: tiles of an incomplete last wave are computed as two 128-column halves
   unsigned long long* stats;    // optional [grid][kStatSlots] stall counters (cycles), null = off
 };
@@ -1087,7 +1088,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         ++local;
         {
           StallTimer st(p);
-          const bool got = mbar_wait(&tmem_full[b], aph, abort_flag, p.mbar_timeout_ns);
+          const bool got = mbar_wait_sleepy(&tmem_full[b], aph, abort_flag, p.mbar_timeout_ns, p.epi_sleep_ns);
           if (leader) st.stop(w_tmem);
           if (!got) {
             ok = false;
@@ -1294,6 +1295,11 @@ cudaError_t fill_params(const GemmArgs& a, int BN, KParams& p) {
   // shared-memory barriers complete within microseconds when everything works; their limit follows the configured
   // wait limit (a flag wait of a producer can legitimately hold a consumer's barrier for that long)
   p.mbar_timeout_ns = a.symm.timeout_ns > 0 ? a.symm.timeout_ns : 4000000000ull;
+  static const uint32_t epi_sleep = [] {
+    const char* e = std::getenv("TDB200_EPI_SLEEP_NS");
+    return e != nullptr ? static_cast<uint32_t>(std::atoi(e)) : 0u;
+  }();
+  p.epi_sleep_ns = epi_sleep;
   p.split_tail = a.split_tail;
   p.stats = reinterpret_cast<unsigned long long*>(a.stats);
   if (a.mode == kGemmAllGather && p.tiles_m_seg > a.max_chunks) return cudaErrorInvalidValue;

@@ -93,6 +93,24 @@ TDB_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* ab
   return true;
 }
 
+// The same, for waits that are expected to be long (an epilogue warp waiting for the next accumulator): the thread
+// sleeps `sleep_ns` between polls, so that a hundred-odd waiting threads do not spend issue slots and power on polling
+// while the tensor core works.  sleep_ns == 0 behaves like mbar_wait.
+TDB_DEVICE bool mbar_wait_sleepy(uint64_t* bar, uint32_t parity, const volatile int* abort_flag, uint64_t timeout_ns,
+                                 uint32_t sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if (sleep_ns != 0u) __nanosleep(sleep_ns);
+    if ((++it & 31u) == 0u) {
+      if (abort_flag != nullptr && *abort_flag != 0) return false;
+      if (globaltimer_ns() - t0 > timeout_ns) return false;
+    }
+  }
+  return true;
+}
+
 // ----------------------------------------------------------------------------
 // Proxy fences
 // ----------------------------------------------------------------------------
