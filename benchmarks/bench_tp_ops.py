@@ -82,7 +82,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--n-comm", default="0", help="comma list of comm-CTA counts for the AG-GEMM (0 = automatic)")
     ap.add_argument("--stats", type=int, default=1, help="also report the kernel's stall counters")
-    ap.add_argument("--multimem", type=int, default=0)
+    ap.add_argument("--multimem", type=int, default=-1, help="AG push: 1 NVLS ring, 0 unicast, -1 the library's default")
     ap.add_argument("--only", default="", help="comma list of op names to run (default: all)")
     args = ap.parse_args()
     tdb.initialize_distributed(seed=0)
@@ -146,9 +146,9 @@ def main():
         emit("torch_gemm_only_rs_shape", timed(lambda: torch.matmul(h, w2t, out=part), args.iters, args.warmup, fl, rt))
     for nc in ([int(v) for v in args.n_comm.split(",")] if want("own_ag_gemm") else []):
         ag_ctx = ops.create_ag_gemm_context(max_M=M, K=K, dtype=torch.bfloat16, n_comm_ctas=nc,
-                                            use_multimem=bool(args.multimem))
+                                            use_multimem=None if args.multimem < 0 else bool(args.multimem))
         f_ag = lambda: ops.ag_gemm(a, w1, ag_ctx, out=h)   # noqa: E731
-        extra = {"n_comm": nc, "multimem": args.multimem}
+        extra = {"n_comm": nc, "multimem": int(bool(ag_ctx.use_multimem))}
         ms = timed(f_ag, args.iters, args.warmup, fl, rt)
         extra["loop_ms"] = loop_ms(f_ag, args.iters, rt)
         if args.stats and W > 1:

@@ -34,7 +34,9 @@ constexpr int kTN = 128;    // output columns per tile (MMA M)
 constexpr int kBK = 64;
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
-constexpr uint64_t kMbarTimeoutNs = 4000000000ull;
+// shared-memory barrier waits follow the configured wait limit of the launch (symm.timeout_ns, TDB200_WAIT_TIMEOUT_S;
+// four seconds when the caller passes none)
+#define kMbarTimeoutNs (p.symm.timeout_ns != 0 ? p.symm.timeout_ns : 4000000000ull)
 
 template <int MPAD>
 struct Layout {

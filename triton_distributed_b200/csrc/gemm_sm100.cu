@@ -112,6 +112,7 @@ struct KParams {
   SymmInfo symm;
   uint64_t mbar_timeout_ns;     // limit of every shared-memory barrier wait
   uint32_t epi_sleep_ns;        // pair kernel: sleep between polls of an epilogue warp waiting for its accumulator
+  int pair_group_m;             // pair kernel: M tiles (of 256 rows) swept together over all columns
   int split_tail;               // pair kernel: tiles of an incomplete last wave are computed as two 128-column halves
   unsigned long long* stats;    // optional [grid][kStatSlots] stall counters (cycles), null = off
 };
@@ -848,14 +849,14 @@ __device__ __forceinline__ PairTile decode_pair_item(const KParams& p, const Pai
   const int per_seg = sc.tiles_m_pair * p.tiles_n;
   if (p.mode == kGemmAllGather && p.use_mc && t >= per_seg) {
     // NVLS all-gather: every shard arrives chunk by chunk at the same pace, so the remote part is visited chunk-major:
-    // the M tiles are ordered (pair chunk, ring distance) and swept in groups of kGroupM over all columns
+    // the M tiles are ordered (pair chunk, ring distance) and swept in groups of p.pair_group_m over all columns
     const int rem = t - per_seg;
     const int nrem = p.num_seg - 1;
     const int total_m = sc.tiles_m_pair * nrem;
-    const int group_sz = kGroupM * p.tiles_n;
+    const int group_sz = p.pair_group_m * p.tiles_n;
     const int g = rem / group_sz;
-    const int first_m = g * kGroupM;
-    const int gm = min(total_m - first_m, kGroupM);
+    const int first_m = g * p.pair_group_m;
+    const int gm = min(total_m - first_m, p.pair_group_m);
     const int in_g = rem - g * group_sz;
     const int m_lin = first_m + in_g % gm;
     r.nt = in_g / gm;
@@ -865,10 +866,10 @@ __device__ __forceinline__ PairTile decode_pair_item(const KParams& p, const Pai
     const int si = t / per_seg;
     const int rem = t - si * per_seg;
     r.seg = (p.seg_first + si) % p.num_seg;
-    const int group_sz = kGroupM * p.tiles_n;
+    const int group_sz = p.pair_group_m * p.tiles_n;
     const int g = rem / group_sz;
-    const int first_m = g * kGroupM;
-    const int gm = min(sc.tiles_m_pair - first_m, kGroupM);
+    const int first_m = g * p.pair_group_m;
+    const int gm = min(sc.tiles_m_pair - first_m, p.pair_group_m);
     const int in_g = rem - g * group_sz;
     r.mt = first_m + in_g % gm;
     r.nt = in_g / gm;
@@ -1300,6 +1301,18 @@ cudaError_t fill_params(const GemmArgs& a, int BN, KParams& p) {
     return e != nullptr ? static_cast<uint32_t>(std::atoi(e)) : 0u;
   }();
   p.epi_sleep_ns = epi_sleep;
+  // Rasterisation of the pair kernel: a group of M tiles is swept over all columns, so its A rows (group x 256 x K
+  // elements) stay in L2 while B streams through once per group.  A larger group halves the number of passes over B;
+  // it is taken while the group's A rows fit comfortably in L2 (67 MB at K = 8192).
+  {
+    static const int forced = [] {
+      const char* e = std::getenv("TDB200_PAIR_GROUP_M");
+      return e != nullptr ? std::atoi(e) : 0;
+    }();
+    const uint64_t a_bytes_16 = 16ull * 256ull * static_cast<uint64_t>(a.K) * 2ull;
+    // (plain mode only: in the fused modes the order also decides which chunk flags a wave waits for)
+    p.pair_group_m = forced > 0 ? forced : ((a.mode == kGemmPlain && a_bytes_16 <= (80ull << 20)) ? 16 : kGroupM);
+  }
   p.split_tail = a.split_tail;
   p.stats = reinterpret_cast<unsigned long long*>(a.stats);
   if (a.mode == kGemmAllGather && p.tiles_m_seg > a.max_chunks) return cudaErrorInvalidValue;

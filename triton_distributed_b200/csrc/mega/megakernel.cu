@@ -26,7 +26,8 @@ constexpr int kTN = 128;
 constexpr int kBK = 64;
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
-constexpr uint64_t kMbarTimeoutNs = 4000000000ull;
+// shared-memory barrier waits follow the configured wait limit of the launch (symm.timeout_ns, TDB200_WAIT_TIMEOUT_S)
+#define kMbarTimeoutNs (p.symm.timeout_ns)
 
 template <int MPAD>
 struct Layout {
