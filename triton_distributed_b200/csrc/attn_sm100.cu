@@ -274,16 +274,21 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       tc_fence_before_sync();
       mbar_arrive(s_free);                          // S may be overwritten by the next block's product
       const int t0 = j * kBN;
+      // Blocks that every row of the warp sees completely (all but the ones on the causal diagonal and the last one of
+      // a sequence) skip the masking; the scale is folded into the exponent (one FMA per element), so an element
+      // costs a max, an FMA, an ex2, an add and half a pack.
+      const bool full = __all_sync(0xffffffffu, t0 + kBN <= lim);
+      if (!full) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if (t0 + c >= lim) s0[c] = 0xff800000u;          // -inf
+          if (t0 + 32 + c >= lim) s1[c] = 0xff800000u;
+        }
+      }
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float a = __uint_as_float(s0[c]) * p.scale_log2, bq = __uint_as_float(s1[c]) * p.scale_log2;
-        a = (t0 + c < lim) ? a : -INFINITY;
-        bq = (t0 + 32 + c < lim) ? bq : -INFINITY;
-        s0[c] = __float_as_uint(a);
-        s1[c] = __float_as_uint(bq);
-        mx = fmaxf(mx, fmaxf(a, bq));
-      }
+      for (int c = 0; c < 32; ++c) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])));
+      mx *= p.scale_log2;                                   // scale > 0: the maximum commutes with it
       // raise the reference only when the row maximum has outgrown it by more than the step (or there is none yet)
       float alpha = 1.f;
       bool raise = false;
@@ -322,8 +327,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int c = c8 * 8 + 2 * e;
-          const float x0 = ex2(__uint_as_float(c < 32 ? s0[c] : s1[c - 32]) - m_use);
-          const float x1 = ex2(__uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]) - m_use);
+          const float x0 = ex2(fmaf(__uint_as_float(c < 32 ? s0[c] : s1[c - 32]), p.scale_log2, -m_use));
+          const float x1 = ex2(fmaf(__uint_as_float(c + 1 < 32 ? s0[c + 1] : s1[c + 1 - 32]), p.scale_log2, -m_use));
           sum += x0 + x1;
           pk[e] = pack_bf16x2(x0, x1);
         }
@@ -385,6 +390,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
 cudaError_t launch_flash_fwd_sm100(const FlashFwdSm100Args& a, cudaStream_t stream) {
   if (a.head_dim != kD || a.num_q_heads % a.num_kv_heads != 0 || a.Lp % kBN != 0 || a.Lp <= 0) return cudaErrorInvalidValue;
+  if (!(a.scale > 0.f)) return cudaErrorInvalidValue;   // the row maximum is taken before scaling
   if (a.batch == 0 || a.max_q_len == 0) return cudaSuccess;
   PackParams pk;
   pk.k_cache = reinterpret_cast<const __nv_bfloat16*>(a.kv.k_cache);
