@@ -14,6 +14,7 @@
 #include <cuda_fp8.h>
 
 #include "tdb/ep.h"
+#include "tdb/launch.cuh"
 #include "tdb/symm_device.cuh"
 
 namespace tdb {
@@ -920,8 +921,8 @@ cudaError_t launch_ep_combine(const EpCombineArgs& a, cudaStream_t s) {
     resident = sms * per_sm;
   }
   if (ctas > resident) ctas = resident;
-  ep_combine_kernel<<<ctas, kEpThreads, 0, s>>>(p);
-  return cudaGetLastError();
+  // cooperative: every CTA waits for flags that only the LAST CTA of each rank raises, so all CTAs of a rank must run
+  return launch_coop(ep_combine_kernel, dim3(ctas), dim3(kEpThreads), static_cast<size_t>(0), s, p);
 }
 
 cudaError_t launch_a2a_single(const void* in, void* out, const int32_t* splits_all, int64_t row_bytes, uint32_t* flags,

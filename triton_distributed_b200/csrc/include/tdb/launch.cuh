@@ -46,4 +46,26 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Cooperative launch: the kernel starts only when ALL of its CTAs can be resident at once, and the launch fails (instead
+// of deadlocking later) when the grid exceeds what the device can hold.  For kernels whose CTAs wait for one another
+// inside a rank (scoreboards, grid-wide counters).  TDB200_COOP=0 falls back to a plain launch.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_coop(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  static const bool coop = [] {
+    const char* e = std::getenv("TDB200_COOP");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = coop ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace tdb

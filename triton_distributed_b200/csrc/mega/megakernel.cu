@@ -14,6 +14,7 @@
 #include <cuda.h>
 
 #include "tdb/attn_device.cuh"
+#include "tdb/launch.cuh"
 #include "tdb/mega.h"
 #include "tdb/profiler.cuh"
 #include "tdb/symm_device.cuh"
@@ -682,8 +683,8 @@ cudaError_t launch_t(const KP& p, int grid, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     set = true;
   }
-  mega_kernel<MPAD><<<grid, kThreads, smem, stream>>>(p);
-  return cudaGetLastError();
+  // every CTA waits on scoreboard counters that other CTAs of the launch bump: all of them must be resident
+  return launch_coop(mega_kernel<MPAD>, dim3(grid), dim3(kThreads), static_cast<size_t>(smem), stream, p);
 }
 
 }  // namespace

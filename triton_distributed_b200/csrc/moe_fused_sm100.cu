@@ -733,6 +733,10 @@ cudaError_t launch_moe_fused(const MoeFusedArgs& a, cudaStream_t stream) {
   if (a.num_ctas - n_aux < 1) return cudaErrorInvalidValue;
   CUtensorMap tb;
   memcpy(&tb, a.tmap_b.bytes, sizeof(CUtensorMap));
+  if (a.mode == kMoeReduceRS || a.mode == kMoeReduceAR) {
+    // the reducer CTAs wait for chunk counters that the GEMM CTAs of the same launch bump: all CTAs must be resident
+    return launch_coop(moe_fused_kernel, dim3(a.num_ctas), dim3(kThreads), static_cast<size_t>(smem), stream, tb, p);
+  }
   moe_fused_kernel<<<a.num_ctas, kThreads, smem, stream>>>(tb, p);
   return cudaGetLastError();
 }
