@@ -110,26 +110,6 @@ def main():
         g = graphed("triton_dist_gemm_ar")
         emit("fused_gemm_ar_cuda_graph", timed(g.replay, reset))
         del g
-    if "prefill" in arms:
-        # one prompt of --prefill tokens through the whole model: NCCL + cuBLAS layers against the overlapped layers
-        P = args.prefill
-        pcache = KV_Cache(a.num_hidden_layers, 1, P + 8, max(1, a.num_key_value_heads // W), a.head_dim, device=dev)
-        pids = torch.randint(0, a.vocab_size, (1, P), device=dev)
-        ppos = torch.arange(P, device=dev).unsqueeze(0)
-
-        def prefill_step():
-            pcache.kv_offset.zero_()
-            model.inference(pids, ppos, pcache)
-
-        for mode in ("torch", "triton_dist"):
-            if mode != "torch":
-                model.init_ctx_for(mode, P)
-            model.set_fwd(mode)
-            ms = timed(prefill_step, lambda: None)
-            if rt.rank == 0:
-                print(json.dumps({"arm": f"prefill_{mode}", "model": args.model, "layers": a.num_hidden_layers, "tp": W,
-                                  "tokens": P, "ms": ms}), flush=True)
-        del pcache
     for arm_name, pre in (("mega", False), ("mega_prefetch", True)):
         if arm_name not in arms:
             continue
@@ -153,6 +133,27 @@ def main():
         rt.host_barrier()
         emit("megakernel" + ("_prefetch" if pre else "") + "_cuda_graph", timed(g.replay, reset))
         del mega, g
+    if "prefill" in arms:
+        # one prompt of --prefill tokens through the whole model: NCCL + cuBLAS layers against the overlapped layers
+        P = args.prefill
+        pcache = KV_Cache(a.num_hidden_layers, 1, P + 8, max(1, a.num_key_value_heads // W), a.head_dim, device=dev)
+        pids = torch.randint(0, a.vocab_size, (1, P), device=dev)
+        ppos = torch.arange(P, device=dev).unsqueeze(0)
+
+        def prefill_step():
+            pcache.kv_offset.zero_()
+            model.inference(pids, ppos, pcache)
+
+        # (the AG -> GEMM / GEMM -> RS backend shards the BATCH over the ranks, so a single prompt runs on the all-reduce one)
+        for mode in ("torch", "triton_dist_AR"):
+            if mode != "torch":
+                model.init_ctx_for(mode, P)
+            model.set_fwd(mode)
+            ms = timed(prefill_step, lambda: None)
+            if rt.rank == 0:
+                print(json.dumps({"arm": f"prefill_{mode}", "model": args.model, "layers": a.num_hidden_layers, "tp": W,
+                                  "tokens": P, "ms": ms}), flush=True)
+        del pcache
     torch.cuda.synchronize()
     rt.host_barrier()
     sys.stdout.flush()
