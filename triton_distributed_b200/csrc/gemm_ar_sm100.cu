@@ -8,7 +8,7 @@
 // units; every CTA takes one contiguous, equally long range of it ("stream-K"), so all SMs stream the same number of
 // weight bytes whatever the tile count is, and the weights are read exactly once through a deep TMA ring, which is
 // what bounds decode GEMMs.  A range covers pieces of one to three tiles.  A piece that spans a tile's whole K is
-// stored directly; other pieces are added with red.global.add.f32 into an accumulation buffer, and the CTA that
+// stored directly; other pieces are added with red.global.add.v4.f32 into a column-major accumulation buffer, and the CTA that
 // arrives last on a column tile converts it, clears the buffer again (self-cleaning, CUDA-graph safe) and, in
 // all-reduce mode, runs the cross-rank sum for that tile right away:
 //     NVLS:  store the bf16 partial tile to the heap, flag all ranks, wait for all ranks' flags of this tile,
@@ -53,10 +53,11 @@ struct Layout {
 struct KP {
   int M, N, K;
   int tiles_n, kb_total;
-  int per_cta;               // (tile, k-block) units per CTA
+  int per_cta;               // (tile, k-block) units per CTA (stream-K form)
+  int cluster_s;             // CTAs per column tile (cluster form)
   __nv_bfloat16* out;        // [M, N]
   int64_t ld_out;
-  float* acc;                // [M_cap, N] fp32 split-K accumulation (all zero between calls)
+  float* acc;                // [tiles_n * 128, M_pad] fp32 split-K accumulation (all zero between calls)
   uint32_t* counters;        // [tiles_n] arrivals per tile (zero between calls)
   int mode;                  // 0 plain, 1 all-reduce
   int use_mc;
@@ -70,6 +71,9 @@ struct KP {
 };
 
 TDB_DEVICE void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+TDB_DEVICE void red_add_v4_f32(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 
 // The pieces of this CTA's unit range, in order: (column tile, [kb0, kb1)).
 struct PieceIter {
@@ -92,6 +96,95 @@ struct PieceIter {
 // number of CTAs whose ranges touch tile nt
 TDB_DEVICE int pieces_of_tile(const KP& p, int nt) {
   return ((nt + 1) * p.kb_total - 1) / p.per_cta - (nt * p.kb_total) / p.per_cta + 1;
+}
+
+// Cross-rank sum of column tile nt, run by the 128 epilogue threads of one CTA after the rank's bf16 partial of the tile
+// is complete in `dst` (the heap partial of this parity): push or NVLS form.  False when a peer's flag did not arrive
+// within the wait limit.
+TDB_DEVICE bool tile_exchange(const KP& p, int nt, __nv_bfloat16* dst, int par, uint32_t epoch) {
+  const int W = p.symm.world, rank = p.symm.rank;
+  // ---- cross-rank sum of this tile
+  const int tn = min(kTN, p.N - nt * kTN);   // valid columns of the tile (multiple of 8)
+  if (!p.use_mc) {
+    // push the tile into slot [rank] of every peer
+    epi_bar();
+    const int vec_per_row = tn / 8;
+    const int et = threadIdx.x - 64;
+    for (int v = et; v < p.M * vec_per_row; v += 128) {
+      const int m = v / vec_per_row, cv = v - m * vec_per_row;
+      __nv_bfloat16* src = dst + static_cast<int64_t>(m) * p.N + nt * kTN + cv * 8;
+      const uint4 u = ld_v4(src);
+      for (int j = 1; j < W; ++j) st_v4(symm_at(p.symm, src, (rank + j) % W), u);
+    }
+  }
+  epi_bar();
+  const int et = threadIdx.x - 64;   // 0..127 within the epilogue warps
+  bool wok = true;
+  if (et < W) {
+    fence_acq_rel_sys();
+    st_release_sys(symm_at(p.symm, p.flags + static_cast<int64_t>(rank) * p.max_tiles + nt, (rank + et) % W), epoch);
+    wok = wait_until(p.symm, p.flags + static_cast<int64_t>(et) * p.max_tiles + nt, epoch, kCmpGe, kKernelGemmAr, 40,
+                     et, nt);
+  }
+  // combine the per-thread results without leaving the named barrier unbalanced
+  __shared__ int s_wok;
+  if (et == 0) s_wok = 1;
+  epi_bar();
+  if (!wok) s_wok = 0;
+  epi_bar();
+  if (s_wok == 0) return false;
+  const int vec_per_row = tn / 8;
+  const int total_vec = p.M * vec_per_row;
+  if (p.use_mc) {
+    // the switch returns the sum over all ranks; eight requests per thread are in flight at a time (one NVLS
+    // round trip costs microseconds, and a tile of 128 tokens has sixteen 16-byte vectors per thread)
+    constexpr int kInFlight = 8;
+    for (int v0 = et; v0 < total_vec; v0 += 128 * kInFlight) {
+      uint4 o[kInFlight];
+#pragma unroll
+      for (int i = 0; i < kInFlight; ++i) {
+        const int v = v0 + i * 128;
+        if (v < total_vec) {
+          const int m = v / vec_per_row, cv = v - m * vec_per_row;
+          const __nv_bfloat16* src = p.partial + par * p.partial_half + static_cast<int64_t>(m) * p.N + nt * kTN + cv * 8;
+          o[i] = multimem_ld_reduce_bf16x8(mc_ptr(p.symm, src));
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kInFlight; ++i) {
+        const int v = v0 + i * 128;
+        if (v < total_vec) {
+          const int m = v / vec_per_row, cv = v - m * vec_per_row;
+          st_v4(p.out + static_cast<int64_t>(m) * p.ld_out + nt * kTN + cv * 8, o[i]);
+        }
+      }
+    }
+  } else {
+    for (int v = et; v < total_vec; v += 128) {
+      const int m = v / vec_per_row, cv = v - m * vec_per_row;
+      const int col = nt * kTN + cv * 8;
+      uint4 u[kMaxRanks];
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s)
+        if (s < W)
+          u[s] = ld_relaxed_sys_v4(p.partial + par * p.partial_half + (static_cast<uint64_t>(s) * p.m_cap + m) * p.N + col);
+      float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s) {
+        if (s < W) {
+          const float2 f0 = unpack_bf16x2(u[s].x), f1 = unpack_bf16x2(u[s].y), f2 = unpack_bf16x2(u[s].z),
+                       f3 = unpack_bf16x2(u[s].w);
+          accv[0] += f0.x; accv[1] += f0.y; accv[2] += f1.x; accv[3] += f1.y;
+          accv[4] += f2.x; accv[5] += f2.y; accv[6] += f3.x; accv[7] += f3.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(accv[0], accv[1]); o.y = pack_bf16x2(accv[2], accv[3]);
+      o.z = pack_bf16x2(accv[4], accv[5]); o.w = pack_bf16x2(accv[6], accv[7]);
+      st_v4(p.out + static_cast<int64_t>(m) * p.ld_out + col, o);
+    }
+  }
+  return true;
 }
 
 template <int MPAD>
@@ -204,7 +297,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   } else {
     const int q = warp & 3;
     const bool leader = (warp == 2 && lane == 0);
-    const int W = p.symm.world, rank = p.symm.rank;
+    const int rank = p.symm.rank;
     int local = 0;
     bool ok = true;
     for (PieceIter pc(p); ok && pc.next(); ++local) {
@@ -236,22 +329,28 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         dst = p.partial + par * p.partial_half + static_cast<uint64_t>(rank) * p.m_cap * p.N;
         ld_dst = p.N;
       }
+      // split accumulation buffer: [column][M_pad] fp32, so that a thread's sixteen consecutive tokens of its column
+      // are contiguous and go out as four 16-byte vector reductions
+      float* acc_col = p.acc + static_cast<int64_t>(nt * kTN + q * 32 + lane) * MPAD;
 #pragma unroll 1
       for (int c = 0; c < MPAD / 16; ++c) {
         uint32_t r[16];
         tmem_ld_32x16(tmem_base + b * MPAD + c * 16 + (static_cast<uint32_t>(q * 32) << 16), r);
         tmem_ld_wait();
         if (!n_ok) continue;
+        if (single) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = c * 16 + j;
-          if (m < p.M) {
-            if (single) {
-              dst[static_cast<int64_t>(m) * ld_dst + n] = __float2bfloat16(__uint_as_float(r[j]));
-            } else {
-              atomicAdd(p.acc + static_cast<int64_t>(m) * p.N + n, __uint_as_float(r[j]));
-            }
+          for (int j = 0; j < 16; ++j) {
+            const int m = c * 16 + j;
+            if (m < p.M) dst[static_cast<int64_t>(m) * ld_dst + n] = __float2bfloat16(__uint_as_float(r[j]));
           }
+        } else {
+          // rows at or beyond M are zero (the activation tile is zero-filled there), so whole quads are added
+#pragma unroll
+          for (int j = 0; j < 16; j += 4)
+            if (c * 16 + j < p.M)
+              red_add_v4_f32(acc_col + c * 16 + j, __uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                             __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
         }
       }
       tc_fence_before_sync();
@@ -271,107 +370,32 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         __threadfence();
         // finalise: fp32 accumulation -> bf16 (out, or the heap partial for the all-reduce); clear the accumulator
         if (n_ok) {
-          // batches of independent loads: one L2 round trip per batch instead of one per row
+          // batches of independent 16-byte loads: one L2 round trip per batch
           constexpr int kBatch = MPAD < 32 ? MPAD : 32;
           for (int m0 = 0; m0 < p.M; m0 += kBatch) {
-            float v[kBatch];
+            float4 v[kBatch / 4];
 #pragma unroll
-            for (int j = 0; j < kBatch; ++j)
-              v[j] = (m0 + j < p.M) ? __ldcg(p.acc + static_cast<int64_t>(m0 + j) * p.N + n) : 0.f;
+            for (int j = 0; j < kBatch / 4; ++j)
+              v[j] = (m0 + 4 * j < p.M) ? __ldcg(reinterpret_cast<const float4*>(acc_col + m0 + 4 * j))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int j = 0; j < kBatch; ++j) {
-              if (m0 + j < p.M) {
-                p.acc[static_cast<int64_t>(m0 + j) * p.N + n] = 0.f;
-                dst[static_cast<int64_t>(m0 + j) * ld_dst + n] = __float2bfloat16(v[j]);
+            for (int j = 0; j < kBatch / 4; ++j) {
+              if (m0 + 4 * j < p.M) {
+                *reinterpret_cast<float4*>(acc_col + m0 + 4 * j) = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float f[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (m0 + 4 * j + e < p.M)
+                    dst[static_cast<int64_t>(m0 + 4 * j + e) * ld_dst + n] = __float2bfloat16(f[e]);
               }
             }
           }
         }
       }
       if (p.mode == 0) continue;
-      // ---- cross-rank sum of this tile
-      const int tn = min(kTN, p.N - nt * kTN);   // valid columns of the tile (multiple of 8)
-      if (!p.use_mc) {
-        // push the tile into slot [rank] of every peer
-        epi_bar();
-        const int vec_per_row = tn / 8;
-        const int et = threadIdx.x - 64;
-        for (int v = et; v < p.M * vec_per_row; v += 128) {
-          const int m = v / vec_per_row, cv = v - m * vec_per_row;
-          __nv_bfloat16* src = dst + static_cast<int64_t>(m) * p.N + nt * kTN + cv * 8;
-          const uint4 u = ld_v4(src);
-          for (int j = 1; j < W; ++j) st_v4(symm_at(p.symm, src, (rank + j) % W), u);
-        }
-      }
-      epi_bar();
-      const int et = threadIdx.x - 64;   // 0..127 within the epilogue warps
-      bool wok = true;
-      if (et < W) {
-        fence_acq_rel_sys();
-        st_release_sys(symm_at(p.symm, p.flags + static_cast<int64_t>(rank) * p.max_tiles + nt, (rank + et) % W), epoch);
-        wok = wait_until(p.symm, p.flags + static_cast<int64_t>(et) * p.max_tiles + nt, epoch, kCmpGe, kKernelGemmAr, 40,
-                         et, nt);
-      }
-      // combine the per-thread results without leaving the named barrier unbalanced
-      __shared__ int s_wok;
-      if (et == 0) s_wok = 1;
-      epi_bar();
-      if (!wok) s_wok = 0;
-      epi_bar();
-      if (s_wok == 0) {
+      if (!tile_exchange(p, nt, dst, par, epoch)) {
         ok = false;
         break;
-      }
-      const int vec_per_row = tn / 8;
-      const int total_vec = p.M * vec_per_row;
-      if (p.use_mc) {
-        // the switch returns the sum over all ranks; eight requests per thread are in flight at a time (one NVLS
-        // round trip costs microseconds, and a tile of 128 tokens has sixteen 16-byte vectors per thread)
-        constexpr int kInFlight = 8;
-        for (int v0 = et; v0 < total_vec; v0 += 128 * kInFlight) {
-          uint4 o[kInFlight];
-#pragma unroll
-          for (int i = 0; i < kInFlight; ++i) {
-            const int v = v0 + i * 128;
-            if (v < total_vec) {
-              const int m = v / vec_per_row, cv = v - m * vec_per_row;
-              const __nv_bfloat16* src = p.partial + par * p.partial_half + static_cast<int64_t>(m) * p.N + nt * kTN + cv * 8;
-              o[i] = multimem_ld_reduce_bf16x8(mc_ptr(p.symm, src));
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < kInFlight; ++i) {
-            const int v = v0 + i * 128;
-            if (v < total_vec) {
-              const int m = v / vec_per_row, cv = v - m * vec_per_row;
-              st_v4(p.out + static_cast<int64_t>(m) * p.ld_out + nt * kTN + cv * 8, o[i]);
-            }
-          }
-        }
-      } else {
-        for (int v = et; v < total_vec; v += 128) {
-          const int m = v / vec_per_row, cv = v - m * vec_per_row;
-          const int col = nt * kTN + cv * 8;
-          uint4 u[kMaxRanks];
-#pragma unroll
-          for (int s = 0; s < kMaxRanks; ++s)
-            if (s < W)
-              u[s] = ld_relaxed_sys_v4(p.partial + par * p.partial_half + (static_cast<uint64_t>(s) * p.m_cap + m) * p.N + col);
-          float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int s = 0; s < kMaxRanks; ++s) {
-            if (s < W) {
-              const float2 f0 = unpack_bf16x2(u[s].x), f1 = unpack_bf16x2(u[s].y), f2 = unpack_bf16x2(u[s].z),
-                           f3 = unpack_bf16x2(u[s].w);
-              accv[0] += f0.x; accv[1] += f0.y; accv[2] += f1.x; accv[3] += f1.y;
-              accv[4] += f2.x; accv[5] += f2.y; accv[6] += f3.x; accv[7] += f3.y;
-            }
-          }
-          uint4 o;
-          o.x = pack_bf16x2(accv[0], accv[1]); o.y = pack_bf16x2(accv[2], accv[3]);
-          o.z = pack_bf16x2(accv[4], accv[5]); o.w = pack_bf16x2(accv[6], accv[7]);
-          st_v4(p.out + static_cast<int64_t>(m) * p.ld_out + col, o);
-        }
       }
     }
     if (!ok) *abort_flag = 1;
@@ -395,6 +419,280 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       }
     }
   }
+}
+
+TDB_DEVICE float4 ld_dsmem_v4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
+TDB_DEVICE void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+TDB_DEVICE void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+
+// Cluster form of the same GEMM: the S CTAs of a thread-block cluster share ONE column tile and split its K range
+// evenly.  Every CTA accumulates its part in TMEM, parks it as fp32 in its own shared memory (the drained TMA ring),
+// and after a cluster barrier CTA r sums rows [r * M / S, (r + 1) * M / S) over all S parts through distributed shared
+// memory and stores them as bf16 rows of 256 bytes.  No global accumulation buffer, no atomics, no arrival counters; the
+// result does not depend on arrival order.  In all-reduce mode CTA 0 of the cluster then runs the cross-rank sum of
+// the tile.
+template <int MPAD>
+__global__ void __launch_bounds__(kThreads, 1)
+skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const KP p) {
+  using L = Layout<MPAD>;
+  constexpr int kStages = L::kStages;
+  static_assert(MPAD * kTN * 4 <= L::kBarOffset, "the fp32 part must fit into the drained ring");
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(tmem_full + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_smem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.cluster_s;
+  const int r = static_cast<int>(cluster_ctarank());
+  const int nt = static_cast<int>(blockIdx.x) / S;
+  const int kb0 = static_cast<int>(static_cast<int64_t>(p.kb_total) * r / S);
+  const int kb1 = static_cast<int>(static_cast<int64_t>(p.kb_total) * (r + 1) / S);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    mbar_init(&tmem_full[0], 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_smem, L::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_smem;
+  float* part = reinterpret_cast<float*>(smem);   // [M][128] fp32, written once the ring has drained
+  // Programmatic dependent launch: the successor may be scheduled from here on, and this kernel may itself be running
+  // before its predecessor has finished.  The weights are constant, so the producer fills the ring with weight tiles
+  // first; everything the predecessor may write (activations, the epoch, flags, outputs) is touched after pdl_wait().
+  pdl_launch_dependents();
+  const int pre = (warp == 0 && lane == 0) ? min(kb1 - kb0, kStages) : 0;
+  for (int i = 0; i < pre; ++i) {
+    uint8_t* sw = smem + i * L::kStageBytes;
+    mbar_arrive_expect_tx(&full_bar[i], L::kWBytes + L::kXBytesRaw);
+    tma_load_2d(sw, &tmap_w, &full_bar[i], (kb0 + i) * kBK, nt * kTN);
+  }
+  pdl_wait();
+  const uint32_t epoch = (p.ctx != nullptr) ? ld_volatile(&p.ctx->epoch) : 1u;
+  const int par = epoch & 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t issued = 0;
+      bool ok = true;
+      for (; issued < static_cast<uint32_t>(pre); ++issued)
+        tma_load_2d(smem + issued * L::kStageBytes + L::kWBytes, &tmap_x, &full_bar[issued], (kb0 + issued) * kBK, 0);
+      for (int kb = kb0 + pre; kb < kb1; ++kb, ++issued) {
+        const int s = issued % kStages;
+        const uint32_t ph = (issued / kStages) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kMbarTimeoutNs)) {
+          ok = false;
+          report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 50, -1, s, (int)ph, nt);
+          break;
+        }
+        uint8_t* sw = smem + s * L::kStageBytes;
+        mbar_arrive_expect_tx(&full_bar[s], L::kWBytes + L::kXBytesRaw);
+        tma_load_2d(sw, &tmap_w, &full_bar[s], kb * kBK, nt * kTN);
+        tma_load_2d(sw + L::kWBytes, &tmap_x, &full_bar[s], kb * kBK, 0);
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        const uint32_t first = issued > (uint32_t)kStages ? issued - kStages : 0;
+        for (uint32_t j = first; j < issued; ++j) mbar_wait(&full_bar[j % kStages], (j / kStages) & 1, nullptr, 200000000ull);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(1u, kTN, MPAD);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (!mbar_wait(&full_bar[s], ph, abort_flag, kMbarTimeoutNs)) {
+          ok = false;
+          report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 51, -1, s, (int)ph, nt);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t sw = smem_u32(smem + s * L::kStageBytes);
+        const uint64_t adesc = make_smem_desc_sw128(sw);
+        const uint64_t bdesc = make_smem_desc_sw128(sw + L::kWBytes);
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k)
+          umma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      if (ok) umma_commit(&tmem_full[0]);
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    const int q = warp & 3;
+    if (mbar_wait(&tmem_full[0], 0, abort_flag, kMbarTimeoutNs)) {
+      tc_fence_after_sync();
+      // all MMAs are complete, so every stage of the ring has been consumed and the fp32 part may overwrite it
+      float* mine = part + q * 32 + lane;
+      if constexpr (MPAD >= 32) {
+#pragma unroll 1
+        for (int c = 0; c < MPAD / 32; ++c) {
+          if (c * 32 >= p.M) break;
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mine[(c * 32 + j) * kTN] = __uint_as_float(v[j]);
+        }
+      } else {
+        uint32_t v[16];
+        tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16), v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) mine[j * kTN] = __uint_as_float(v[j]);
+      }
+      tc_fence_before_sync();
+    } else {
+      if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 52, -1, 0, 0, nt);
+      *abort_flag = 1;
+    }
+  }
+
+  // ---- every part of the tile is parked: CTA r reduces its share of the rows
+  __syncthreads();
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  __nv_bfloat16* dst;
+  int64_t ld_dst;
+  if (p.mode == 0) {
+    dst = p.out;
+    ld_dst = p.ld_out;
+  } else if (p.use_mc) {
+    dst = p.partial + par * p.partial_half;
+    ld_dst = p.N;
+  } else {
+    dst = p.partial + par * p.partial_half + static_cast<uint64_t>(p.symm.rank) * p.m_cap * p.N;
+    ld_dst = p.N;
+  }
+  if (warp >= 2) {
+    const int et = threadIdx.x - 64;
+    const int c4 = et & 31;                         // columns [4 * c4, 4 * c4 + 4) of the tile
+    const int rows_per = (p.M + S - 1) / S;
+    const int m_hi = min(p.M, (r + 1) * rows_per);
+    const bool col_ok = nt * kTN + c4 * 4 < p.N;    // N is a multiple of 4
+    for (int m = r * rows_per + (et >> 5); m < m_hi; m += 4) {
+      const uint32_t local = smem_u32(part + m * kTN + c4 * 4);
+      float4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < S) v[j] = ld_dsmem_v4(mapa_u32(local, static_cast<uint32_t>((r + j) % S)));
+      float4 a = v[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j)
+        if (j < S) {
+          a.x += v[j].x; a.y += v[j].y; a.z += v[j].z; a.w += v[j].w;
+        }
+      if (col_ok) {
+        uint2 o;
+        o.x = pack_bf16x2(a.x, a.y);
+        o.y = pack_bf16x2(a.z, a.w);
+        *reinterpret_cast<uint2*>(dst + static_cast<int64_t>(m) * ld_dst + nt * kTN + c4 * 4) = o;
+      }
+    }
+    __threadfence();
+  }
+  // no CTA may leave (or reuse its shared memory) while a peer still reads its part
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  if (p.mode == 1 && r == 0 && warp >= 2) {
+    if (!tile_exchange(p, nt, dst, par, epoch)) *abort_flag = 1;
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, L::kTmemCols);
+  }
+  if (p.ctx != nullptr) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const uint32_t prev = atomicAdd(&p.ctx->done, 1u);
+      if (prev == gridDim.x - 1) {
+        p.ctx->done = 0;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(&p.ctx->epoch) = epoch + 1;
+      }
+    }
+  }
+}
+
+template <int MPAD>
+cudaError_t launch_cluster_t(const SkinnyGemmArgs& a, KP& p, int want_s, cudaStream_t stream, bool* launched) {
+  using L = Layout<MPAD>;
+  const int smem = L::kTotal + 1024;
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(skinny_cluster_kernel<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    set = true;
+  }
+  // co-resident clusters per cluster size, asked once per process
+  static int max_clusters[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  static const bool pdl = [] {
+    const char* e = std::getenv("TDB200_PDL");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 2 : 1;
+  int s = want_s;
+  for (; s >= 1; --s) {
+    attr[0].val.clusterDim.x = s;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3(p.tiles_n * s);
+    if (max_clusters[s] == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, skinny_cluster_kernel<MPAD>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = -1;
+      }
+      max_clusters[s] = n > 0 ? n : -1;
+    }
+    if (max_clusters[s] >= p.tiles_n) break;      // one wave
+  }
+  *launched = false;
+  if (s < 1) return cudaSuccess;                  // the caller falls back to the stream-K form
+  p.cluster_s = s;
+  CUtensorMap tw, tx;
+  memcpy(&tw, a.tmap_w.bytes, sizeof(CUtensorMap));
+  memcpy(&tx, a.tmap_x.bytes, sizeof(CUtensorMap));
+  *launched = true;
+  return cudaLaunchKernelEx(&cfg, skinny_cluster_kernel<MPAD>, tw, tx, p);
 }
 
 template <int MPAD>
@@ -480,6 +778,37 @@ cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream) {
   if ((p.per_cta < p.kb_total || p.per_cta % p.kb_total != 0 || p.mode == 1) && (a.acc == nullptr || a.counters == nullptr))
     return cudaErrorInvalidValue;
   if (p.mode == 1 && (p.tiles_n > a.max_tiles || a.M > a.m_cap || a.ctx == nullptr)) return cudaErrorInvalidValue;
+  // form: without an explicit split count, the cluster kernel when the column tiles fit into one wave of clusters
+  // (every CTA of a cluster gets at least four k-blocks); else, with splits >= 1 or with TDB200_SKINNY_FORM=1, the
+  // stream-K kernel.  TDB200_SKINNY_CLUSTER_S fixes the cluster size.
+  static const int form = [] {
+    const char* e = std::getenv("TDB200_SKINNY_FORM");
+    return e ? std::atoi(e) : 0;
+  }();
+  static const int force_s = [] {
+    const char* e = std::getenv("TDB200_SKINNY_CLUSTER_S");
+    return e ? std::atoi(e) : 0;
+  }();
+  p.cluster_s = 0;
+  if (form != 1 && a.splits < 1 && a.N % 4 == 0 && p.tiles_n <= num_ctas) {
+    int s = num_ctas / p.tiles_n;
+    if (s > 8) s = 8;
+    while (s > 1 && p.kb_total / s < 4) --s;
+    if (force_s >= 1 && force_s <= 8 && force_s <= p.kb_total) s = force_s;
+    if (s >= 1 && p.kb_total >= s) {
+      bool launched = false;
+      cudaError_t e;
+      switch (skinny_gemm_mpad(a.M)) {
+        case 16: e = launch_cluster_t<16>(a, p, s, stream, &launched); break;
+        case 32: e = launch_cluster_t<32>(a, p, s, stream, &launched); break;
+        case 64: e = launch_cluster_t<64>(a, p, s, stream, &launched); break;
+        case 128: e = launch_cluster_t<128>(a, p, s, stream, &launched); break;
+        case 256: e = launch_cluster_t<256>(a, p, s, stream, &launched); break;
+        default: return cudaErrorInvalidValue;
+      }
+      if (e != cudaSuccess || launched) return e;
+    }
+  }
   const int grid = (total_units + p.per_cta - 1) / p.per_cta;
   switch (skinny_gemm_mpad(a.M)) {
     case 16: return launch_t<16>(a, p, grid, stream);

@@ -118,16 +118,19 @@ def create_ll_gemm_ar_context(rank: Optional[int] = None, world_size: Optional[i
 
 
 def pick_gemm_ar_splits(M: int, N: int = 5120, K: int = 3200, num_sms: int = 148) -> int:
-    """K splits per 128-column tile of the swap-AB kernel.  Up to 16 tokens the weights are everything and the
-    stream-K partition over all SMs (0) wins; from 32 tokens on the fp32 split accumulation (M x 128 atomics per piece,
-    then a read-back by the last arriver) costs more than idle SMs, so a tile is computed whole by one CTA and goes
-    straight to its bf16 destination - unless K is so long (more than 64 k-blocks per CTA) that the few CTAs would
-    stream for too long; then K is split as far as the SM count allows.  ``TDB200_GEMM_AR_SPLITS`` overrides."""
+    """K splits per 128-column tile of the swap-AB kernel; 0 leaves the choice to the launcher, which then runs the
+    cluster form (the CTAs of a thread-block cluster split one tile's K range and sum their parts through distributed
+    shared memory) wherever the tiles fit into one wave of clusters.  With ``TDB200_SKINNY_FORM=1`` (stream-K form
+    only): up to 16 tokens the weights are everything and the stream-K partition over all SMs (0) wins; from 32 tokens
+    on the fp32 split accumulation (M x 128 atomics per piece, then a read-back by the last arriver) costs more than
+    idle SMs, so a tile is computed whole by one CTA and goes straight to its bf16 destination - unless K is so long
+    (more than 64 k-blocks per CTA) that the few CTAs would stream for too long; then K is split as far as the SM
+    count allows.  ``TDB200_GEMM_AR_SPLITS`` overrides."""
     import os
     v = os.environ.get("TDB200_GEMM_AR_SPLITS")
     if v not in (None, ""):
         return int(v)
-    if M <= 16:
+    if M <= 16 or os.environ.get("TDB200_SKINNY_FORM", "0") != "1":
         return 0
     tiles = (N + 127) // 128
     kb = (K + 63) // 64
