@@ -432,18 +432,33 @@ TDB_DEVICE float4 ld_dsmem_v4(uint32_t cluster_addr) {
 TDB_DEVICE void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
 TDB_DEVICE void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 
-// Cluster form of the same GEMM: the S CTAs of a thread-block cluster share ONE column tile and split its K range
-// evenly.  Every CTA accumulates its part in TMEM, parks it as fp32 in its own shared memory (the drained TMA ring),
-// and after a cluster barrier CTA r sums rows [r * M / S, (r + 1) * M / S) over all S parts through distributed shared
-// memory and stores them as bf16 rows of 256 bytes.  No global accumulation buffer, no atomics, no arrival counters; the
-// result does not depend on arrival order.  In all-reduce mode CTA 0 of the cluster then runs the cross-rank sum of
-// the tile.
-template <int MPAD>
+// Cluster form of the same GEMM: the S CTAs of a thread-block cluster share ONE column tile (128 * NT columns) and
+// split its K range evenly.  Every CTA accumulates its part in TMEM (NT accumulators that share each activation tile),
+// parks it as fp32 in its own shared memory (the drained TMA ring), and after a cluster barrier CTA r sums rows
+// [r * M / S, (r + 1) * M / S) over all S parts through distributed shared memory and stores them as bf16 rows.  No
+// global accumulation buffer, no atomics, no arrival counters; the result does not depend on arrival order.  In
+// all-reduce mode CTA 0 of the cluster then runs the cross-rank sum of the tile's NT column blocks.
+template <int MPAD, int NT>
+struct ClusterLayout {
+  static constexpr int kWBytes = NT * kTN * kBK * 2;   // NT weight boxes of 16 KB
+  static constexpr int kXBytesRaw = MPAD * kBK * 2;
+  static constexpr int kXBytes = (kXBytesRaw + 1023) / 1024 * 1024;
+  static constexpr int kStageBytes = kWBytes + kXBytes;
+  static constexpr int kStages = (200 * 1024) / kStageBytes > 12 ? 12 : (200 * 1024) / kStageBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 32;
+  static constexpr int kTmemCols = (NT * MPAD) < 32 ? 32 : NT * MPAD;
+  static constexpr int kPartBytes = NT * MPAD * kTN * 4;
+  static_assert(kPartBytes <= kBarOffset, "the fp32 part must fit into the drained ring");
+  static_assert(kTmemCols <= 512, "accumulators exceed TMEM");
+};
+
+template <int MPAD, int NT>
 __global__ void __launch_bounds__(kThreads, 1)
 skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const KP p) {
-  using L = Layout<MPAD>;
+  using L = ClusterLayout<MPAD, NT>;
   constexpr int kStages = L::kStages;
-  static_assert(MPAD * kTN * 4 <= L::kBarOffset, "the fp32 part must fit into the drained ring");
+  constexpr int kCols = NT * kTN;                 // columns of the CTA tile
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
@@ -455,7 +470,7 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.cluster_s;
   const int r = static_cast<int>(cluster_ctarank());
-  const int nt = static_cast<int>(blockIdx.x) / S;
+  const int ct = static_cast<int>(blockIdx.x) / S;   // CTA tile: columns [ct * kCols, (ct + 1) * kCols)
   const int kb0 = static_cast<int>(static_cast<int64_t>(p.kb_total) * r / S);
   const int kb1 = static_cast<int>(static_cast<int64_t>(p.kb_total) * (r + 1) / S);
 
@@ -478,7 +493,7 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_smem;
-  float* part = reinterpret_cast<float*>(smem);   // [M][128] fp32, written once the ring has drained
+  float* part = reinterpret_cast<float*>(smem);   // [M][kCols] fp32, written once the ring has drained
   // Programmatic dependent launch: the successor may be scheduled from here on, and this kernel may itself be running
   // before its predecessor has finished.  The weights are constant, so the producer fills the ring with weight tiles
   // first; everything the predecessor may write (activations, the epoch, flags, outputs) is touched after pdl_wait().
@@ -487,7 +502,9 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   for (int i = 0; i < pre; ++i) {
     uint8_t* sw = smem + i * L::kStageBytes;
     mbar_arrive_expect_tx(&full_bar[i], L::kWBytes + L::kXBytesRaw);
-    tma_load_2d(sw, &tmap_w, &full_bar[i], (kb0 + i) * kBK, nt * kTN);
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+      tma_load_2d(sw + j * (kTN * kBK * 2), &tmap_w, &full_bar[i], (kb0 + i) * kBK, ct * kCols + j * kTN);
   }
   pdl_wait();
   const uint32_t epoch = (p.ctx != nullptr) ? ld_volatile(&p.ctx->epoch) : 1u;
@@ -504,12 +521,14 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         const uint32_t ph = (issued / kStages) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kMbarTimeoutNs)) {
           ok = false;
-          report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 50, -1, s, (int)ph, nt);
+          report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 50, -1, s, (int)ph, ct);
           break;
         }
         uint8_t* sw = smem + s * L::kStageBytes;
         mbar_arrive_expect_tx(&full_bar[s], L::kWBytes + L::kXBytesRaw);
-        tma_load_2d(sw, &tmap_w, &full_bar[s], kb * kBK, nt * kTN);
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+          tma_load_2d(sw + j * (kTN * kBK * 2), &tmap_w, &full_bar[s], kb * kBK, ct * kCols + j * kTN);
         tma_load_2d(sw + L::kWBytes, &tmap_x, &full_bar[s], kb * kBK, 0);
       }
       if (!ok) {
@@ -528,16 +547,19 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         const uint32_t ph = (it / kStages) & 1;
         if (!mbar_wait(&full_bar[s], ph, abort_flag, kMbarTimeoutNs)) {
           ok = false;
-          report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 51, -1, s, (int)ph, nt);
+          report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 51, -1, s, (int)ph, ct);
           break;
         }
         tc_fence_after_sync();
         const uint32_t sw = smem_u32(smem + s * L::kStageBytes);
-        const uint64_t adesc = make_smem_desc_sw128(sw);
         const uint64_t bdesc = make_smem_desc_sw128(sw + L::kWBytes);
 #pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k)
-          umma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        for (int j = 0; j < NT; ++j) {
+          const uint64_t adesc = make_smem_desc_sw128(sw + j * (kTN * kBK * 2));
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_f16(tmem_base + j * MPAD, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        }
         umma_commit(&empty_bar[s]);
       }
       if (ok) umma_commit(&tmem_full[0]);
@@ -548,33 +570,36 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     if (mbar_wait(&tmem_full[0], 0, abort_flag, kMbarTimeoutNs)) {
       tc_fence_after_sync();
       // all MMAs are complete, so every stage of the ring has been consumed and the fp32 part may overwrite it
-      float* mine = part + q * 32 + lane;
-      if constexpr (MPAD >= 32) {
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        float* mine = part + j * kTN + q * 32 + lane;
+        if constexpr (MPAD >= 32) {
 #pragma unroll 1
-        for (int c = 0; c < MPAD / 32; ++c) {
-          if (c * 32 >= p.M) break;
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_base + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+          for (int c = 0; c < MPAD / 32; ++c) {
+            if (c * 32 >= p.M) break;
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + j * MPAD + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mine[(c * 32 + i) * kCols] = __uint_as_float(v[i]);
+          }
+        } else {
+          uint32_t v[16];
+          tmem_ld_32x16(tmem_base + j * MPAD + (static_cast<uint32_t>(q * 32) << 16), v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mine[(c * 32 + j) * kTN] = __uint_as_float(v[j]);
+          for (int i = 0; i < 16; ++i) mine[i * kCols] = __uint_as_float(v[i]);
         }
-      } else {
-        uint32_t v[16];
-        tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16), v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) mine[j * kTN] = __uint_as_float(v[j]);
       }
       tc_fence_before_sync();
     } else {
-      if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 52, -1, 0, 0, nt);
+      if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 52, -1, 0, 0, ct);
       *abort_flag = 1;
     }
   }
 
-  // ---- every part of the tile is parked: CTA r reduces its share of the rows
-  __syncthreads();
+  // ---- every part of the tile is parked: CTA r reduces its share of the rows (each thread arrives after its own
+  // writes, and the barrier completes only when all threads of all CTAs have arrived)
   cluster_arrive_release();
   cluster_wait_acquire();
   __nv_bfloat16* dst;
@@ -591,12 +616,14 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   }
   if (warp >= 2) {
     const int et = threadIdx.x - 64;
-    const int c4 = et & 31;                         // columns [4 * c4, 4 * c4 + 4) of the tile
+    constexpr int kVecRow = kCols / 4;              // float4 per row of the part: 32 or 64
+    constexpr int kRowsPerPass = 128 / kVecRow;     // 4 or 2
+    const int c4 = et % kVecRow;                    // columns [4 * c4, 4 * c4 + 4) of the CTA tile
     const int rows_per = (p.M + S - 1) / S;
     const int m_hi = min(p.M, (r + 1) * rows_per);
-    const bool col_ok = nt * kTN + c4 * 4 < p.N;    // N is a multiple of 4
-    for (int m = r * rows_per + (et >> 5); m < m_hi; m += 4) {
-      const uint32_t local = smem_u32(part + m * kTN + c4 * 4);
+    const bool col_ok = ct * kCols + c4 * 4 < p.N;  // N is a multiple of 4
+    for (int m = r * rows_per + et / kVecRow; m < m_hi; m += kRowsPerPass) {
+      const uint32_t local = smem_u32(part + m * kCols + c4 * 4);
       float4 v[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j)
@@ -611,16 +638,19 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         uint2 o;
         o.x = pack_bf16x2(a.x, a.y);
         o.y = pack_bf16x2(a.z, a.w);
-        *reinterpret_cast<uint2*>(dst + static_cast<int64_t>(m) * ld_dst + nt * kTN + c4 * 4) = o;
+        *reinterpret_cast<uint2*>(dst + static_cast<int64_t>(m) * ld_dst + ct * kCols + c4 * 4) = o;
       }
     }
-    __threadfence();
+    if (p.mode == 1) __threadfence();   // CTA 0 of the cluster reads these rows back for the cross-rank sum
   }
   // no CTA may leave (or reuse its shared memory) while a peer still reads its part
   cluster_arrive_release();
   cluster_wait_acquire();
   if (p.mode == 1 && r == 0 && warp >= 2) {
-    if (!tile_exchange(p, nt, dst, par, epoch)) *abort_flag = 1;
+    bool ok = true;
+    for (int j = 0; ok && j < NT; ++j)
+      if ((ct * NT + j) * kTN < p.N) ok = tile_exchange(p, ct * NT + j, dst, par, epoch);
+    if (!ok) *abort_flag = 1;
   }
 
   tc_fence_before_sync();
@@ -643,56 +673,116 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   }
 }
 
-template <int MPAD>
-cudaError_t launch_cluster_t(const SkinnyGemmArgs& a, KP& p, int want_s, cudaStream_t stream, bool* launched) {
-  using L = Layout<MPAD>;
-  const int smem = L::kTotal + 1024;
-  static bool set = false;
-  if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(skinny_cluster_kernel<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    set = true;
-  }
-  // co-resident clusters per cluster size, asked once per process
-  static int max_clusters[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
-  cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  static const bool pdl = [] {
-    const char* e = std::getenv("TDB200_PDL");
-    return e == nullptr || std::atoi(e) != 0;
-  }();
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 2 : 1;
-  int s = want_s;
-  for (; s >= 1; --s) {
+// Cluster launches of one (M_pad, NT) instantiation: the largest cluster size <= want_s whose clusters all fit into one
+// wave (asked from the occupancy API once per process and size), and the launch itself.
+template <int MPAD, int NT>
+struct ClusterForm {
+  using L = ClusterLayout<MPAD, NT>;
+  static constexpr int kSmem = L::kTotal + 1024;
+
+  static void fill(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int tiles, int s, cudaStream_t stream) {
+    static const bool pdl = [] {
+      const char* e = std::getenv("TDB200_PDL");
+      return e == nullptr || std::atoi(e) != 0;
+    }();
+    cfg = cudaLaunchConfig_t{};
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmem;
+    cfg.stream = stream;
+    cfg.gridDim = dim3(tiles * s);
+    attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = s;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    cfg.gridDim = dim3(p.tiles_n * s);
-    if (max_clusters[s] == 0) {
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, skinny_cluster_kernel<MPAD>, &cfg) != cudaSuccess) {
-        cudaGetLastError();
-        n = -1;
-      }
-      max_clusters[s] = n > 0 ? n : -1;
-    }
-    if (max_clusters[s] >= p.tiles_n) break;      // one wave
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 2 : 1;
   }
+
+  static int feasible_s(int tiles, int want_s) {
+    static bool set = false;
+    if (!set) {
+      if (cudaFuncSetAttribute(skinny_cluster_kernel<MPAD, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+          cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+      }
+      set = true;
+    }
+    static int max_clusters[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = want_s; s >= 1; --s) {
+      if (max_clusters[s] == 0) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[2];
+        fill(cfg, attr, tiles, s, nullptr);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, skinny_cluster_kernel<MPAD, NT>, &cfg) != cudaSuccess) {
+          cudaGetLastError();
+          n = -1;
+        }
+        max_clusters[s] = n > 0 ? n : -1;
+      }
+      if (max_clusters[s] >= tiles) return s;   // one wave
+    }
+    return 0;
+  }
+
+  static cudaError_t launch(const SkinnyGemmArgs& a, KP& p, int tiles, int s, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[2];
+    fill(cfg, attr, tiles, s, stream);
+    p.cluster_s = s;
+    CUtensorMap tw, tx;
+    memcpy(&tw, a.tmap_w.bytes, sizeof(CUtensorMap));
+    memcpy(&tx, a.tmap_x.bytes, sizeof(CUtensorMap));
+    return cudaLaunchKernelEx(&cfg, skinny_cluster_kernel<MPAD, NT>, tw, tx, p);
+  }
+};
+
+// Chooses between 128- and 256-column CTA tiles (the wider tile reads every activation tile half as often and may fill
+// the SMs better or worse, depending on the tile count) by the bytes one CTA has to stream, and launches.  `launched`
+// stays false when no cluster form fits; the caller then runs the stream-K form.
+template <int MPAD>
+cudaError_t launch_cluster_form(const SkinnyGemmArgs& a, KP& p, int num_ctas, int force_s, int force_nt,
+                                cudaStream_t stream, bool* launched) {
   *launched = false;
-  if (s < 1) return cudaSuccess;                  // the caller falls back to the stream-K form
-  p.cluster_s = s;
-  CUtensorMap tw, tx;
-  memcpy(&tw, a.tmap_w.bytes, sizeof(CUtensorMap));
-  memcpy(&tx, a.tmap_x.bytes, sizeof(CUtensorMap));
+  int best_nt = 0, best_s = 0, best_tiles = 0;
+  double best_cost = 1e30;
+  for (int nt = 1; nt <= 2; ++nt) {
+    // measured: the wider tile pays off up to 16 tokens (fewer, longer streams); above, its doubled per-CTA epilogue
+    // (TMEM drain and the exchange through distributed shared memory) costs more than the activation re-reads it saves
+    if (nt == 2 && (MPAD > 128 || (MPAD > 16 && force_nt != 2))) break;
+    if (force_nt != 0 && force_nt != nt) continue;
+    const int tiles = (a.N + nt * kTN - 1) / (nt * kTN);
+    if (tiles > num_ctas) continue;
+    int s = num_ctas / tiles;
+    if (s > 8) s = 8;
+    while (s > 1 && p.kb_total / s < 4) --s;
+    if (force_s >= 1 && force_s <= 8) s = force_s;
+    if (s > p.kb_total) s = p.kb_total;
+    if constexpr (MPAD <= 128) {
+      s = nt == 1 ? ClusterForm<MPAD, 1>::feasible_s(tiles, s) : ClusterForm<MPAD, 2>::feasible_s(tiles, s);
+    } else {
+      s = ClusterForm<MPAD, 1>::feasible_s(tiles, s);
+    }
+    if (s < 1) continue;
+    const int unit = nt * kTN * kBK * 2 + MPAD * kBK * 2;
+    // bytes one CTA streams, plus a fixed cost per CTA worth about six k-blocks of a 128-column tile
+    const double cost = (static_cast<double>(p.kb_total) / s) * unit + 6.0 * kTN * kBK * 2;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best_nt = nt;
+      best_s = s;
+      best_tiles = tiles;
+    }
+  }
+  if (best_nt == 0) return cudaSuccess;
   *launched = true;
-  return cudaLaunchKernelEx(&cfg, skinny_cluster_kernel<MPAD>, tw, tx, p);
+  if constexpr (MPAD <= 128) {
+    if (best_nt == 2) return ClusterForm<MPAD, 2>::launch(a, p, best_tiles, best_s, stream);
+  }
+  return ClusterForm<MPAD, 1>::launch(a, p, best_tiles, best_s, stream);
 }
 
 template <int MPAD>
@@ -780,7 +870,8 @@ cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream) {
   if (p.mode == 1 && (p.tiles_n > a.max_tiles || a.M > a.m_cap || a.ctx == nullptr)) return cudaErrorInvalidValue;
   // form: without an explicit split count, the cluster kernel when the column tiles fit into one wave of clusters
   // (every CTA of a cluster gets at least four k-blocks); else, with splits >= 1 or with TDB200_SKINNY_FORM=1, the
-  // stream-K kernel.  TDB200_SKINNY_CLUSTER_S fixes the cluster size.
+  // stream-K kernel.  TDB200_SKINNY_CLUSTER_S fixes the cluster size, TDB200_SKINNY_CLUSTER_NT the tile width (1: 128
+  // columns, 2: 256).
   static const int form = [] {
     const char* e = std::getenv("TDB200_SKINNY_FORM");
     return e ? std::atoi(e) : 0;
@@ -789,25 +880,23 @@ cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream) {
     const char* e = std::getenv("TDB200_SKINNY_CLUSTER_S");
     return e ? std::atoi(e) : 0;
   }();
+  static const int force_nt = [] {
+    const char* e = std::getenv("TDB200_SKINNY_CLUSTER_NT");
+    return e ? std::atoi(e) : 0;
+  }();
   p.cluster_s = 0;
-  if (form != 1 && a.splits < 1 && a.N % 4 == 0 && p.tiles_n <= num_ctas) {
-    int s = num_ctas / p.tiles_n;
-    if (s > 8) s = 8;
-    while (s > 1 && p.kb_total / s < 4) --s;
-    if (force_s >= 1 && force_s <= 8 && force_s <= p.kb_total) s = force_s;
-    if (s >= 1 && p.kb_total >= s) {
-      bool launched = false;
-      cudaError_t e;
-      switch (skinny_gemm_mpad(a.M)) {
-        case 16: e = launch_cluster_t<16>(a, p, s, stream, &launched); break;
-        case 32: e = launch_cluster_t<32>(a, p, s, stream, &launched); break;
-        case 64: e = launch_cluster_t<64>(a, p, s, stream, &launched); break;
-        case 128: e = launch_cluster_t<128>(a, p, s, stream, &launched); break;
-        case 256: e = launch_cluster_t<256>(a, p, s, stream, &launched); break;
-        default: return cudaErrorInvalidValue;
-      }
-      if (e != cudaSuccess || launched) return e;
+  if (form != 1 && a.splits < 1 && a.N % 4 == 0) {
+    bool launched = false;
+    cudaError_t e;
+    switch (skinny_gemm_mpad(a.M)) {
+      case 16: e = launch_cluster_form<16>(a, p, num_ctas, force_s, force_nt, stream, &launched); break;
+      case 32: e = launch_cluster_form<32>(a, p, num_ctas, force_s, force_nt, stream, &launched); break;
+      case 64: e = launch_cluster_form<64>(a, p, num_ctas, force_s, force_nt, stream, &launched); break;
+      case 128: e = launch_cluster_form<128>(a, p, num_ctas, force_s, force_nt, stream, &launched); break;
+      case 256: e = launch_cluster_form<256>(a, p, num_ctas, force_s, force_nt, stream, &launched); break;
+      default: return cudaErrorInvalidValue;
     }
+    if (e != cudaSuccess || launched) return e;
   }
   const int grid = (total_units + p.per_cta - 1) / p.per_cta;
   switch (skinny_gemm_mpad(a.M)) {

@@ -39,6 +39,8 @@ __global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat1
                                int64_t ldx, float eps) {
   __shared__ float red[32];
   extern __shared__ uint4 row_cache[];  // H/8 vectors
+  pdl_wait();                 // x and the residual come from the previous kernels
+  pdl_launch_dependents();    // a weight-streaming successor may start fetching its weights now
   const int64_t row = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
   uint4* rr = residual ? reinterpret_cast<uint4*>(residual + row * H) : nullptr;
@@ -84,6 +86,8 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloa
                                 int I, int64_t ld_in) {
   const int nv = I >> 3;
   const int64_t total = T * nv;
+  pdl_wait();
+  pdl_launch_dependents();
   for (int64_t v = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; v < total;
        v += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t t = v / nv;
@@ -277,18 +281,16 @@ cudaError_t launch_rmsnorm(const void* x, void* residual, const void* w, void* o
       set = true;
     }
   }
-  rmsnorm_kernel<<<static_cast<unsigned>(T), threads, smem, s>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(residual),
-      reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(out), H, ldx, eps);
-  return cudaGetLastError();
+  return launch_pdl(rmsnorm_kernel, dim3(static_cast<unsigned>(T)), dim3(threads), smem, s,
+                    reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<__nv_bfloat16*>(residual),
+                    reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(out), H, ldx, eps);
 }
 
 cudaError_t launch_silu_mul(const void* in, void* out, int64_t T, int I, int64_t ld_in, cudaStream_t s) {
   if (I % 8 != 0 || ld_in % 8 != 0) return cudaErrorInvalidValue;
   if (T == 0) return cudaSuccess;
-  silu_mul_kernel<<<grid_for(T * (I / 8), 256, 148 * 8), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(in),
-                                                                      reinterpret_cast<__nv_bfloat16*>(out), T, I, ld_in);
-  return cudaGetLastError();
+  return launch_pdl(silu_mul_kernel, dim3(grid_for(T * (I / 8), 256, 148 * 8)), dim3(256), 0, s,
+                    reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), T, I, ld_in);
 }
 
 cudaError_t launch_add(const void* a, const void* b, void* out, int64_t n, cudaStream_t s) {

@@ -6,6 +6,7 @@ torch reference is used.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -15,6 +16,9 @@ from ..utils.oplog import logged_op
 
 
 SKINNY_M = 128   # up to this many rows the weight-streaming kernel wins
+# TDB200_SMALL_M_GEMM=cublas sends plain (unfused) GEMMs of 9..SKINNY_M rows to the library instead of the own
+# weight-streaming kernel; a measurement switch, the fused GEMM + all-reduce layers are not affected.
+_SMALL_M_LIBRARY = os.environ.get("TDB200_SMALL_M_GEMM", "own") == "cublas"
 
 
 def use_cta_pair(kernel_form: str, rows: int, n: int, out: Optional[torch.Tensor] = None) -> bool:
@@ -91,6 +95,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, b
             if (a2.shape[0] <= GEMV_FAST_M and gemv_supported(a2.shape[0], a2.shape[1]) and b.stride(0) % 8 == 0
                     and a2.stride(0) % 8 == 0 and a2.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0):
                 gemv_fused(a2, b, out=o2)
+            elif _SMALL_M_LIBRARY:
+                torch.matmul(a2, b.t(), out=o2)
             else:
                 skinny_gemm(a2, b, out=o2)
         else:
