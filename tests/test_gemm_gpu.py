@@ -105,6 +105,29 @@ def test_skinny_gemm_split_k(shape):
         assert err < 2e-2, f"skinny {shape} splits={splits}: rel err {err}"
 
 
+@pytest.mark.parametrize("shape,cluster", [
+    ((16, 2560, 5120), (1, 6)), ((16, 2560, 5120), (2, 8)), ((16, 2560, 5120), (3, 4)), ((16, 2560, 5120), (4, 3)),
+    ((128, 5120, 2048), (1, 3)), ((128, 5120, 2048), (2, 5)), ((128, 5120, 2048), (3, 2)),
+    ((64, 520, 264), (1, 1)), ((64, 520, 264), (2, 2)), ((33, 520, 264), (3, 1)), ((200, 1280, 1024), (1, 4)),
+])
+def test_skinny_gemm_cluster_forms(shape, cluster):
+    """Every tile width / cluster size of the cluster form against the fp32 reference (column edge: N = 520)."""
+    from triton_distributed_b200.ops import skinny_gemm
+
+    M, N, K = shape
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    try:
+        out = skinny_gemm(a, b, cluster=cluster)
+    except RuntimeError as e:
+        pytest.skip(f"cluster form {cluster} cannot run here: {e}")
+    out = skinny_gemm(a, b, cluster=cluster)
+    torch.cuda.synchronize()
+    err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+    assert err < 2e-2, f"cluster form {cluster} on {shape}: rel err {err}"
+
+
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 8, 12, 16])
 @pytest.mark.parametrize("mode", ["plain", "norm", "silu", "norm_residual"])
 def test_gemv_fused(M, mode):

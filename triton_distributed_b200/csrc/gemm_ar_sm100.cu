@@ -438,19 +438,29 @@ TDB_DEVICE void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acqu
 // [r * M / S, (r + 1) * M / S) over all S parts through distributed shared memory and stores them as bf16 rows.  No
 // global accumulation buffer, no atomics, no arrival counters; the result does not depend on arrival order.  In
 // all-reduce mode CTA 0 of the cluster then runs the cross-rank sum of the tile's NT column blocks.
+constexpr int cluster_stage_bytes(int mpad, int nt) { return nt * kTN * kBK * 2 + (mpad * kBK * 2 + 1023) / 1024 * 1024; }
+constexpr int cluster_stages(int mpad, int nt) {
+  return (200 * 1024) / cluster_stage_bytes(mpad, nt) > 12 ? 12 : (200 * 1024) / cluster_stage_bytes(mpad, nt);
+}
+constexpr int pow2_at_least(int v) { return v <= 32 ? 32 : v <= 64 ? 64 : v <= 128 ? 128 : v <= 256 ? 256 : 512; }
+// a (token pad, tile width) pair can run when its accumulators fit TMEM, its fp32 part fits the drained ring and the
+// ring keeps at least three stages
+constexpr bool cluster_form_ok(int mpad, int nt) {
+  return nt * mpad <= 512 && cluster_stages(mpad, nt) >= 3 &&
+         nt * mpad * kTN * 4 <= cluster_stages(mpad, nt) * cluster_stage_bytes(mpad, nt);
+}
+
 template <int MPAD, int NT>
 struct ClusterLayout {
   static constexpr int kWBytes = NT * kTN * kBK * 2;   // NT weight boxes of 16 KB
   static constexpr int kXBytesRaw = MPAD * kBK * 2;
   static constexpr int kXBytes = (kXBytesRaw + 1023) / 1024 * 1024;
   static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kStages = (200 * 1024) / kStageBytes > 12 ? 12 : (200 * 1024) / kStageBytes;
+  static constexpr int kStages = cluster_stages(MPAD, NT);
   static constexpr int kBarOffset = kStages * kStageBytes;
   static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 32;
-  static constexpr int kTmemCols = (NT * MPAD) < 32 ? 32 : NT * MPAD;
-  static constexpr int kPartBytes = NT * MPAD * kTN * 4;
-  static_assert(kPartBytes <= kBarOffset, "the fp32 part must fit into the drained ring");
-  static_assert(kTmemCols <= 512, "accumulators exceed TMEM");
+  static constexpr int kTmemCols = pow2_at_least(NT * MPAD);
+  static_assert(cluster_form_ok(MPAD, NT), "invalid cluster form");
 };
 
 template <int MPAD, int NT>
@@ -616,17 +626,18 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   }
   if (warp >= 2) {
     const int et = threadIdx.x - 64;
-    constexpr int kVecRow = kCols / 4;              // float4 per row of the part: 32 or 64
-    constexpr int kRowsPerPass = 128 / kVecRow;     // 4 or 2
+    constexpr int kVecRow = kCols / 4;              // float4 per row of the part: 32, 64, 96 or 128
+    constexpr int kRowsPerPass = 128 / kVecRow;     // 4, 2, 1 (32 threads idle) or 1
     const int c4 = et % kVecRow;                    // columns [4 * c4, 4 * c4 + 4) of the CTA tile
     const int rows_per = (p.M + S - 1) / S;
-    const int m_hi = min(p.M, (r + 1) * rows_per);
+    const int m_hi = et < kRowsPerPass * kVecRow ? min(p.M, (r + 1) * rows_per) : 0;
     const bool col_ok = ct * kCols + c4 * 4 < p.N;  // N is a multiple of 4
     for (int m = r * rows_per + et / kVecRow; m < m_hi; m += kRowsPerPass) {
       const uint32_t local = smem_u32(part + m * kCols + c4 * 4);
       float4 v[8];
+      v[0] = *reinterpret_cast<const float4*>(part + m * kCols + c4 * 4);   // the own part: a plain shared load
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
+      for (int j = 1; j < 8; ++j)
         if (j < S) v[j] = ld_dsmem_v4(mapa_u32(local, static_cast<uint32_t>((r + j) % S)));
       float4 a = v[0];
 #pragma unroll
@@ -700,32 +711,31 @@ struct ClusterForm {
     cfg.numAttrs = pdl ? 2 : 1;
   }
 
-  static int feasible_s(int tiles, int want_s) {
+  // whether `tiles` clusters of s CTAs are co-resident (asked from the occupancy API once per process and size)
+  static bool fits(int tiles, int s) {
     static bool set = false;
     if (!set) {
       if (cudaFuncSetAttribute(skinny_cluster_kernel<MPAD, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
           cudaSuccess) {
         cudaGetLastError();
-        return 0;
+        return false;
       }
       set = true;
     }
     static int max_clusters[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
-    for (int s = want_s; s >= 1; --s) {
-      if (max_clusters[s] == 0) {
-        cudaLaunchConfig_t cfg;
-        cudaLaunchAttribute attr[2];
-        fill(cfg, attr, tiles, s, nullptr);
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, skinny_cluster_kernel<MPAD, NT>, &cfg) != cudaSuccess) {
-          cudaGetLastError();
-          n = -1;
-        }
-        max_clusters[s] = n > 0 ? n : -1;
+    if (s < 1 || s > 8) return false;
+    if (max_clusters[s] == 0) {
+      cudaLaunchConfig_t cfg;
+      cudaLaunchAttribute attr[2];
+      fill(cfg, attr, tiles, s, nullptr);
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, skinny_cluster_kernel<MPAD, NT>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = -1;
       }
-      if (max_clusters[s] >= tiles) return s;   // one wave
+      max_clusters[s] = n > 0 ? n : -1;
     }
-    return 0;
+    return max_clusters[s] >= tiles;   // one wave
   }
 
   static cudaError_t launch(const SkinnyGemmArgs& a, KP& p, int tiles, int s, cudaStream_t stream) {
@@ -740,49 +750,77 @@ struct ClusterForm {
   }
 };
 
-// Chooses between 128- and 256-column CTA tiles (the wider tile reads every activation tile half as often and may fill
-// the SMs better or worse, depending on the tile count) by the bytes one CTA has to stream, and launches.  `launched`
-// stays false when no cluster form fits; the caller then runs the stream-K form.
+// One (tile width, cluster size) candidate of the cluster form: its cost in bytes one CTA has to move.  Streaming a
+// byte of weights or activations into shared memory is the unit; a byte of the fp32 exchange through distributed shared
+// memory costs about 2.5 of them (measured: the exchange of a 64 KB part takes as long as streaming 160 KB), and every
+// CTA pays a fixed cost worth about 96 KB.
+template <int MPAD, int NT>
+void cluster_candidates(const SkinnyGemmArgs& a, const KP& p, int num_ctas, int force_s, double* best_cost, int* best_nt,
+                        int* best_s, int* best_tiles) {
+  if constexpr (cluster_form_ok(MPAD, NT)) {
+    const int tiles = (a.N + NT * kTN - 1) / (NT * kTN);
+    if (tiles > num_ctas) return;
+    int s_max = num_ctas / tiles;
+    if (s_max > 8) s_max = 8;
+    if (s_max > p.kb_total) s_max = p.kb_total;
+    const double unit = NT * kTN * kBK * 2 + MPAD * kBK * 2;
+    const double part = static_cast<double>(NT) * MPAD * kTN * 4;
+    for (int s = s_max; s >= 1; --s) {
+      if (force_s >= 1 && s != force_s) continue;
+      if (s > 1 && p.kb_total / s < 4 && force_s < 1) continue;
+      if (!ClusterForm<MPAD, NT>::fits(tiles, s)) continue;
+      const double kb = (p.kb_total + s - 1) / s;
+      const double cost = kb * unit + (s > 1 ? 2.5 * part * (s - 1) / s : 0.0) + 96.0 * 1024;
+      if (cost < *best_cost) {
+        *best_cost = cost;
+        *best_nt = NT;
+        *best_s = s;
+        *best_tiles = tiles;
+      }
+    }
+  }
+}
+
+template <int MPAD, int NT>
+cudaError_t cluster_launch_if(const SkinnyGemmArgs& a, KP& p, int tiles, int s, cudaStream_t stream) {
+  if constexpr (cluster_form_ok(MPAD, NT)) {
+    return ClusterForm<MPAD, NT>::launch(a, p, tiles, s, stream);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+}
+
+// Chooses the CTA tile width (128 to 512 columns: a wider tile reads every activation tile less often, but has a larger
+// part to exchange and leaves fewer tiles to spread over the SMs) and the cluster size, and launches.  Measured on the
+// Qwen3-32B shapes at TP 2 / 4 / 8: from 64 tokens on the 128-column tile with the largest cluster that fits always
+// won, so only that is considered there; below, the byte-cost model decides.  A choice that ends at one CTA per tile
+// is left to the stream-K kernel, whose unsplit tiles go from TMEM straight to their destination (`whole_tiles`).
+// `launched` stays false when no cluster form fits or is wanted; the caller then runs the stream-K form.
 template <int MPAD>
 cudaError_t launch_cluster_form(const SkinnyGemmArgs& a, KP& p, int num_ctas, int force_s, int force_nt,
-                                cudaStream_t stream, bool* launched) {
+                                bool explicit_cfg, cudaStream_t stream, bool* launched, bool* whole_tiles) {
   *launched = false;
-  int best_nt = 0, best_s = 0, best_tiles = 0;
-  double best_cost = 1e30;
-  for (int nt = 1; nt <= 2; ++nt) {
-    // measured: the wider tile pays off up to 16 tokens (fewer, longer streams); above, its doubled per-CTA epilogue
-    // (TMEM drain and the exchange through distributed shared memory) costs more than the activation re-reads it saves
-    if (nt == 2 && (MPAD > 128 || (MPAD > 16 && force_nt != 2))) break;
-    if (force_nt != 0 && force_nt != nt) continue;
-    const int tiles = (a.N + nt * kTN - 1) / (nt * kTN);
-    if (tiles > num_ctas) continue;
-    int s = num_ctas / tiles;
-    if (s > 8) s = 8;
-    while (s > 1 && p.kb_total / s < 4) --s;
-    if (force_s >= 1 && force_s <= 8) s = force_s;
-    if (s > p.kb_total) s = p.kb_total;
-    if constexpr (MPAD <= 128) {
-      s = nt == 1 ? ClusterForm<MPAD, 1>::feasible_s(tiles, s) : ClusterForm<MPAD, 2>::feasible_s(tiles, s);
-    } else {
-      s = ClusterForm<MPAD, 1>::feasible_s(tiles, s);
-    }
-    if (s < 1) continue;
-    const int unit = nt * kTN * kBK * 2 + MPAD * kBK * 2;
-    // bytes one CTA streams, plus a fixed cost per CTA worth about six k-blocks of a 128-column tile
-    const double cost = (static_cast<double>(p.kb_total) / s) * unit + 6.0 * kTN * kBK * 2;
-    if (cost < best_cost) {
-      best_cost = cost;
-      best_nt = nt;
-      best_s = s;
-      best_tiles = tiles;
-    }
+  int nt = 0, s = 0, tiles = 0;
+  double cost = 1e30;
+  const bool narrow_only = MPAD >= 64 && force_nt == 0;
+  if (force_nt == 0 || force_nt == 1) cluster_candidates<MPAD, 1>(a, p, num_ctas, force_s, &cost, &nt, &s, &tiles);
+  if (!narrow_only) {
+    if (force_nt == 0 || force_nt == 2) cluster_candidates<MPAD, 2>(a, p, num_ctas, force_s, &cost, &nt, &s, &tiles);
+    if (force_nt == 0 || force_nt == 3) cluster_candidates<MPAD, 3>(a, p, num_ctas, force_s, &cost, &nt, &s, &tiles);
+    if (force_nt == 0 || force_nt == 4) cluster_candidates<MPAD, 4>(a, p, num_ctas, force_s, &cost, &nt, &s, &tiles);
   }
-  if (best_nt == 0) return cudaSuccess;
+  if (nt == 0) return cudaSuccess;
+  if (s == 1 && !explicit_cfg && force_s == 0) {
+    *whole_tiles = true;
+    return cudaSuccess;
+  }
   *launched = true;
-  if constexpr (MPAD <= 128) {
-    if (best_nt == 2) return ClusterForm<MPAD, 2>::launch(a, p, best_tiles, best_s, stream);
+  switch (nt) {
+    case 1: return cluster_launch_if<MPAD, 1>(a, p, tiles, s, stream);
+    case 2: return cluster_launch_if<MPAD, 2>(a, p, tiles, s, stream);
+    case 3: return cluster_launch_if<MPAD, 3>(a, p, tiles, s, stream);
+    default: return cluster_launch_if<MPAD, 4>(a, p, tiles, s, stream);
   }
-  return ClusterForm<MPAD, 1>::launch(a, p, best_tiles, best_s, stream);
 }
 
 template <int MPAD>
@@ -870,33 +908,43 @@ cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream) {
   if (p.mode == 1 && (p.tiles_n > a.max_tiles || a.M > a.m_cap || a.ctx == nullptr)) return cudaErrorInvalidValue;
   // form: without an explicit split count, the cluster kernel when the column tiles fit into one wave of clusters
   // (every CTA of a cluster gets at least four k-blocks); else, with splits >= 1 or with TDB200_SKINNY_FORM=1, the
-  // stream-K kernel.  TDB200_SKINNY_CLUSTER_S fixes the cluster size, TDB200_SKINNY_CLUSTER_NT the tile width (1: 128
-  // columns, 2: 256).
+  // stream-K kernel.  TDB200_SKINNY_CLUSTER_S fixes the cluster size, TDB200_SKINNY_CLUSTER_NT the tile width in
+  // units of 128 columns (1 to 4).
   static const int form = [] {
     const char* e = std::getenv("TDB200_SKINNY_FORM");
     return e ? std::atoi(e) : 0;
   }();
-  static const int force_s = [] {
+  static const int env_s = [] {
     const char* e = std::getenv("TDB200_SKINNY_CLUSTER_S");
     return e ? std::atoi(e) : 0;
   }();
-  static const int force_nt = [] {
+  static const int env_nt = [] {
     const char* e = std::getenv("TDB200_SKINNY_CLUSTER_NT");
     return e ? std::atoi(e) : 0;
   }();
+  // an explicit (tile width, cluster size) of the caller, e.g. from the tuned table, comes before the environment; when
+  // it cannot run (clusters not co-resident, accumulators or part too large), the launch fails instead of silently
+  // running another form
+  const bool explicit_cfg = a.cluster_nt >= 1 && a.cluster_s >= 1;
+  const int force_nt = explicit_cfg ? a.cluster_nt : env_nt;
+  const int force_s = explicit_cfg ? a.cluster_s : env_s;
   p.cluster_s = 0;
   if (form != 1 && a.splits < 1 && a.N % 4 == 0) {
-    bool launched = false;
+    bool launched = false, whole_tiles = false;
     cudaError_t e;
     switch (skinny_gemm_mpad(a.M)) {
-      case 16: e = launch_cluster_form<16>(a, p, num_ctas, force_s, force_nt, stream, &launched); break;
-      case 32: e = launch_cluster_form<32>(a, p, num_ctas, force_s, force_nt, stream, &launched); break;
-      case 64: e = launch_cluster_form<64>(a, p, num_ctas, force_s, force_nt, stream, &launched); break;
-      case 128: e = launch_cluster_form<128>(a, p, num_ctas, force_s, force_nt, stream, &launched); break;
-      case 256: e = launch_cluster_form<256>(a, p, num_ctas, force_s, force_nt, stream, &launched); break;
+      case 16: e = launch_cluster_form<16>(a, p, num_ctas, force_s, force_nt, explicit_cfg, stream, &launched, &whole_tiles); break;
+      case 32: e = launch_cluster_form<32>(a, p, num_ctas, force_s, force_nt, explicit_cfg, stream, &launched, &whole_tiles); break;
+      case 64: e = launch_cluster_form<64>(a, p, num_ctas, force_s, force_nt, explicit_cfg, stream, &launched, &whole_tiles); break;
+      case 128: e = launch_cluster_form<128>(a, p, num_ctas, force_s, force_nt, explicit_cfg, stream, &launched, &whole_tiles); break;
+      case 256: e = launch_cluster_form<256>(a, p, num_ctas, force_s, force_nt, explicit_cfg, stream, &launched, &whole_tiles); break;
       default: return cudaErrorInvalidValue;
     }
     if (e != cudaSuccess || launched) return e;
+    if (explicit_cfg) return cudaErrorInvalidConfiguration;
+    // one CTA per tile was the best the cluster form could offer: the stream-K kernel with unsplit tiles does the same
+    // work with a shorter epilogue
+    if (whole_tiles && skinny_gemm_mpad(a.M) >= 64) p.per_cta = even > p.kb_total ? even : p.kb_total;
   }
   const int grid = (total_units + p.per_cta - 1) / p.per_cta;
   switch (skinny_gemm_mpad(a.M)) {

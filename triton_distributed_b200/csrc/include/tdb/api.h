@@ -142,7 +142,10 @@ struct SkinnyGemmArgs {
   TensorMap tmap_x;        // X [M, K], box [M_pad x 64], 128-byte swizzle
   void* out;               // bf16 [M, ld_out]
   int64_t ld_out;
-  int splits;              // 0: automatic stream-K partition; >= 1: about this many pieces per column tile
+  int splits;              // 0: automatic (cluster form where it fits); >= 1: stream-K form, about this many pieces per
+                           // column tile
+  int cluster_nt;          // cluster form: CTA tile width in units of 128 columns (1..4), 0 = chosen by the launcher
+  int cluster_s;           // cluster form: CTAs per tile (1..8), 0 = chosen by the launcher
   int num_ctas;
   float* acc;              // fp32 [m_cap, N], all zero between calls
   uint32_t* counters;      // [ceil(N/128)], zero between calls

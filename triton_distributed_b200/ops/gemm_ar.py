@@ -37,15 +37,36 @@ def _scratch(device, need_acc: int, need_tiles: int):
     return cur
 
 
-def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, splits: int = 0) -> torch.Tensor:
-    """``x`` [M<=256, K] @ ``w`` [N, K]^T with the weight-streaming split-K kernel."""
+def _mpad(m: int) -> int:
+    return 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128 if m <= 128 else 256
+
+
+def cluster_config(M: int, N: int, K: int) -> Tuple[int, int]:
+    """(tile width in 128-column blocks, CTAs per tile) of the cluster form for this problem: what the autotuner is
+    trying, else the measured winner from ``ops.tuned_configs``, else (0, 0) = the launcher's cost model."""
+    tuned = current_config()
+    if "cluster_nt" in tuned and "cluster_s" in tuned:
+        return int(tuned["cluster_nt"]), int(tuned["cluster_s"])
+    from .tuned_configs import lookup
+    cfg = lookup("skinny_gemm", 1, _mpad(M), N, K)
+    if cfg and sm_count(torch.cuda.current_device()) == 148:   # the table was measured on 148 SMs
+        return int(cfg["cluster_nt"]), int(cfg["cluster_s"])
+    return 0, 0
+
+
+def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, splits: int = 0,
+                cluster: Optional[Tuple[int, int]] = None) -> torch.Tensor:
+    """``x`` [M<=256, K] @ ``w`` [N, K]^T with the weight-streaming kernel.  ``splits`` >= 1 asks for the stream-K form
+    with about that many pieces per column tile; 0 runs the cluster form where it fits.  ``cluster`` = (tile width in
+    128-column blocks, CTAs per tile) fixes the cluster form's shape (an infeasible one raises)."""
     lib = _native.load(True)
     M, K = x.shape
     N = w.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)
     acc, cnt = _scratch(x.device, M * N, (N + 127) // 128)
-    lib.skinny_gemm_bf16(x, w, out, acc, cnt, splits, 0)
+    nt, s = cluster if cluster is not None else (cluster_config(M, N, K) if splits < 1 else (0, 0))
+    lib.skinny_gemm_bf16(x, w, out, acc, cnt, splits, 0, nt, s)
     return out
 
 
@@ -130,7 +151,14 @@ def pick_gemm_ar_splits(M: int, N: int = 5120, K: int = 3200, num_sms: int = 148
     v = os.environ.get("TDB200_GEMM_AR_SPLITS")
     if v not in (None, ""):
         return int(v)
-    if M <= 16 or os.environ.get("TDB200_SKINNY_FORM", "0") != "1":
+    if os.environ.get("TDB200_SKINNY_FORM", "0") != "1":
+        return 0
+    return pick_stream_k_splits(M, N, K, num_sms)
+
+
+def pick_stream_k_splits(M: int, N: int, K: int, num_sms: int = 148) -> int:
+    """Split count of the stream-K form (see :func:`pick_gemm_ar_splits`)."""
+    if M <= 16:
         return 0
     tiles = (N + 127) // 128
     kb = (K + 63) // 64
@@ -182,8 +210,9 @@ def gemm_allreduce_op(ctx: GemmARContext, a: torch.Tensor, b: torch.Tensor, cfg=
     tuned = current_config()
     splits = tuned["gemm_ar_splits"] if "gemm_ar_splits" in tuned else (
         ctx.splits if ctx.splits is not None else pick_gemm_ar_splits(M, N, K))
+    nt, s = cluster_config(M, N, K) if int(splits) < 1 else (0, 0)
     lib.gemm_ar_bf16(rt.heap, a, b, output, ctx.acc, ctx.counters, ctx.partial, ctx.flags, ctx.ctx_dev, ctx.m_cap,
-                     ctx.max_tiles, int(splits), 0, bool(ctx.use_multimem), rt.config.wait_timeout_s)
+                     ctx.max_tiles, int(splits), 0, bool(ctx.use_multimem), rt.config.wait_timeout_s, nt, s)
     ctx.calls += 1
     return output
 

@@ -19,6 +19,15 @@ _TABLE: Dict[Tuple[str, int, int, int, int], Dict] = {
     # unicast comm CTAs starved the GEMM for a third of its time and twenty cost a whole wave of tiles.
     ("ag_gemm", 4, 2048, 7168, 8192): {"use_multimem": True, "n_comm_ctas": 4},
     ("ag_gemm", 8, 1024, 3584, 8192): {"use_multimem": True, "n_comm_ctas": 4},
+    # Decode GEMM, cluster form ("skinny_gemm", 1, token pad, N, K): CTA tile width in 128-column blocks and CTAs per
+    # tile, where `benchmarks/tune_skinny.py` found a pair at least 3 % faster than the launcher's cost model on a
+    # 148-SM B200 (Qwen3-32B per-rank shapes; microseconds: winner / model / cuBLAS).
+    ("skinny_gemm", 1, 16, 6400, 5120): {"cluster_nt": 2, "cluster_s": 4},    # TP8 gate_up   15.5 / 16.0 / 14.7
+    ("skinny_gemm", 1, 32, 6400, 5120): {"cluster_nt": 2, "cluster_s": 4},    #               16.8 / 17.5 / 15.4
+    ("skinny_gemm", 1, 16, 5120, 3200): {"cluster_nt": 2, "cluster_s": 6},    # TP8 down      11.1 / 11.7 / 10.1
+    ("skinny_gemm", 1, 16, 2560, 5120): {"cluster_nt": 2, "cluster_s": 8},    # TP4 qkv       10.3 / 10.7 / 10.3
+    ("skinny_gemm", 1, 16, 5120, 2048): {"cluster_nt": 2, "cluster_s": 4},    # TP4 o_proj     9.3 /  9.8 /  7.9
+    ("skinny_gemm", 1, 16, 5120, 5120): {"cluster_nt": 2, "cluster_s": 6},    # TP2 qkv       13.9 / 14.7 / 13.6
 }
 
 
