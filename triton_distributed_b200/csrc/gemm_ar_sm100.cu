@@ -802,7 +802,9 @@ cudaError_t launch_cluster_form(const SkinnyGemmArgs& a, KP& p, int num_ctas, in
   *launched = false;
   int nt = 0, s = 0, tiles = 0;
   double cost = 1e30;
-  const bool narrow_only = MPAD >= 64 && force_nt == 0;
+  // all-reduce mode: one 128-column block per cluster, so that the cross-rank exchanges of all blocks run side by side
+  // (the blocks of a wider tile would be exchanged one after the other by the cluster's first CTA)
+  const bool narrow_only = (MPAD >= 64 || a.all_reduce != 0) && force_nt == 0;
   if (force_nt == 0 || force_nt == 1) cluster_candidates<MPAD, 1>(a, p, num_ctas, force_s, &cost, &nt, &s, &tiles);
   if (!narrow_only) {
     if (force_nt == 0 || force_nt == 2) cluster_candidates<MPAD, 2>(a, p, num_ctas, force_s, &cost, &nt, &s, &tiles);

@@ -113,6 +113,15 @@ def create_gemm_ar_context(ar_stream=None, rank: Optional[int] = None, world_siz
     rt = get_runtime()
     rank = rt.rank if rank is None else rank
     world_size = rt.world_size if world_size is None else world_size
+    import os
+    # With two ranks the push form (each rank stores its partial tile into the peer's slot, one NVLink latency) beat
+    # the NVLS form (flag, then multimem.ld_reduce: two latencies) by 2-10 %; with more ranks the switch does the sum.
+    # TDB200_GEMM_AR_MC=0 / 1 forces one form.
+    mc_env = os.environ.get("TDB200_GEMM_AR_MC", "")
+    if mc_env in ("0", "1"):
+        use_multimem = mc_env == "1"
+    elif world_size == 2:
+        use_multimem = False
     ctx = GemmARContext(rt=rt, rank=rank, world_size=world_size, max_M=max_M, N=N, dtype=dtype,
                         use_multimem=use_multimem)
     if rt.is_cuda and world_size > 1:
@@ -210,7 +219,10 @@ def gemm_allreduce_op(ctx: GemmARContext, a: torch.Tensor, b: torch.Tensor, cfg=
     tuned = current_config()
     splits = tuned["gemm_ar_splits"] if "gemm_ar_splits" in tuned else (
         ctx.splits if ctx.splits is not None else pick_gemm_ar_splits(M, N, K))
-    nt, s = cluster_config(M, N, K) if int(splits) < 1 else (0, 0)
+    nt, s = 0, 0          # the launcher's choice: in all-reduce mode always 128-column tiles (one exchange per cluster)
+    tuned_now = current_config()
+    if "cluster_nt" in tuned_now and "cluster_s" in tuned_now and int(splits) < 1:
+        nt, s = int(tuned_now["cluster_nt"]), int(tuned_now["cluster_s"])
     lib.gemm_ar_bf16(rt.heap, a, b, output, ctx.acc, ctx.counters, ctx.partial, ctx.flags, ctx.ctx_dev, ctx.m_cap,
                      ctx.max_tiles, int(splits), 0, bool(ctx.use_multimem), rt.config.wait_timeout_s, nt, s)
     ctx.calls += 1
