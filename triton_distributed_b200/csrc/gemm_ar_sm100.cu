@@ -4,17 +4,27 @@
 //
 // The problem is swapped so that the weight rows fill the 128-row dimension of tcgen05.mma: the A operand is a
 // 128 x 64 weight tile, the B operand the M_pad x 64 activation tile, and the accumulator in TMEM is
-// [128 lanes = output columns] x [M_pad columns = tokens].  The work is the flattened list of (column tile, k-block)
-// units; every CTA takes one contiguous, equally long range of it ("stream-K"), so all SMs stream the same number of
-// weight bytes whatever the tile count is, and the weights are read exactly once through a deep TMA ring, which is
-// what bounds decode GEMMs.  A range covers pieces of one to three tiles.  A piece that spans a tile's whole K is
-// stored directly; other pieces are added with red.global.add.v4.f32 into a column-major accumulation buffer, and the CTA that
-// arrives last on a column tile converts it, clears the buffer again (self-cleaning, CUDA-graph safe) and, in
-// all-reduce mode, runs the cross-rank sum for that tile right away:
+// [128 lanes = output columns] x [M_pad columns = tokens].  The weights are read exactly once through a deep TMA ring,
+// which is what bounds decode GEMMs.  Two kernels share this core:
+//
+//   cluster form (skinny_cluster_kernel, the default): the S <= 8 CTAs of a thread-block cluster share one tile of
+//     128 * NT columns and split its K range evenly; their fp32 parts meet through distributed shared memory
+//     (no global scratch, no atomics, a result that does not depend on arrival order).  Launched with programmatic
+//     dependent launch: weight tiles are requested before griddepcontrol.wait.
+//   stream-K form (skinny_gemm_kernel; more column tiles than SMs, explicit split counts, unsplit tiles): the work is
+//     the flattened list of (column tile, k-block) units; every CTA takes one contiguous, equally long range of it, so
+//     all SMs stream the same number of weight bytes whatever the tile count is.  A range covers pieces of one to three
+//     tiles.  A piece that spans a tile's whole K is stored directly; other pieces are added with
+//     red.global.add.v4.f32 into a column-major accumulation buffer, and the CTA that arrives last on a column tile
+//     converts it and clears the buffer again (self-cleaning, CUDA-graph safe).
+//
+// In all-reduce mode the CTA that completes a column tile (the last arriver, or the first CTA of the cluster) runs the
+// cross-rank sum for that tile right away:
 //     NVLS:  store the bf16 partial tile to the heap, flag all ranks, wait for all ranks' flags of this tile,
 //            multimem.ld_reduce the tile (summed inside the switch) -> out
 //     push:  store the partial tile into slot [rank] on every peer, flag, wait, sum the W slots -> out
-// so the all-reduce of early tiles overlaps the GEMM of later ones and there is one launch per layer op.
+// so there is one launch per layer op, and in the stream-K form the all-reduce of early tiles overlaps the GEMM of
+// later ones.
 //
 // Reference behaviour being matched (not its code): python/triton_dist/kernels/nvidia/gemm_allreduce.py:124-315
 // (per-tile flags, consumer CTAs reduce with multimem.ld_reduce, double-buffered phases :74-92), layer wrapper
