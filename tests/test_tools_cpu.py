@@ -103,6 +103,35 @@ def test_autotuner_drives_op_knobs():
     assert tuned_configs.lookup("ag_gemm", 8, 1000, 3584, 8192) is None
 
 
+def test_decode_gemm_form_selection(monkeypatch):
+    """Host-side choice of the decode GEMM's form: 0 splits (cluster form, launcher's choice) by default, the stream-K
+    split rule only under TDB200_SKINNY_FORM=1, an explicit TDB200_GEMM_AR_SPLITS always, and the cluster shape from the
+    autotuner's active configuration before the tuned table."""
+    from triton_distributed_b200.ops import gemm_ar, tuned_configs
+    from triton_distributed_b200.tools.autotuner import config_space, contextual_autotune
+
+    monkeypatch.delenv("TDB200_GEMM_AR_SPLITS", raising=False)
+    monkeypatch.delenv("TDB200_SKINNY_FORM", raising=False)
+    assert gemm_ar.pick_gemm_ar_splits(128, 5120, 3200) == 0
+    monkeypatch.setenv("TDB200_SKINNY_FORM", "1")
+    assert gemm_ar.pick_gemm_ar_splits(16, 5120, 3200) == 0
+    assert gemm_ar.pick_gemm_ar_splits(128, 5120, 3200) == gemm_ar.pick_stream_k_splits(128, 5120, 3200) == 1
+    assert gemm_ar.pick_stream_k_splits(64, 1280, 12800) == 4          # few tiles, long K: split as far as the SMs allow
+    monkeypatch.setenv("TDB200_GEMM_AR_SPLITS", "3")
+    assert gemm_ar.pick_gemm_ar_splits(16, 5120, 3200) == 3
+    assert [gemm_ar._mpad(m) for m in (1, 16, 17, 64, 65, 129, 256)] == [16, 16, 32, 64, 128, 256, 256]
+    hit = tuned_configs.lookup("skinny_gemm", 1, 16, 2560, 5120)
+    assert hit and 1 <= hit["cluster_nt"] <= 4 and 1 <= hit["cluster_s"] <= 8
+    seen = []
+
+    @contextual_autotune(configs=config_space(cluster_nt=[1, 2], cluster_s=[3]), key=lambda: "k", n_repeat=1, n_warmup=1)
+    def thunk():
+        seen.append(gemm_ar.cluster_config(16, 2560, 5120))
+
+    thunk()
+    assert set(seen) == {(1, 3), (2, 3)}
+
+
 def test_op_log_records_json(tmp_path):
     import json
     import torch
