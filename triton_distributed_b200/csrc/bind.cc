@@ -417,7 +417,7 @@ void gemm_rs_fp8(SymmHeap& h, const at::Tensor& a_q, const at::Tensor& a_s, cons
 
 // Small-M GEMM (decode): out[M,N] = x[M,K] @ w[N,K]^T with split-K; acc / counters are caller-kept scratch.
 void skinny_gemm_bf16(const at::Tensor& x, const at::Tensor& w, at::Tensor& out, at::Tensor& acc, at::Tensor& counters,
-                      int splits, int num_ctas, int cluster_nt, int cluster_s) {
+                      int splits, int num_ctas, int cluster_nt, int cluster_s, int bulk_exchange) {
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16,
               "skinny_gemm: bf16 expected");
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1,
@@ -442,6 +442,7 @@ void skinny_gemm_bf16(const at::Tensor& x, const at::Tensor& w, at::Tensor& out,
   a.splits = splits > 0 ? splits : 0;
   a.cluster_nt = cluster_nt;
   a.cluster_s = cluster_s;
+  a.bulk_exchange = bulk_exchange;
   a.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
   {
     TORCH_CHECK(acc.scalar_type() == at::kFloat && acc.numel() >= M * N, "skinny_gemm: accumulation buffer too small");
@@ -458,7 +459,7 @@ void skinny_gemm_bf16(const at::Tensor& x, const at::Tensor& w, at::Tensor& out,
 void gemm_ar_bf16(SymmHeap& h, const at::Tensor& x, const at::Tensor& w, at::Tensor& out, at::Tensor& acc,
                   at::Tensor& counters, at::Tensor& partial, at::Tensor& flags, at::Tensor& ctx, int64_t m_cap,
                   int64_t max_tiles, int splits, int num_ctas, bool use_multimem, double timeout_s, int cluster_nt,
-                  int cluster_s) {
+                  int cluster_s, int bulk_exchange) {
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16,
               "gemm_ar: bf16 expected");
   TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm_ar: contiguous rows expected");
@@ -486,6 +487,7 @@ void gemm_ar_bf16(SymmHeap& h, const at::Tensor& x, const at::Tensor& w, at::Ten
   a.splits = splits > 0 ? splits : 0;
   a.cluster_nt = cluster_nt;
   a.cluster_s = cluster_s;
+  a.bulk_exchange = bulk_exchange;
   a.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
   a.acc = acc.data_ptr<float>();
   a.counters = reinterpret_cast<uint32_t*>(counters.data_ptr());
@@ -633,11 +635,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("num_ctas"), py::arg("timeout_s"), py::arg("stats") = py::none());
   m.def("gemm_smem_bytes", &tdb::gemm_smem_bytes);
   m.def("skinny_gemm_bf16", &skinny_gemm_bf16, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("acc"),
-        py::arg("counters"), py::arg("splits"), py::arg("num_ctas"), py::arg("cluster_nt") = 0, py::arg("cluster_s") = 0);
+        py::arg("counters"), py::arg("splits"), py::arg("num_ctas"), py::arg("cluster_nt") = 0, py::arg("cluster_s") = 0,
+        py::arg("bulk_exchange") = 0);
   m.def("gemm_ar_bf16", &gemm_ar_bf16, py::arg("heap"), py::arg("x"), py::arg("w"), py::arg("out"), py::arg("acc"),
         py::arg("counters"), py::arg("partial"), py::arg("flags"), py::arg("ctx"), py::arg("m_cap"), py::arg("max_tiles"),
         py::arg("splits"), py::arg("num_ctas"), py::arg("use_multimem"), py::arg("timeout_s"), py::arg("cluster_nt") = 0,
-        py::arg("cluster_s") = 0);
+        py::arg("cluster_s") = 0, py::arg("bulk_exchange") = 0);
   m.def("skinny_gemm_pick_splits", &tdb::skinny_gemm_pick_splits);
   m.def("gemv_bf16", &gemv_bf16, py::arg("x"), py::arg("w"), py::arg("out"), py::arg("norm_w") = py::none(),
         py::arg("eps") = 1e-6, py::arg("silu_mul") = false, py::arg("residual") = py::none(), py::arg("num_ctas") = 0);

@@ -65,6 +65,7 @@ struct KP {
   int tiles_n, kb_total;
   int per_cta;               // (tile, k-block) units per CTA (stream-K form)
   int cluster_s;             // CTAs per column tile (cluster form)
+  int bulk_exchange;         // cluster form: parts travel as bulk copies into the reducing CTA's shared memory
   __nv_bfloat16* out;        // [M, N]
   int64_t ld_out;
   float* acc;                // [tiles_n * 128, M_pad] fp32 split-K accumulation (all zero between calls)
@@ -439,6 +440,14 @@ TDB_DEVICE float4 ld_dsmem_v4(uint32_t cluster_addr) {
                : "memory");
   return v;
 }
+// shared::cta -> shared::cluster bulk copy; completes `bytes` on the destination CTA's mbarrier.  Addresses 16-byte
+// aligned, size a multiple of 16.
+TDB_DEVICE void bulk_copy_to_cluster(uint32_t dst_cluster_addr, const void* src, uint32_t bytes, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   dst_cluster_addr),
+               "r"(smem_u32(src)), "r"(bytes), "r"(bar_cluster_addr)
+               : "memory");
+}
 TDB_DEVICE void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
 TDB_DEVICE void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 
@@ -470,6 +479,10 @@ struct ClusterLayout {
   static constexpr int kBarOffset = kStages * kStageBytes;
   static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 32;
   static constexpr int kTmemCols = pow2_at_least(NT * MPAD);
+  static constexpr int kPartBytes = NT * MPAD * kTN * 4;
+  // room for the part and, behind it, the slices received from up to seven peers (at most the part's size plus one
+  // row per peer)
+  static constexpr bool kBulkOk = 2 * kPartBytes + 8 * NT * kTN * 4 <= kBarOffset;
   static_assert(cluster_form_ok(MPAD, NT), "invalid cluster form");
 };
 
@@ -500,6 +513,7 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       mbar_init(&empty_bar[i], 1);
     }
     mbar_init(&tmem_full[0], 1);
+    mbar_init(&tmem_full[1], 1);   // arrival of the peers' slices (bulk exchange)
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_w);
@@ -514,6 +528,10 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_smem;
   float* part = reinterpret_cast<float*>(smem);   // [M][kCols] fp32, written once the ring has drained
+  uint64_t* recv_bar = &tmem_full[1];
+  const bool bulk = L::kBulkOk && p.bulk_exchange != 0 && S > 1;
+  const int rows_per = (p.M + S - 1) / S;         // rows of the tile that one CTA of the cluster reduces
+  float* recv = part + MPAD * kCols;              // [S - 1][rows_per][kCols] fp32: the peers' rows of this CTA's slice
   // Programmatic dependent launch: the successor may be scheduled from here on, and this kernel may itself be running
   // before its predecessor has finished.  The weights are constant, so the producer fills the ring with weight tiles
   // first; everything the predecessor may write (activations, the epoch, flags, outputs) is touched after pdl_wait().
@@ -612,9 +630,14 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         }
       }
       tc_fence_before_sync();
+      if (bulk) fence_proxy_async_smem();   // the copy engine reads the part
     } else {
       if (lane == 0) report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 52, -1, 0, 0, ct);
       *abort_flag = 1;
+    }
+    if (bulk && threadIdx.x == 64) {
+      const int mine_rows = max(0, min(p.M, (r + 1) * rows_per) - r * rows_per);
+      mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((S - 1) * mine_rows * kCols * 4));
     }
   }
 
@@ -639,16 +662,44 @@ skinny_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     constexpr int kVecRow = kCols / 4;              // float4 per row of the part: 32, 64, 96 or 128
     constexpr int kRowsPerPass = 128 / kVecRow;     // 4, 2, 1 (32 threads idle) or 1
     const int c4 = et % kVecRow;                    // columns [4 * c4, 4 * c4 + 4) of the CTA tile
-    const int rows_per = (p.M + S - 1) / S;
+    const int m_lo = r * rows_per;
     const int m_hi = et < kRowsPerPass * kVecRow ? min(p.M, (r + 1) * rows_per) : 0;
     const bool col_ok = ct * kCols + c4 * 4 < p.N;  // N is a multiple of 4
-    for (int m = r * rows_per + et / kVecRow; m < m_hi; m += kRowsPerPass) {
-      const uint32_t local = smem_u32(part + m * kCols + c4 * 4);
+    bool recv_ok = true;
+    if (bulk) {
+      // push form: every CTA sends each peer the rows that peer reduces (one bulk copy per peer, into the slot of this
+      // CTA in the peer's receive area), then sums its own rows from local shared memory only
+      if (et == 0) {
+        for (int j = 1; j < S; ++j) {
+          const int d = (r + j) % S;
+          const int lo = d * rows_per, hi = min(p.M, (d + 1) * rows_per);
+          if (hi <= lo) continue;
+          const int slot = r < d ? r : r - 1;
+          bulk_copy_to_cluster(mapa_u32(smem_u32(recv + static_cast<size_t>(slot) * rows_per * kCols), d),
+                               part + static_cast<size_t>(lo) * kCols, static_cast<uint32_t>((hi - lo) * kCols * 4),
+                               mapa_u32(smem_u32(recv_bar), d));
+        }
+      }
+      recv_ok = mbar_wait(recv_bar, 0, abort_flag, kMbarTimeoutNs);
+      if (!recv_ok) {
+        if (et == 0) report(p.symm, kTimeoutMbarrier, kKernelGemmAr, 53, -1, r, S, ct);
+        *abort_flag = 1;
+      }
+    }
+    for (int m = m_lo + et / kVecRow; recv_ok && m < m_hi; m += kRowsPerPass) {
       float4 v[8];
       v[0] = *reinterpret_cast<const float4*>(part + m * kCols + c4 * 4);   // the own part: a plain shared load
+      if (bulk) {
 #pragma unroll
-      for (int j = 1; j < 8; ++j)
-        if (j < S) v[j] = ld_dsmem_v4(mapa_u32(local, static_cast<uint32_t>((r + j) % S)));
+        for (int j = 1; j < 8; ++j)
+          if (j < S)
+            v[j] = *reinterpret_cast<const float4*>(recv + (static_cast<size_t>(j - 1) * rows_per + (m - m_lo)) * kCols + c4 * 4);
+      } else {
+        const uint32_t local = smem_u32(part + m * kCols + c4 * 4);
+#pragma unroll
+        for (int j = 1; j < 8; ++j)
+          if (j < S) v[j] = ld_dsmem_v4(mapa_u32(local, static_cast<uint32_t>((r + j) % S)));
+      }
       float4 a = v[0];
 #pragma unroll
       for (int j = 1; j < 8; ++j)
@@ -941,6 +992,7 @@ cudaError_t launch_skinny_gemm(const SkinnyGemmArgs& a, cudaStream_t stream) {
   const int force_nt = explicit_cfg ? a.cluster_nt : env_nt;
   const int force_s = explicit_cfg ? a.cluster_s : env_s;
   p.cluster_s = 0;
+  p.bulk_exchange = a.bulk_exchange;
   if (form != 1 && a.splits < 1 && a.N % 4 == 0) {
     bool launched = false, whole_tiles = false;
     cudaError_t e;

@@ -146,6 +146,8 @@ struct SkinnyGemmArgs {
                            // column tile
   int cluster_nt;          // cluster form: CTA tile width in units of 128 columns (1..4), 0 = chosen by the launcher
   int cluster_s;           // cluster form: CTAs per tile (1..8), 0 = chosen by the launcher
+  int bulk_exchange;       // cluster form: 1 = parts travel as bulk copies into the reducing CTA's shared memory,
+                           // 0 = the reducing CTA loads them from its peers' shared memory
   int num_ctas;
   float* acc;              // fp32 [m_cap, N], all zero between calls
   uint32_t* counters;      // [ceil(N/128)], zero between calls

@@ -22,6 +22,15 @@ from ..utils.oplog import logged_op
 from .common import new_ctx_dev, ref_all_reduce, sm_count
 
 MAX_SKINNY_M = 256
+# Exchange of the split-K parts inside a cluster: "ld" = the reducing CTA loads its rows from the peers' shared memory,
+# "bulk" = every CTA sends each peer its rows with one bulk copy.  TDB200_SKINNY_EXCHANGE overrides.
+SKINNY_EXCHANGE = "ld"
+
+
+def _bulk_exchange() -> int:
+    import os
+    return 1 if os.environ.get("TDB200_SKINNY_EXCHANGE", SKINNY_EXCHANGE) == "bulk" else 0
+
 _SCRATCH: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
 
 
@@ -66,7 +75,7 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)
     acc, cnt = _scratch(x.device, M * N, (N + 127) // 128)
     nt, s = cluster if cluster is not None else (cluster_config(M, N, K) if splits < 1 else (0, 0))
-    lib.skinny_gemm_bf16(x, w, out, acc, cnt, splits, 0, nt, s)
+    lib.skinny_gemm_bf16(x, w, out, acc, cnt, splits, 0, nt, s, _bulk_exchange())
     return out
 
 
@@ -224,7 +233,8 @@ def gemm_allreduce_op(ctx: GemmARContext, a: torch.Tensor, b: torch.Tensor, cfg=
     if "cluster_nt" in tuned_now and "cluster_s" in tuned_now and int(splits) < 1:
         nt, s = int(tuned_now["cluster_nt"]), int(tuned_now["cluster_s"])
     lib.gemm_ar_bf16(rt.heap, a, b, output, ctx.acc, ctx.counters, ctx.partial, ctx.flags, ctx.ctx_dev, ctx.m_cap,
-                     ctx.max_tiles, int(splits), 0, bool(ctx.use_multimem), rt.config.wait_timeout_s, nt, s)
+                     ctx.max_tiles, int(splits), 0, bool(ctx.use_multimem), rt.config.wait_timeout_s, nt, s,
+                     _bulk_exchange())
     ctx.calls += 1
     return output
 
