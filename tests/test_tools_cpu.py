@@ -132,6 +132,27 @@ def test_decode_gemm_form_selection(monkeypatch):
     assert set(seen) == {(1, 3), (2, 3)}
 
 
+def test_cluster_exchange_index_arithmetic():
+    """The row slices, receive slots and shared-memory bounds of the decode GEMM's cluster exchange
+    (csrc/gemm_ar_sm100.cu, skinny_cluster_kernel), restated on the host: the S slices partition the M rows, every
+    destination sees its S - 1 sources in distinct slots, and the receive area never exceeds the room the kernel
+    reserves behind the part (the part's size plus eight rows)."""
+    for mpad in (16, 32, 64, 128, 256):
+        for M in range(1, mpad + 1):
+            if M <= mpad // 2 and mpad > 16:
+                continue                                   # a smaller pad would have been chosen
+            for S in range(1, 9):
+                rows_per = -(-M // S)
+                covered = []
+                for r in range(S):
+                    covered += list(range(r * rows_per, min(M, (r + 1) * rows_per)))
+                assert covered == list(range(M))
+                for d in range(S):
+                    slots = sorted((r if r < d else r - 1) for r in range(S) if r != d)
+                    assert slots == list(range(S - 1))
+                assert (S - 1) * rows_per <= mpad + 8
+
+
 def test_op_log_records_json(tmp_path):
     import json
     import torch
