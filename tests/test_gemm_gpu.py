@@ -105,6 +105,24 @@ def test_skinny_gemm_split_k(shape):
         assert err < 2e-2, f"skinny {shape} splits={splits}: rel err {err}"
 
 
+def test_skinny_gemm_stream_k_scratch_covers_the_token_pad():
+    """65 tokens are padded to 128 in the column-major accumulation buffer of the stream-K form: the scratch must be
+    sized by the pad (150 column tiles here, so the cluster form does not apply and every tile is split)."""
+    from triton_distributed_b200.ops import gemm_ar, skinny_gemm
+
+    M, N, K = 65, 19200, 1024
+    assert gemm_ar.split_scratch_elems(M, N) == 19200 * 128
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    for splits in (0, 3):
+        for _ in range(2):
+            out = skinny_gemm(a, b, splits=splits)
+        torch.cuda.synchronize()
+        err = (out.float() - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+        assert err < 2e-2, f"splits={splits}: rel err {err}"
+
+
 @pytest.mark.parametrize("shape,cluster", [
     ((16, 2560, 5120), (1, 6)), ((16, 2560, 5120), (2, 8)), ((16, 2560, 5120), (3, 4)), ((16, 2560, 5120), (4, 3)),
     ((128, 5120, 2048), (1, 3)), ((128, 5120, 2048), (2, 5)), ((128, 5120, 2048), (3, 2)),

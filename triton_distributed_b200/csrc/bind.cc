@@ -445,7 +445,9 @@ void skinny_gemm_bf16(const at::Tensor& x, const at::Tensor& w, at::Tensor& out,
   a.bulk_exchange = bulk_exchange;
   a.num_ctas = num_ctas > 0 ? num_ctas : sm_count();
   {
-    TORCH_CHECK(acc.scalar_type() == at::kFloat && acc.numel() >= M * N, "skinny_gemm: accumulation buffer too small");
+    // the stream-K form accumulates column-major: [ceil(N / 128) * 128 columns][M_pad tokens] fp32
+    TORCH_CHECK(acc.scalar_type() == at::kFloat && acc.numel() >= (N + 127) / 128 * 128 * mpad,
+                "skinny_gemm: accumulation buffer too small (needs ceil(N / 128) * 128 * M_pad floats)");
     TORCH_CHECK(counters.scalar_type() == at::kInt && counters.numel() >= (N + 127) / 128, "skinny_gemm: counters too small");
     a.acc = acc.data_ptr<float>();
     a.counters = reinterpret_cast<uint32_t*>(counters.data_ptr());
@@ -469,7 +471,9 @@ void gemm_ar_bf16(SymmHeap& h, const at::Tensor& x, const at::Tensor& w, at::Ten
   const int W = h.world();
   const bool mc = use_multimem && h.has_multicast();
   TORCH_CHECK(static_cast<uint64_t>(partial.numel()) >= 2ull * (mc ? 1 : W) * m_cap * N, "gemm_ar: partial buffer too small");
-  TORCH_CHECK(acc.numel() >= m_cap * N && counters.numel() >= (N + 127) / 128, "gemm_ar: scratch too small");
+  TORCH_CHECK(acc.scalar_type() == at::kFloat && acc.numel() >= (N + 127) / 128 * 128 * tdb::skinny_gemm_mpad(M) &&
+                  counters.numel() >= (N + 127) / 128,
+              "gemm_ar: scratch too small (the accumulation buffer needs ceil(N / 128) * 128 * M_pad floats)");
   c10::cuda::CUDAGuard guard(x.device());
   tdb::SkinnyGemmArgs a;
   std::memset(&a, 0, sizeof(a));

@@ -50,6 +50,12 @@ def _mpad(m: int) -> int:
     return 16 if m <= 16 else 32 if m <= 32 else 64 if m <= 64 else 128 if m <= 128 else 256
 
 
+def split_scratch_elems(m: int, n: int) -> int:
+    """fp32 elements of the stream-K form's accumulation buffer for up to ``m`` tokens and ``n`` columns: column-major
+    [ceil(n / 128) * 128][token pad], so that a thread's consecutive tokens are contiguous (vector reductions)."""
+    return (n + 127) // 128 * 128 * _mpad(m)
+
+
 def cluster_config(M: int, N: int, K: int) -> Tuple[int, int]:
     """(tile width in 128-column blocks, CTAs per tile) of the cluster form for this problem: what the autotuner is
     trying, else the measured winner from ``ops.tuned_configs``, else (0, 0) = the launcher's cost model."""
@@ -73,7 +79,7 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
     N = w.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)
-    acc, cnt = _scratch(x.device, M * N, (N + 127) // 128)
+    acc, cnt = _scratch(x.device, split_scratch_elems(M, N), (N + 127) // 128)
     nt, s = cluster if cluster is not None else (cluster_config(M, N, K) if splits < 1 else (0, 0))
     lib.skinny_gemm_bf16(x, w, out, acc, cnt, splits, 0, nt, s, _bulk_exchange())
     return out
@@ -139,7 +145,7 @@ def create_gemm_ar_context(ar_stream=None, rank: Optional[int] = None, world_siz
         slots = 1 if (use_multimem and rt.has_multicast) else world_size
         ctx.partial = rt.symm_tensor((2, slots, ctx.m_cap, N), dtype, zero=False)
         ctx.flags = rt.symm_tensor((world_size, ctx.max_tiles), torch.int32)
-        ctx.acc = torch.zeros(ctx.m_cap * N, dtype=torch.float32, device=rt.device)
+        ctx.acc = torch.zeros(split_scratch_elems(ctx.m_cap, N), dtype=torch.float32, device=rt.device)
         ctx.counters = torch.zeros(ctx.max_tiles, dtype=torch.int32, device=rt.device)
         ctx.ctx_dev = new_ctx_dev(rt)
         if max_M > MAX_SKINNY_M:
