@@ -1,6 +1,7 @@
 """Sweep of the decode GEMM's cluster form on one GPU: for every Qwen3-32B per-rank linear shape (TP given by --tp) and
 token count, times every feasible (tile width, cluster size) pair, the launcher's own choice, the stream-K form and
-torch.matmul, and prints one JSON line per problem with the winner in the form `ops/tuned_configs.py` takes.
+torch.matmul, and prints one JSON line per problem with the winner in the form `ops/tuned_configs.py` takes (`--json-out FILE`
+writes the winners as a table that `TDB200_TUNED_CONFIGS=FILE` loads in front of the built-in one).
 
   python benchmarks/tune_skinny.py --tp 8,4,2 --Ms 16,32,64,128
 
@@ -50,8 +51,11 @@ def main():
     ap.add_argument("--tp", default="8,4,2")
     ap.add_argument("--Ms", default="16,32,64,128")
     ap.add_argument("--max-nt", type=int, default=4)
+    ap.add_argument("--json-out", default=None,
+                    help="write the winners as a table file for the TDB200_TUNED_CONFIGS environment variable")
     args = ap.parse_args()
     seen = set()
+    winners = []
     for tp in [int(t) for t in args.tp.split(",")]:
         H, I, Hq, Hkv, D = 5120, 25600 // tp, 64 // tp, max(1, 8 // tp), 128
         shapes = {"qkv": ((Hq + 2 * Hkv) * D, H), "o_proj": (H, Hq * D), "gate_up": (2 * I, H), "down": (H, I)}
@@ -93,9 +97,14 @@ def main():
                     rec["best"] = {"cluster_nt": nt, "cluster_s": s, "us": grid[best]}
                     rec["table_line"] = (f'("skinny_gemm", 1, {ops.gemm_ar._mpad(M)}, {N}, {K}): '
                                          f'{{"cluster_nt": {nt}, "cluster_s": {s}}},')
+                    winners.append({"op": "skinny_gemm", "world": 1, "rows": ops.gemm_ar._mpad(M), "n": N, "k": K,
+                                    "config": {"cluster_nt": nt, "cluster_s": s}})
                 print(json.dumps(rec), flush=True)
             del ws
             torch.cuda.empty_cache()
+    if args.json_out:
+        with open(args.json_out, "w") as f:
+            json.dump(winners, f, indent=1)
 
 
 if __name__ == "__main__":

@@ -132,6 +132,23 @@ def test_decode_gemm_form_selection(monkeypatch):
     assert set(seen) == {(1, 3), (2, 3)}
 
 
+def test_user_tuned_table_comes_first(tmp_path, monkeypatch):
+    from triton_distributed_b200.ops import tuned_configs
+
+    path = tmp_path / "tuned.json"
+    path.write_text(json.dumps([
+        {"op": "skinny_gemm", "world": 1, "rows": 16, "n": 2560, "k": 5120, "config": {"cluster_nt": 1, "cluster_s": 5}},
+        {"op": "skinny_gemm", "world": 1, "rows": 64, "n": 777, "k": 888, "config": {"cluster_nt": 1, "cluster_s": 2}}]))
+    monkeypatch.setenv("TDB200_TUNED_CONFIGS", str(path))
+    monkeypatch.setattr(tuned_configs, "_USER_TABLE", None)
+    assert tuned_configs.lookup("skinny_gemm", 1, 16, 2560, 5120) == {"cluster_nt": 1, "cluster_s": 5}   # overrides
+    assert tuned_configs.lookup("skinny_gemm", 1, 64, 777, 888) == {"cluster_nt": 1, "cluster_s": 2}     # adds
+    assert tuned_configs.lookup("ag_gemm", 8, 1024, 3584, 8192)["n_comm_ctas"] == 4                      # built-in stays
+    monkeypatch.setattr(tuned_configs, "_USER_TABLE", None)
+    monkeypatch.delenv("TDB200_TUNED_CONFIGS")
+    assert tuned_configs.lookup("skinny_gemm", 1, 64, 777, 888) is None
+
+
 def test_cluster_exchange_index_arithmetic():
     """The row slices, receive slots and shared-memory bounds of the decode GEMM's cluster exchange
     (csrc/gemm_ar_sm100.cu, skinny_cluster_kernel), restated on the host: the S slices partition the M rows, every

@@ -31,5 +31,30 @@ _TABLE: Dict[Tuple[str, int, int, int, int], Dict] = {
 }
 
 
+_USER_TABLE: Optional[Dict[Tuple[str, int, int, int, int], Dict]] = None
+
+
+def _user_table() -> Dict[Tuple[str, int, int, int, int], Dict]:
+    """Entries from the JSON file named by ``TDB200_TUNED_CONFIGS`` (read once per process): a list of
+    ``{"op", "world", "rows", "n", "k", "config": {...}}`` records, as ``benchmarks/tune_skinny.py --json-out`` writes
+    them.  They come before the built-in table, so a box can carry its own winners without a source change."""
+    global _USER_TABLE
+    if _USER_TABLE is None:
+        import json
+        import os
+
+        table: Dict[Tuple[str, int, int, int, int], Dict] = {}
+        path = os.environ.get("TDB200_TUNED_CONFIGS", "")
+        if path:
+            with open(path) as f:
+                for rec in json.load(f):
+                    key = (str(rec["op"]), int(rec["world"]), int(rec["rows"]), int(rec["n"]), int(rec["k"]))
+                    table[key] = dict(rec["config"])
+        _USER_TABLE = table
+    return _USER_TABLE
+
+
 def lookup(op: str, world: int, rows_per_rank: int, n_local: int, k: int) -> Optional[Dict]:
-    return _TABLE.get((op, int(world), int(rows_per_rank), int(n_local), int(k)))
+    key = (op, int(world), int(rows_per_rank), int(n_local), int(k))
+    user = _user_table()
+    return user[key] if key in user else _TABLE.get(key)
