@@ -62,11 +62,11 @@ def cluster_config(M: int, N: int, K: int) -> Tuple[int, int]:
     tuned = current_config()
     if "cluster_nt" in tuned and "cluster_s" in tuned:
         return int(tuned["cluster_nt"]), int(tuned["cluster_s"])
-    from .tuned_configs import lookup
-    cfg = lookup("skinny_gemm", 1, _mpad(M), N, K)
-    if cfg and sm_count(torch.cuda.current_device()) == 148:   # the table was measured on 148 SMs
-        return int(cfg["cluster_nt"]), int(cfg["cluster_s"])
-    return 0, 0
+    from .tuned_configs import lookup, lookup_user
+    cfg = lookup_user("skinny_gemm", 1, _mpad(M), N, K)
+    if cfg is None and sm_count(torch.cuda.current_device()) == 148:   # the built-in table was measured on 148 SMs
+        cfg = lookup("skinny_gemm", 1, _mpad(M), N, K)
+    return (int(cfg["cluster_nt"]), int(cfg["cluster_s"])) if cfg else (0, 0)
 
 
 def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, splits: int = 0,

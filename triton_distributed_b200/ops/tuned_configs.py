@@ -54,6 +54,11 @@ def _user_table() -> Dict[Tuple[str, int, int, int, int], Dict]:
     return _USER_TABLE
 
 
+def lookup_user(op: str, world: int, rows_per_rank: int, n_local: int, k: int) -> Optional[Dict]:
+    """The entry of the user's table only (measured on the box it runs on)."""
+    return _user_table().get((op, int(world), int(rows_per_rank), int(n_local), int(k)))
+
+
 def lookup(op: str, world: int, rows_per_rank: int, n_local: int, k: int) -> Optional[Dict]:
     key = (op, int(world), int(rows_per_rank), int(n_local), int(k))
     user = _user_table()
