@@ -132,6 +132,35 @@ def test_decode_gemm_form_selection(monkeypatch):
     assert set(seen) == {(1, 3), (2, 3)}
 
 
+def test_decode_gemm_routes_misaligned_outputs_to_the_scalar_store_form(monkeypatch):
+    """The cluster form stores four bf16 values at a time.  An output view whose rows do not start on 8-byte boundaries
+    must go through the stream-K form (splits >= 1), and an explicit cluster shape on such a view is refused."""
+    import pytest
+    from triton_distributed_b200 import _native
+    from triton_distributed_b200.ops import gemm_ar
+
+    calls = []
+
+    class FakeLib:
+        def skinny_gemm_bf16(self, x, w, out, acc, cnt, splits, num_ctas, nt, s, bulk):
+            calls.append((splits, nt, s, acc.numel()))
+
+    monkeypatch.setattr(_native, "load", lambda *a, **k: FakeLib())
+    monkeypatch.setattr(gemm_ar, "cluster_config", lambda M, N, K: (0, 0))
+    monkeypatch.setattr(gemm_ar, "_scratch", lambda dev, need_acc, need_tiles: (torch.zeros(need_acc), torch.zeros(need_tiles)))
+    x = torch.zeros(65, 64, dtype=torch.bfloat16)
+    w = torch.zeros(640, 64, dtype=torch.bfloat16)
+    big = torch.zeros(65, 648, dtype=torch.bfloat16)
+    gemm_ar.skinny_gemm(x, w, out=big[:, :640])                 # rows 1296 bytes apart, start aligned: cluster form
+    gemm_ar.skinny_gemm(x, w, out=big[:, 1:641])                # starts 2 bytes in: stream-K form
+    odd = torch.zeros(65, 641, dtype=torch.bfloat16)
+    gemm_ar.skinny_gemm(x, w, out=odd[:, :640])                 # row pitch 1282 bytes: stream-K form
+    assert [c[0] for c in calls] == [0, 1, 1]
+    assert all(c[3] >= 640 * 128 for c in calls)                # scratch sized by the token pad (65 -> 128)
+    with pytest.raises(ValueError):
+        gemm_ar.skinny_gemm(x, w, out=big[:, 1:641], cluster=(1, 2))
+
+
 def test_user_tuned_table_comes_first(tmp_path, monkeypatch):
     from triton_distributed_b200.ops import tuned_configs
 

@@ -69,6 +69,11 @@ def cluster_config(M: int, N: int, K: int) -> Tuple[int, int]:
     return (int(cfg["cluster_nt"]), int(cfg["cluster_s"])) if cfg else (0, 0)
 
 
+def _rows_aligned(t: torch.Tensor, nbytes: int) -> bool:
+    """Whether every row of the 2-D tensor starts on an ``nbytes`` boundary."""
+    return t.data_ptr() % nbytes == 0 and (t.stride(0) * t.element_size()) % nbytes == 0
+
+
 def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, splits: int = 0,
                 cluster: Optional[Tuple[int, int]] = None) -> torch.Tensor:
     """``x`` [M<=256, K] @ ``w`` [N, K]^T with the weight-streaming kernel.  ``splits`` >= 1 asks for the stream-K form
@@ -80,6 +85,12 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
     if out is None:
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)
     acc, cnt = _scratch(x.device, split_scratch_elems(M, N), (N + 127) // 128)
+    if splits < 1 and not _rows_aligned(out, 8):
+        # the cluster form stores four bf16 values at a time: an output view whose rows do not start on 8-byte boundaries
+        # goes through the stream-K form, which stores single values
+        if cluster is not None and cluster[0] >= 1:
+            raise ValueError("skinny_gemm: the cluster form needs output rows that start on 8-byte boundaries")
+        splits, cluster = max(1, pick_stream_k_splits(M, N, K)), None
     nt, s = cluster if cluster is not None else (cluster_config(M, N, K) if splits < 1 else (0, 0))
     lib.skinny_gemm_bf16(x, w, out, acc, cnt, splits, 0, nt, s, _bulk_exchange())
     return out
@@ -234,6 +245,10 @@ def gemm_allreduce_op(ctx: GemmARContext, a: torch.Tensor, b: torch.Tensor, cfg=
     tuned = current_config()
     splits = tuned["gemm_ar_splits"] if "gemm_ar_splits" in tuned else (
         ctx.splits if ctx.splits is not None else pick_gemm_ar_splits(M, N, K))
+    final = None
+    if not _rows_aligned(output, 16):
+        # the cross-rank sum stores 16 bytes at a time: a misaligned output view is filled through an aligned buffer
+        final, output = output, torch.empty((M, N), dtype=a.dtype, device=a.device)
     nt, s = 0, 0          # the launcher's choice: in all-reduce mode always 128-column tiles (one exchange per cluster)
     tuned_now = current_config()
     if "cluster_nt" in tuned_now and "cluster_s" in tuned_now and int(splits) < 1:
@@ -242,6 +257,9 @@ def gemm_allreduce_op(ctx: GemmARContext, a: torch.Tensor, b: torch.Tensor, cfg=
                      ctx.max_tiles, int(splits), 0, bool(ctx.use_multimem), rt.config.wait_timeout_s, nt, s,
                      _bulk_exchange())
     ctx.calls += 1
+    if final is not None:
+        final.copy_(output)
+        return final
     return output
 
 
