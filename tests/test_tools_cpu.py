@@ -160,6 +160,23 @@ def test_decode_gemm_routes_misaligned_outputs_to_the_scalar_store_form(monkeypa
     with pytest.raises(ValueError):
         gemm_ar.skinny_gemm(x, w, out=big[:, 1:641], cluster=(1, 2))
 
+    # a table entry that does not fit this GPU is a hint: one refusal, then the launcher's own choice from then on
+    class PickyLib(FakeLib):
+        def skinny_gemm_bf16(self, x, w, out, acc, cnt, splits, num_ctas, nt, s, bulk):
+            calls.append((splits, nt, s, acc.numel()))
+            if (nt, s) == (2, 6):
+                raise RuntimeError("launch_skinny_gemm: invalid configuration argument")
+
+    del calls[:]
+    monkeypatch.setattr(_native, "load", lambda *a, **k: PickyLib())
+    monkeypatch.setattr(gemm_ar, "cluster_config", lambda M, N, K: (2, 6))
+    monkeypatch.setattr(gemm_ar, "_UNFIT_TABLE_SHAPES", set())
+    gemm_ar.skinny_gemm(x, w, out=big[:, :640])
+    gemm_ar.skinny_gemm(x, w, out=big[:, :640])
+    assert [(c[1], c[2]) for c in calls] == [(2, 6), (0, 0), (0, 0)]
+    with pytest.raises(RuntimeError):
+        gemm_ar.skinny_gemm(x, w, out=big[:, :640], cluster=(2, 6))      # an explicit request stays a demand
+
 
 def test_user_tuned_table_comes_first(tmp_path, monkeypatch):
     from triton_distributed_b200.ops import tuned_configs

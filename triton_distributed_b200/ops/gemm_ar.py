@@ -32,6 +32,7 @@ def _bulk_exchange() -> int:
     return 1 if os.environ.get("TDB200_SKINNY_EXCHANGE", SKINNY_EXCHANGE) == "bulk" else 0
 
 _SCRATCH: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
+_UNFIT_TABLE_SHAPES: set = set()   # (token pad, N, K, tile width, cluster size) from the tuned table that did not fit here
 
 
 def _scratch(device, need_acc: int, need_tiles: int):
@@ -92,7 +93,18 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = 
             raise ValueError("skinny_gemm: the cluster form needs output rows that start on 8-byte boundaries")
         splits, cluster = max(1, pick_stream_k_splits(M, N, K)), None
     nt, s = cluster if cluster is not None else (cluster_config(M, N, K) if splits < 1 else (0, 0))
-    lib.skinny_gemm_bf16(x, w, out, acc, cnt, splits, 0, nt, s, _bulk_exchange())
+    if cluster is None and (_mpad(M), N, K, nt, s) in _UNFIT_TABLE_SHAPES:
+        nt, s = 0, 0
+    try:
+        lib.skinny_gemm_bf16(x, w, out, acc, cnt, splits, 0, nt, s, _bulk_exchange())
+    except RuntimeError:
+        # a shape from the tuned table that this GPU cannot hold in one wave of clusters (the SMs per GPC differ from
+        # part to part) is a hint, not a demand: remember it and let the launcher choose.  The refusal happens on the
+        # host before anything is launched.
+        if cluster is not None or (nt, s) == (0, 0):
+            raise
+        _UNFIT_TABLE_SHAPES.add((_mpad(M), N, K, nt, s))
+        lib.skinny_gemm_bf16(x, w, out, acc, cnt, splits, 0, 0, 0, _bulk_exchange())
     return out
 
 
