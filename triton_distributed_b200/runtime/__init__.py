@@ -254,8 +254,16 @@ class Runtime:
             self._barrier_flags = None
             self.heap.destroy()
             self.heap = None
-        # The process group is left to torch's own exit handling: destroying it here can block when CUDA graphs that
-        # captured NCCL work are still alive in the caller.
+        # On a GPU the process group is left to torch's own exit handling: destroying it here can block when CUDA graphs
+        # that captured NCCL work are still alive in the caller.  CPU ranks (gloo) destroy it: a gloo group that is
+        # still alive at interpreter exit can abort the process from its background threads
+        # ("terminate called without an active exception").
+        if not self.is_cuda and self._own_pg and dist.is_initialized():
+            try:
+                dist.barrier()
+                dist.destroy_process_group()
+            except Exception:
+                pass
 
 
 class Watchdog:
