@@ -91,3 +91,11 @@ def wait_eq(flag: torch.Tensor, value: int, stream=None, geq: bool = False, time
 
 notify = set_signal
 wait = wait_eq
+
+
+def consume_token(value, token=None):
+    """The reference ties a loaded value to the token of a preceding ``wait`` so that the compiler cannot hoist the
+    load above the wait (python/triton_dist/language/distributed_ops.py:75-87).  Here the ordering is the stream's: work
+    enqueued after ``wait`` runs after it, so the value is returned unchanged.  (Inside the CUDA kernels of this
+    package the same guarantee comes from the acquire load in ``wait_until``.)"""
+    return value

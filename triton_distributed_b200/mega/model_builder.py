@@ -228,6 +228,23 @@ class ModelBuilder:
         self._wrote(s2, out)
         return s2
 
+    # ------------------------------------------------------------------ prefill tasks of the reference
+    def _prefill_not_built(self, name: str):
+        raise NotImplementedError(
+            f"ModelBuilder.{name}: the task interpreter of this package is decode-only (one token per sequence and "
+            "step).  Prefill runs through the layer path (models.DenseLLM.inference with ops.flash_attn_varlen, the "
+            "tcgen05 prefill kernel); the megakernel takes over from the first decode step "
+            "(reference: mega_triton_kernel/models/model_builder.py make_flash_attn / make_qkv_pack_*).")
+
+    def make_flash_attn(self, *args, **kwargs):
+        self._prefill_not_built("make_flash_attn")
+
+    def make_qkv_pack_flash_attn(self, *args, **kwargs):
+        self._prefill_not_built("make_qkv_pack_flash_attn")
+
+    def make_qkv_pack_qk_norm_rope_split_v(self, *args, **kwargs):
+        self._prefill_not_built("make_qkv_pack_qk_norm_rope_split_v")
+
     def make_silu_mul_up(self, x: torch.Tensor, out: torch.Tensor) -> int:
         I = x.shape[-1] // 2
         nchunks = max(1, min(16, self.num_sms // max(1, self.batch), I // 2048))

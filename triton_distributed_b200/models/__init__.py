@@ -4,6 +4,7 @@ from .kv_cache import KV_Cache, PagedKVCache  # noqa: F401
 from .safetensors_io import SafetensorsFile, ShardedCheckpoint, save_file  # noqa: F401
 from .dense import DenseLLM, DenseLLMLayer  # noqa: F401
 from .engine import Engine  # noqa: F401
+from .qwen_moe import Qwen3MoE, Qwen3MoELayer  # noqa: F401
 
 
 class AutoLLM:

@@ -11,7 +11,8 @@ from .reduce_scatter import (ReduceScatter2DContext, create_reduce_scater_2d_ctx
                              reduce_scatter_2d_op, ring_reduce)
 from .allgather import (AllGatherMethod, get_auto_all_gather_method, FastAllGatherContext,  # noqa: F401
                         create_fast_allgather_context, fast_allgather, all_gather_ll, all_gather,
-                        cp_engine_producer_all_gather_intra_node)
+                        cp_engine_producer_all_gather_intra_node,
+                        cp_engine_producer_all_gather_inter_node)
 from .elementwise import (rmsnorm, silu_mul, residual_add, qk_norm_rope_kv, embedding, argmax, sample_token,  # noqa: F401
                           abs_sum)
 from .attention import (flash_attn_varlen, gqa_fwd_batch_decode, gqa_fwd_batch_decode_intra_rank,  # noqa: F401

@@ -158,3 +158,14 @@ def cp_engine_producer_all_gather_intra_node(rank, num_ranks, local_tensor, remo
             remote_buffers[rank][src * n:(src + 1) * n].copy_(remote_buffers[src][src * n:(src + 1) * n], non_blocking=True)
             if signal_buffers is not None:
                 lib.stream_write_value32(signal_buffers[rank][src:src + 1].data_ptr(), 1)
+
+
+def cp_engine_producer_all_gather_inter_node(rank, num_ranks, local_tensor, remote_buffers, ag_stream=None,
+                                             signal_buffers=None, all_gather_method=AllGatherMethod.Auto,
+                                             internode_ag_stream=None, local_world_size=None):
+    """The reference's two-level producer (allgather.py:539: peers of the same node by copy engine, other nodes over the
+    network).  One NVSwitch domain has no second level, so every peer is a same-node peer and the copies are those of
+    :func:`cp_engine_producer_all_gather_intra_node`; ``internode_ag_stream`` and ``local_world_size`` are accepted for
+    signature compatibility."""
+    return cp_engine_producer_all_gather_intra_node(rank, num_ranks, local_tensor, remote_buffers, ag_stream,
+                                                    signal_buffers, all_gather_method)
