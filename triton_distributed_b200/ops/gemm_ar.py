@@ -152,13 +152,15 @@ def create_gemm_ar_context(ar_stream=None, rank: Optional[int] = None, world_siz
     rank = rt.rank if rank is None else rank
     world_size = rt.world_size if world_size is None else world_size
     import os
-    # With two ranks the push form (each rank stores its partial tile into the peer's slot, one NVLink latency) beat
-    # the NVLS form (flag, then multimem.ld_reduce: two latencies) by 2-10 %; with more ranks the switch does the sum.
+    # The push form (each rank stores its partial tile into every peer's slot: one NVLink latency) beat the NVLS form
+    # (flag, then multimem.ld_reduce: two latencies) by 2-10 % on two ranks at every size, and by 9 % on four ranks at
+    # 16 tokens (29.9 against 32.5 us); from 64 tokens on four ranks the switch's sum wins (36.6 against 38.7 us).  The
+    # form is a property of the context (the partial buffers differ), so it follows the context's token capacity.
     # TDB200_GEMM_AR_MC=0 / 1 forces one form.
     mc_env = os.environ.get("TDB200_GEMM_AR_MC", "")
     if mc_env in ("0", "1"):
         use_multimem = mc_env == "1"
-    elif world_size == 2:
+    elif world_size == 2 or max_M <= 32:
         use_multimem = False
     ctx = GemmARContext(rt=rt, rank=rank, world_size=world_size, max_M=max_M, N=N, dtype=dtype,
                         use_multimem=use_multimem)
